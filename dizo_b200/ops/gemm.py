@@ -1,0 +1,75 @@
+"""``linear``: out = act((x @ w.T + bias) * scale) + residual.
+
+CUDA tensors run the tcgen05/TMEM kernel in ``csrc/gemm_sm100.cu``; CPU tensors run the
+plain PyTorch statement of the same op (the oracle the GPU tests compare against).
+Replaces the ``nn.Linear`` calls of the reference's OPT blocks
+(large_models/ht_opt.py:178-197, :274, :356-359).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
+
+
+def linear_reference(x, w, bias=None, act=None, residual=None, scale: float = 1.0,
+                     out_dtype=None):
+    """fp32 statement of the op (any device)."""
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if scale != 1.0:
+        y = y * scale
+    if act == "relu":
+        y = torch.relu(y)
+    elif act == "gelu":
+        y = F.gelu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype or x.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
+           residual: torch.Tensor | None = None, scale: float = 1.0,
+           out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
+           tile_n: int = 0) -> torch.Tensor:
+    """x [..., K] (bf16), w [N, K] (bf16) -> [..., N] in ``out_dtype`` (bf16 or fp32)."""
+    if not x.is_cuda:
+        y = linear_reference(x, w, bias, act, residual, scale, out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "kernel path is bf16"
+    K = x.shape[-1]
+    N = w.shape[0]
+    assert w.shape[1] == K
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    out_dtype = out_dtype or torch.bfloat16
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    out2 = out.reshape(-1, N)
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, N)
+        assert res2.dtype == torch.bfloat16 and res2.stride(-1) == 1
+    assert w.stride(-1) == 1 and out2.stride(-1) == 1
+    if M == 0:
+        return out.reshape(*x.shape[:-1], N)
+    rc = _lib.lib().dz_gemm_bf16_tn(
+        _lib.ptr(x2), ctypes.c_longlong(x2.stride(0)), _lib.ptr(w), ctypes.c_longlong(w.stride(0)),
+        _lib.ptr(out2), ctypes.c_longlong(out2.stride(0)), _lib.ptr(bias), _lib.ptr(res2),
+        ctypes.c_longlong(res2.stride(0) if res2 is not None else 0),
+        M, N, K, ACT[act], int(out_dtype == torch.float32), ctypes.c_float(scale), tile_n,
+        _lib.ptr(_lib.err_word(x.device)), _lib.stream_ptr())
+    _lib.check(rc, "dz_gemm_bf16_tn")
+    return out.reshape(*x.shape[:-1], N)

@@ -1,0 +1,350 @@
+// Zeroth-order parameter sweeps over a flat bf16 parameter arena.
+//
+// All trainable tensors of a model live in one bf16 buffer.  A table describes them:
+// {offset, numel, tensor id (RNG stream), DiZO slot or -1, offset of the anchor copy}.
+// Tensor starts are aligned to ZO_CHUNK (2048) elements, so every 2048-element chunk of
+// the arena belongs to exactly one tensor, and one launch sweeps any contiguous range
+// of the arena (one layer, or the whole model).
+//
+// dz_zo_sweep computes, per element of every tensor in the range,
+//     v   = theta                                   (bf16 -> fp32)
+//     v   = anchor + alpha[slot] * (v - anchor)     if BLEND and the tensor has a slot
+//     v  += c1 * z(seed1) + c2 * z(seed2)           z regenerated from Philox in registers
+//     dst = bf16(v)                                 round-to-nearest or stochastic
+//     chunk_sq[chunk] = sum (v - anchor)^2          if NORM and the tensor has a slot
+// dst may be the arena itself (in-place perturb / restore / update / projection) or a
+// staging buffer (perturbed or projected weights for one forward, theta untouched).
+// Coefficients can come from device memory (c = coef_scale * *coef_ptr), so the
+// projected gradient never visits the host between the two forwards and the update.
+//
+// Replaces the reference's per-tensor torch.normal + three elementwise passes
+// (large_models/trainer.py:1438-1444), its update (:1603-1608), the per-tensor norms
+// (:581-584) and the apply/reverse projection passes (:405-451).
+#include "common.cuh"
+#include "host_util.h"
+#include "philox.cuh"
+
+namespace dz {
+
+constexpr int ZO_CHUNK = 2048;   // elements; tensor starts are aligned to this
+constexpr int ZO_THREADS = 256;  // x 8 elements = one chunk per block iteration
+
+struct ZoTensor {
+  long long offset;         // first element in the arena
+  long long numel;
+  long long anchor_offset;  // first element in the anchor arena (valid if slot >= 0)
+  int tensor_id;            // RNG stream id, stable under any sharding
+  int slot;                 // DiZO constraint index, or -1
+  long long elem_base;      // index of this piece's first element inside the full tensor
+  // Column-sharded pieces of a 2-D tensor (tensor parallel): the piece holds `local_cols`
+  // of the `full_cols` columns of every row, starting at column `col0` (all multiples of
+  // 8).  local_cols == 0 means the piece is contiguous inside the full tensor.
+  long long local_cols, full_cols, col0;
+};
+
+__device__ __forceinline__ uint32_t zo_group(const ZoTensor& t, long long e0) {
+  long long ge = t.elem_base + e0;
+  if (t.local_cols) {
+    long long r = e0 / t.local_cols;
+    ge = t.elem_base + r * t.full_cols + t.col0 + (e0 - r * t.local_cols);
+  }
+  return static_cast<uint32_t>(ge >> 3);
+}
+
+struct ZoSweepArgs {
+  const __nv_bfloat16* src;     // arena
+  __nv_bfloat16* dst;           // arena (in place) or staging laid out like the arena range
+  long long dst_shift;          // dst element index = arena element index - dst_shift
+  const __nv_bfloat16* anchor;  // anchor arena (theta_0 of the slotted tensors) or null
+  const ZoTensor* table;
+  int t_begin, t_end;           // tensors of the range
+  long long chunk_begin, chunk_end;
+  unsigned long long seed1, seed2;
+  float c1, c2;                 // host coefficients
+  const float* c1_ptr;          // if set: c1 = c1 * *c1_ptr
+  const float* c2_ptr;
+  const float* alpha;           // [slots] blend ratios
+  float* chunk_sq;              // [chunks of the arena] partial sums (indexed by absolute chunk)
+  unsigned long long sr_seed;   // stochastic rounding stream
+};
+
+__device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, long long pos) {
+  // last tensor in [lo, hi) whose offset <= pos
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (tab[mid].offset <= pos) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+template <bool Z2, bool BLEND, bool NORM, bool SR>
+__global__ void __launch_bounds__(ZO_THREADS)
+zo_sweep_kernel(const ZoSweepArgs a) {
+  __shared__ float s_red[ZO_THREADS / 32];
+  float c1 = a.c1, c2 = a.c2;
+  if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
+  if (Z2 && a.c2_ptr) c2 *= __ldg(a.c2_ptr);
+
+  int cur = -1;
+  for (long long chunk = a.chunk_begin + blockIdx.x; chunk < a.chunk_end; chunk += gridDim.x) {
+    const long long cpos = chunk * ZO_CHUNK;
+    if (cur < 0 || cpos >= a.table[cur].offset + a.table[cur].numel ||
+        (cur + 1 < a.t_end && cpos >= a.table[cur + 1].offset))
+      cur = find_tensor(a.table, a.t_begin, a.t_end, cpos);
+    const ZoTensor t = a.table[cur];
+    const long long e0 = cpos - t.offset + threadIdx.x * 8;  // element inside this piece
+    float sq = 0.f;
+    if (e0 < t.numel) {
+      const long long pos = cpos + threadIdx.x * 8;
+      uint4 raw = *reinterpret_cast<const uint4*>(a.src + pos);
+      float v[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
+                    bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
+      float an[8];
+      const bool slotted = (BLEND || NORM) && t.slot >= 0;
+      if (slotted) {
+        uint4 ar = *reinterpret_cast<const uint4*>(a.anchor + t.anchor_offset + e0);
+        an[0] = bf16_lo(ar.x); an[1] = bf16_hi(ar.x); an[2] = bf16_lo(ar.y); an[3] = bf16_hi(ar.y);
+        an[4] = bf16_lo(ar.z); an[5] = bf16_hi(ar.z); an[6] = bf16_lo(ar.w); an[7] = bf16_hi(ar.w);
+      }
+      if (BLEND && slotted) {
+        const float al = __ldg(a.alpha + t.slot);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = fmaf(al, v[j] - an[j], an[j]);
+      }
+      const uint32_t grp = zo_group(t, e0);
+      if (c1 != 0.f) {
+        float z[8];
+        gauss8(a.seed1, t.tensor_id, grp, 0u, z);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = fmaf(c1, z[j], v[j]);
+      }
+      if (Z2) {
+        float z[8];
+        gauss8(a.seed2, t.tensor_id, grp, 0u, z);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = fmaf(c2, z[j], v[j]);
+      }
+      uint32_t o[4];
+      if (SR) {
+        // stochastic rounding: add 16 random bits below the bf16 mantissa, truncate
+        Philox4 rb = philox4x32<10>(grp, t.tensor_id, 1u, 0u, static_cast<uint32_t>(a.sr_seed),
+                                    static_cast<uint32_t>(a.sr_seed >> 32));
+        uint32_t rw[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t lo = __float_as_uint(v[2 * j]) + (rw[j] & 0xffffu);
+          uint32_t hi = __float_as_uint(v[2 * j + 1]) + (rw[j] >> 16);
+          o[j] = (lo >> 16) | (hi & 0xffff0000u);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+      }
+      if (e0 + 8 > t.numel) {
+        // ragged tail of a tensor: keep the padding elements as they were
+        const uint32_t rawv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (e0 + j >= t.numel) {
+            uint32_t keep = (j & 1) ? (rawv[j >> 1] & 0xffff0000u) : (rawv[j >> 1] & 0xffffu);
+            o[j >> 1] = (j & 1) ? ((o[j >> 1] & 0xffffu) | keep) : ((o[j >> 1] & 0xffff0000u) | keep);
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(a.dst + (pos - a.dst_shift)) = make_uint4(o[0], o[1], o[2], o[3]);
+      if (NORM && slotted) {
+        // norm of what was stored (the bf16 values), so it equals a later re-read
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (e0 + j < t.numel) {
+            float w = (j & 1) ? bf16_hi(o[j >> 1]) : bf16_lo(o[j >> 1]);
+            float d = w - an[j];
+            sq = fmaf(d, d, sq);
+          }
+        }
+      }
+    }
+    if (NORM) {
+      // fixed-order block reduction -> one partial per chunk (deterministic)
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = sq;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < ZO_THREADS / 32; ++w) tot += s_red[w];
+        a.chunk_sq[chunk] = tot;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Sum the per-chunk partials of each slotted tensor in fixed order: sq[slot] = sum.
+__global__ void zo_reduce_chunks_kernel(const ZoTensor* table, int num_tensors,
+                                        const float* chunk_sq, float* sq_out) {
+  __shared__ float s_red[256];
+  const int ti = blockIdx.x;
+  if (ti >= num_tensors) return;
+  const ZoTensor t = table[ti];
+  if (t.slot < 0) return;
+  const long long c0 = t.offset / ZO_CHUNK;
+  const long long nchunks = (t.numel + ZO_CHUNK - 1) / ZO_CHUNK;
+  float acc = 0.f;
+  for (long long c = threadIdx.x; c < nchunks; c += blockDim.x) acc += chunk_sq[c0 + c];
+  s_red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) s_red[threadIdx.x] += s_red[threadIdx.x + s];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) sq_out[t.slot] = s_red[0];  // one piece per slot per rank
+}
+
+// gamma search bookkeeping on the device (one thread per constraint).
+//  mode 0 (init):    ts = sqrt(sq); gamma = ts (if reinit);
+//  mode 1 (perturb): z = clip(N(0,1), +-(tau/eps) ts); gamma += delta*eps*z
+//  mode 2 (step):    g = (*loss1 - *loss2)/(2 eps); gamma = clip(gamma - step*ts*g*z, (1-tau)ts, (1+tau)ts)
+//  every mode then writes alpha = gamma / (ts + 1e-8).
+// Matches large_models/trainer.py:545-562, :581-612, :453-465.
+__global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, float* gamma,
+                                  float* zbuf, float* alpha, unsigned long long seed, int iter,
+                                  float delta, float tau, float eps, float step_size,
+                                  const float* loss1, const float* loss2, int reinit) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float t;
+  if (mode == 0) {
+    t = sqrtf(sq[i]);
+    ts[i] = t;
+    if (reinit) gamma[i] = t;
+  } else {
+    t = ts[i];
+  }
+  float g = gamma[i];
+  if (mode == 1) {
+    float z;
+    if (delta == 1.0f && iter >= 0) {
+      Philox4 p = philox4x32<10>(static_cast<uint32_t>(i), static_cast<uint32_t>(iter), 2u, 0u,
+                                 static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+      float z0, z1;
+      gauss_pair(p.x, z0, z1);
+      float lim = (tau / eps) * t;
+      z = fminf(fmaxf(z0, -lim), lim);
+      zbuf[i] = z;
+    } else {
+      z = zbuf[i];
+    }
+    g += delta * z * eps;
+  } else if (mode == 2) {
+    float grad = (loss1[0] - loss2[0]) / (2.f * eps);
+    g = g - step_size * t * grad * zbuf[i];
+    g = fminf(fmaxf(g, (1.f - tau) * t), (1.f + tau) * t);
+  }
+  gamma[i] = g;
+  alpha[i] = g / (t + 1e-8f);
+}
+
+// out = (a - b) * scale, all device scalars: the projected gradient (L+ - L-)/(2 eps).
+__global__ void scalar_diff_kernel(const float* a, const float* b, float scale, float* out) {
+  out[0] = (a[0] - b[0]) * scale;
+}
+
+template <bool Z2, bool BLEND, bool NORM, bool SR>
+static int launch_sweep(const ZoSweepArgs& a, cudaStream_t stream) {
+  long long chunks = a.chunk_end - a.chunk_begin;
+  if (chunks <= 0) return DZ_OK;
+  long long max_grid = (long long)sm_count() * 8;
+  int grid = (int)(chunks < max_grid ? chunks : max_grid);
+  zo_sweep_kernel<Z2, BLEND, NORM, SR><<<grid, ZO_THREADS, 0, stream>>>(a);
+  return cuda_rc(cudaGetLastError());
+}
+
+}  // namespace dz
+
+using namespace dz;
+
+extern "C" int dz_zo_chunk() { return ZO_CHUNK; }
+extern "C" int dz_zo_tensor_struct_bytes() { return (int)sizeof(ZoTensor); }
+
+// One sweep over arena chunks [chunk_begin, chunk_end) (tensors [t_begin, t_end) of the
+// table).  flags: bit0 second z term, bit1 blend with anchor, bit2 emit norm partials,
+// bit3 stochastic rounding.
+extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, const void* anchor,
+                           const void* table, int t_begin, int t_end, long long chunk_begin,
+                           long long chunk_end, unsigned long long seed1, float c1,
+                           const float* c1_ptr, unsigned long long seed2, float c2,
+                           const float* c2_ptr, const float* alpha, float* chunk_sq,
+                           unsigned long long sr_seed, int flags, cudaStream_t stream) {
+  if (!src || !dst || !table || t_end <= t_begin) return DZ_ERR_ARG;
+  const bool z2 = flags & 1, blend = flags & 2, norm = flags & 4, sr = flags & 8;
+  if ((blend || norm) && !anchor) return DZ_ERR_ARG;
+  if (blend && !alpha) return DZ_ERR_ARG;
+  if (norm && !chunk_sq) return DZ_ERR_ARG;
+  ZoSweepArgs a{};
+  a.src = (const __nv_bfloat16*)src; a.dst = (__nv_bfloat16*)dst; a.dst_shift = dst_shift;
+  a.anchor = (const __nv_bfloat16*)anchor; a.table = (const ZoTensor*)table;
+  a.t_begin = t_begin; a.t_end = t_end; a.chunk_begin = chunk_begin; a.chunk_end = chunk_end;
+  a.seed1 = seed1; a.seed2 = seed2; a.c1 = c1; a.c2 = c2; a.c1_ptr = c1_ptr; a.c2_ptr = c2_ptr;
+  a.alpha = alpha; a.chunk_sq = chunk_sq; a.sr_seed = sr_seed;
+  int key = (z2 ? 1 : 0) | (blend ? 2 : 0) | (norm ? 4 : 0) | (sr ? 8 : 0);
+  switch (key) {
+#define DZ_CASE(K, A, B, C, D) case K: return launch_sweep<A, B, C, D>(a, stream);
+    DZ_CASE(0, false, false, false, false) DZ_CASE(1, true, false, false, false)
+    DZ_CASE(2, false, true, false, false)  DZ_CASE(3, true, true, false, false)
+    DZ_CASE(4, false, false, true, false)  DZ_CASE(5, true, false, true, false)
+    DZ_CASE(6, false, true, true, false)   DZ_CASE(7, true, true, true, false)
+    DZ_CASE(8, false, false, false, true)  DZ_CASE(9, true, false, false, true)
+    DZ_CASE(10, false, true, false, true)  DZ_CASE(11, true, true, false, true)
+    DZ_CASE(12, false, false, true, true)  DZ_CASE(13, true, false, true, true)
+    DZ_CASE(14, false, true, true, true)   DZ_CASE(15, true, true, true, true)
+#undef DZ_CASE
+  }
+  return DZ_ERR_ARG;
+}
+
+extern "C" int dz_zo_reduce_chunks(const void* table, int num_tensors, const float* chunk_sq,
+                                   float* sq_out, cudaStream_t stream) {
+  if (!table || !chunk_sq || !sq_out || num_tensors <= 0) return DZ_ERR_ARG;
+  zo_reduce_chunks_kernel<<<num_tensors, 256, 0, stream>>>((const ZoTensor*)table, num_tensors,
+                                                           chunk_sq, sq_out);
+  return cuda_rc(cudaGetLastError());
+}
+
+extern "C" int dz_gamma_step(int n, int mode, const float* sq, float* ts, float* gamma, float* zbuf,
+                             float* alpha, unsigned long long seed, int iter, float delta, float tau,
+                             float eps, float step_size, const float* loss1, const float* loss2,
+                             int reinit, cudaStream_t stream) {
+  if (n <= 0 || !ts || !gamma || !zbuf || !alpha) return DZ_ERR_ARG;
+  gamma_step_kernel<<<(n + 127) / 128, 128, 0, stream>>>(n, mode, sq, ts, gamma, zbuf, alpha, seed,
+                                                         iter, delta, tau, eps, step_size, loss1,
+                                                         loss2, reinit);
+  return cuda_rc(cudaGetLastError());
+}
+
+extern "C" int dz_scalar_diff(const float* a, const float* b, float scale, float* out,
+                              cudaStream_t stream) {
+  if (!a || !b || !out) return DZ_ERR_ARG;
+  scalar_diff_kernel<<<1, 1, 0, stream>>>(a, b, scale, out);
+  return cuda_rc(cudaGetLastError());
+}
+
+// z itself (fp32), for tests and for the CPU oracle that consumes the framework's stream.
+__global__ void zo_fill_z_kernel(float* out, long long numel, long long elem_base,
+                                 unsigned long long seed, int tensor_id) {
+  long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long e0 = g * 8;
+  if (e0 >= numel) return;
+  float z[8];
+  gauss8(seed, tensor_id, (uint32_t)((elem_base + e0) >> 3), 0u, z);
+  for (int j = 0; j < 8 && e0 + j < numel; ++j) out[e0 + j] = z[j];
+}
+extern "C" int dz_zo_fill_z(float* out, long long numel, long long elem_base,
+                            unsigned long long seed, int tensor_id, cudaStream_t stream) {
+  if (!out || numel <= 0 || (elem_base & 7)) return DZ_ERR_ARG;
+  long long groups = (numel + 7) / 8;
+  zo_fill_z_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(out, numel, elem_base, seed,
+                                                                        tensor_id);
+  return cuda_rc(cudaGetLastError());
+}

@@ -1,0 +1,88 @@
+"""NumPy statement of the framework's Gaussian stream (the oracle for ``csrc/philox.cuh``).
+
+``z(seed, tensor_id, e)`` is a pure function of the seed, the tensor's stream id and the
+element index ``e`` inside the *full* tensor:
+
+    words = Philox4x32-10(counter=(e >> 3, tensor_id, stream, 0), key=(seed_lo, seed_hi))
+    w     = words[(e & 7) >> 1];  u1 = w & 0xffff;  u2 = w >> 16
+    r     = sqrt(-2 ln((u1 + .5) / 65536));  phi = 2 pi (u2 + .5) / 65536 - pi
+    z     = r cos(phi) for even e, r sin(phi) for odd e
+
+The reference instead calls ``torch.manual_seed(seed)`` and ``torch.normal`` per tensor
+(large_models/trainer.py:1438-1444); bit-matching that generator is not a goal.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+M0 = np.uint64(0xD2511F53)
+M1 = np.uint64(0xCD9E8D57)
+W0 = np.uint32(0x9E3779B9)
+W1 = np.uint32(0xBB67AE85)
+_MASK = np.uint64(0xFFFFFFFF)
+
+
+def philox4x32(c0, c1, c2, c3, k0, k1, rounds: int = 10):
+    """Vectorised Philox4x32; all inputs broadcastable uint32 arrays."""
+    c0 = np.asarray(c0, dtype=np.uint32)
+    shape = np.broadcast(c0, c1, c2, c3).shape
+    c0 = np.broadcast_to(c0, shape).astype(np.uint32)
+    c1 = np.broadcast_to(np.asarray(c1, dtype=np.uint32), shape).astype(np.uint32)
+    c2 = np.broadcast_to(np.asarray(c2, dtype=np.uint32), shape).astype(np.uint32)
+    c3 = np.broadcast_to(np.asarray(c3, dtype=np.uint32), shape).astype(np.uint32)
+    k0 = np.uint32(k0)
+    k1 = np.uint32(k1)
+    with np.errstate(over="ignore"):
+        for _ in range(rounds):
+            p0 = M0 * c0.astype(np.uint64)
+            p1 = M1 * c2.astype(np.uint64)
+            hi0 = (p0 >> np.uint64(32)).astype(np.uint32)
+            lo0 = (p0 & _MASK).astype(np.uint32)
+            hi1 = (p1 >> np.uint64(32)).astype(np.uint32)
+            lo1 = (p1 & _MASK).astype(np.uint32)
+            n0 = hi1 ^ c1 ^ k0
+            n2 = hi0 ^ c3 ^ k1
+            c0, c1, c2, c3 = n0, lo1, n2, lo0
+            k0 = np.uint32((int(k0) + int(W0)) & 0xFFFFFFFF)
+            k1 = np.uint32((int(k1) + int(W1)) & 0xFFFFFFFF)
+    return c0, c1, c2, c3
+
+
+def gauss_words(words: np.ndarray) -> np.ndarray:
+    """[..., 4] uint32 -> [..., 8] float32 normals (pair per word)."""
+    w = words.astype(np.uint32)
+    u1 = ((w & np.uint32(0xFFFF)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 65536.0)
+    u2 = (w >> np.uint32(16)).astype(np.float32) + np.float32(0.5)
+    r = np.sqrt(np.float32(-1.3862943611198906) * np.log2(u1)).astype(np.float32)
+    phi = u2 * np.float32(6.283185307179586 / 65536.0) - np.float32(3.141592653589793)
+    out = np.empty(w.shape[:-1] + (8,), dtype=np.float32)
+    out[..., 0::2] = r * np.cos(phi)
+    out[..., 1::2] = r * np.sin(phi)
+    return out
+
+
+def gaussian(seed: int, tensor_id: int, numel: int, elem_base: int = 0, stream: int = 0) -> np.ndarray:
+    """z for elements [elem_base, elem_base + numel) of tensor ``tensor_id`` (fp32)."""
+    assert elem_base % 8 == 0
+    g0 = elem_base >> 3
+    ngroups = (numel + 7) >> 3
+    grp = (np.arange(g0, g0 + ngroups, dtype=np.uint64) & _MASK).astype(np.uint32)
+    c = philox4x32(grp, np.uint32(tensor_id), np.uint32(stream), np.uint32(0),
+                   seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    words = np.stack(c, axis=-1)
+    return gauss_words(words).reshape(-1)[:numel]
+
+
+def gaussian_cols(seed: int, tensor_id: int, rows: int, local_cols: int, full_cols: int,
+                  col0: int, elem_base: int = 0) -> np.ndarray:
+    """z for a column slice [col0, col0+local_cols) of a [rows, full_cols] tensor."""
+    full = gaussian(seed, tensor_id, rows * full_cols, elem_base).reshape(rows, full_cols)
+    return np.ascontiguousarray(full[:, col0:col0 + local_cols]).reshape(-1)
+
+
+def scalar_gaussian(seed: int, index: int, it: int) -> float:
+    """The gamma-search draw for constraint ``index`` at search iteration ``it``."""
+    c = philox4x32(np.uint32(index), np.uint32(it), np.uint32(2), np.uint32(0),
+                   seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    words = np.stack([np.atleast_1d(x) for x in c], axis=-1)
+    return float(gauss_words(words)[0, 0])

@@ -1,0 +1,593 @@
+"""OPT decoder over flat parameter arenas, forward-only, with in-flight weight transforms.
+
+The graph is the Hugging Face OPT decoder (same parameter names, shapes and numerics
+conventions as ``OPTForCausalLM``; the reference carries a copy in
+large_models/ht_opt.py:485-1005): token + learned-position embedding (offset 2), pre- or
+post-LayerNorm blocks of {QKV, causal attention, out_proj, fc1, activation, fc2}, final
+LayerNorm, tied LM head.  What differs is how it is laid out and executed:
+
+* every parameter lives in one of two flat arenas (``arena``: the tensors ZO optimises,
+  ``frozen``: the rest), grouped per layer so a layer is one contiguous range;
+* q/k/v weights and biases sit back to back and are consumed as one fused [3d, d] GEMM;
+* a forward can be run under a :class:`Transform` (``theta + c*z(seed)`` for the two SPSA
+  evaluations, ``theta_0 + alpha*(theta - theta_0)`` for the DiZO gamma search): each layer's
+  range is swept into a staging buffer on a side stream one layer ahead of the GEMMs that
+  consume it, so theta itself is never rewritten for a forward;
+* LoRA is merged into the staged q/v weights, prefix rows go straight into the attention
+  kernel, and the LM head only sees the rows that predict option tokens.
+
+All math goes through :mod:`dizo_b200.ops`, which runs the sm_100a kernels for CUDA tensors
+and PyTorch statements of the same ops for CPU tensors (fp32 oracle).
+"""
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field
+from types import SimpleNamespace
+from typing import Callable, Iterable
+
+import torch
+
+from ..ops import attention as attn_ops
+from ..ops import gemm, loss as loss_ops, norm, peft as peft_ops
+from ..ops.zo import CHUNK, ParamArena, Piece
+
+
+@dataclass
+class OPTConfig:
+    vocab_size: int = 50272
+    hidden_size: int = 768
+    num_hidden_layers: int = 12
+    ffn_dim: int = 3072
+    num_attention_heads: int = 12
+    max_position_embeddings: int = 2048
+    word_embed_proj_dim: int | None = None
+    do_layer_norm_before: bool = True
+    activation_function: str = "relu"
+    pad_token_id: int = 1
+    bos_token_id: int = 2
+    eos_token_id: int = 2
+    tie_word_embeddings: bool = True
+    layer_norm_eps: float = 1e-5
+    model_type: str = "opt"
+
+    def __post_init__(self):
+        if self.word_embed_proj_dim is None:
+            self.word_embed_proj_dim = self.hidden_size
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @classmethod
+    def from_hf(cls, hf) -> "OPTConfig":
+        d = hf if isinstance(hf, dict) else hf.to_dict()
+        keys = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in d.items() if k in keys})
+
+    def to_hf_dict(self) -> dict:
+        d = asdict(self)
+        d.update(architectures=["OPTForCausalLM"], enable_bias=True,
+                 layer_norm_elementwise_affine=True, _remove_final_layer_norm=False,
+                 dropout=0.0, attention_dropout=0.0, activation_dropout=0.0, layerdrop=0.0,
+                 init_std=0.02, use_cache=True, prefix="</s>")
+        return d
+
+
+def _cfg(d, L, h, f, **kw):
+    return dict(hidden_size=d, num_hidden_layers=L, num_attention_heads=h, ffn_dim=f, **kw)
+
+
+PRESETS: dict[str, dict] = {
+    "opt-tiny": _cfg(64, 2, 4, 128, vocab_size=512, max_position_embeddings=128),
+    "opt-125m": _cfg(768, 12, 12, 3072),
+    "opt-350m": _cfg(1024, 24, 16, 4096, word_embed_proj_dim=512, do_layer_norm_before=False),
+    "opt-1.3b": _cfg(2048, 24, 32, 8192),
+    "opt-2.7b": _cfg(2560, 32, 32, 10240),
+    "opt-6.7b": _cfg(4096, 32, 32, 16384),
+    "opt-13b": _cfg(5120, 40, 40, 20480),
+    "opt-30b": _cfg(7168, 48, 56, 28672),
+    "opt-66b": _cfg(9216, 64, 72, 36864),
+}
+
+
+def preset(name: str, **overrides) -> OPTConfig:
+    key = name.lower().split("/")[-1]
+    if key not in PRESETS:
+        raise KeyError(f"unknown OPT preset {name!r}; known: {sorted(PRESETS)}")
+    kw = dict(PRESETS[key])
+    kw.update(overrides)
+    return OPTConfig(**kw)
+
+
+# ---------------------------------------------------------------------------- names
+_P = "model.decoder."
+
+
+def layer_prefix(i: int) -> str:
+    return f"{_P}layers.{i}."
+
+
+def base_param_specs(cfg: OPTConfig) -> list[tuple[str, tuple, int]]:
+    """(name, shape, group) of every base parameter in Hugging Face ``named_parameters`` order."""
+    d, dp, F, V = cfg.hidden_size, cfg.word_embed_proj_dim, cfg.ffn_dim, cfg.vocab_size
+    specs: list[tuple[str, tuple, int]] = [
+        (_P + "embed_tokens.weight", (V, dp), -1),
+        (_P + "embed_positions.weight", (cfg.max_position_embeddings + 2, d), -1),
+    ]
+    if dp != d:
+        specs += [(_P + "project_out.weight", (dp, d), -1), (_P + "project_in.weight", (d, dp), -1)]
+    if cfg.do_layer_norm_before:
+        specs += [(_P + "final_layer_norm.weight", (d,), -1), (_P + "final_layer_norm.bias", (d,), -1)]
+    for i in range(cfg.num_hidden_layers):
+        lp = layer_prefix(i)
+        for proj in ("k_proj", "v_proj", "q_proj", "out_proj"):
+            specs += [(f"{lp}self_attn.{proj}.weight", (d, d), i), (f"{lp}self_attn.{proj}.bias", (d,), i)]
+        specs += [(lp + "self_attn_layer_norm.weight", (d,), i), (lp + "self_attn_layer_norm.bias", (d,), i),
+                  (lp + "fc1.weight", (F, d), i), (lp + "fc1.bias", (F,), i),
+                  (lp + "fc2.weight", (d, F), i), (lp + "fc2.bias", (d,), i),
+                  (lp + "final_layer_norm.weight", (d,), i), (lp + "final_layer_norm.bias", (d,), i)]
+    return specs
+
+
+def adapter_param_specs(cfg: OPTConfig, lora_r: int, num_prefix: int) -> list[tuple[str, tuple, int]]:
+    d = cfg.hidden_size
+    specs = []
+    for i in range(cfg.num_hidden_layers):
+        lp = layer_prefix(i)
+        if lora_r:
+            for proj in ("q_proj", "v_proj"):
+                specs += [(f"{lp}self_attn.{proj}.lora_A", (lora_r, d), i),
+                          (f"{lp}self_attn.{proj}.lora_B", (d, lora_r), i)]
+        if num_prefix:
+            specs += [(lp + "self_attn.prefix_keys", (num_prefix, d), i),
+                      (lp + "self_attn.prefix_values", (num_prefix, d), i)]
+    return specs
+
+
+# order of a layer's tensors inside an arena: fused operands are adjacent
+_LAYER_ORDER = ["self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                "self_attn.q_proj.bias", "self_attn.k_proj.bias", "self_attn.v_proj.bias",
+                "self_attn.out_proj.weight", "self_attn.out_proj.bias",
+                "self_attn_layer_norm.weight", "self_attn_layer_norm.bias",
+                "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias",
+                "final_layer_norm.weight", "final_layer_norm.bias",
+                "self_attn.q_proj.lora_A", "self_attn.q_proj.lora_B",
+                "self_attn.v_proj.lora_A", "self_attn.v_proj.lora_B",
+                "self_attn.prefix_keys", "self_attn.prefix_values"]
+
+
+def _arena_sort_key(name: str, group: int):
+    if group < 0:
+        return (group, 0, name)
+    suffix = name.split(f"layers.{group}.", 1)[1]
+    return (group, _LAYER_ORDER.index(suffix), name)
+
+
+@dataclass
+class Transform:
+    """How a forward reads the trainable tensors: ``blend(theta) + coef * z(seed)``."""
+    seed: int = 0
+    coef: float = 0.0
+    coef_dev: torch.Tensor | None = None
+    alpha: torch.Tensor | None = None     # DiZO blend ratios per slot (fp32, on the device)
+
+
+@dataclass
+class Batch:
+    """One forward's inputs, already on the model's device.
+
+    ``rows``/``targets`` name the (sequence*L + position) hidden rows that predict option
+    tokens and the tokens they should predict; ``seq_start`` groups rows into sequences,
+    ``ex_start`` groups sequences (candidates) into examples, ``labels`` picks the correct one.
+    With ``cand_ids`` set the loss is the verbalizer shortcut on ``rows`` (one row per example)."""
+    input_ids: torch.Tensor                 # int32 [B, L]
+    pad_left: torch.Tensor | None = None    # int32 [B]
+    positions: torch.Tensor | None = None   # int32 [B, L]
+    rows: torch.Tensor | None = None        # int32 [R]
+    targets: torch.Tensor | None = None     # int32 [R]
+    seq_start: torch.Tensor | None = None   # int32 [S+1]
+    ex_start: torch.Tensor | None = None    # int32 [E+1]
+    labels: torch.Tensor | None = None      # int32 [E]
+    cand_ids: torch.Tensor | None = None    # int32 [C]
+    classification: bool = True
+
+    def to(self, device, non_blocking: bool = True) -> "Batch":
+        kw = {}
+        for k, v in self.__dict__.items():
+            kw[k] = v.to(device, non_blocking=non_blocking) if isinstance(v, torch.Tensor) else v
+        return Batch(**kw)
+
+    def pin(self) -> "Batch":
+        kw = {}
+        for k, v in self.__dict__.items():
+            kw[k] = v.pin_memory() if isinstance(v, torch.Tensor) and not v.is_cuda else v
+        return Batch(**kw)
+
+    def nbytes(self) -> int:
+        return sum(v.numel() * v.element_size() for v in self.__dict__.values()
+                   if isinstance(v, torch.Tensor))
+
+
+class OPTModel:
+    """Forward-only OPT with trainable/frozen arenas.
+
+    ``mode``: ``"full"`` (every tensor except the tied embedding, as the reference's ZO set,
+    large_models/trainer.py:1147-1160), ``"lora"``, ``"prefix"``, ``"lora+prefix"``, or
+    ``"head"`` (LM head only)."""
+
+    def __init__(self, config: OPTConfig, device="cpu", dtype=torch.float32, mode: str = "full",
+                 lora_r: int = 8, lora_alpha: int = 16, num_prefix: int = 5, untie_emb: bool = False,
+                 overlap_transform: bool = True):
+        self.config = config
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.mode = mode
+        self.use_lora = "lora" in mode
+        self.use_prefix = "prefix" in mode
+        self.lora_r = lora_r if self.use_lora else 0
+        self.lora_scaling = (lora_alpha / lora_r) if self.use_lora else 0.0
+        self.num_prefix = num_prefix if self.use_prefix else 0
+        self.untied = untie_emb or mode == "head" or not config.tie_word_embeddings
+        self.overlap_transform = overlap_transform and self.device.type == "cuda"
+
+        base = base_param_specs(config)
+        extra = []
+        if self.untied:
+            extra.append(("lm_head.weight", (config.vocab_size, config.word_embed_proj_dim), -1))
+        adapters = adapter_param_specs(config, self.lora_r, self.num_prefix)
+        # canonical RNG stream ids: independent of mode, sharding and arena order
+        canon = [n for n, _, _ in base] + ["lm_head.weight"] + \
+                [n for n, _, _ in adapter_param_specs(config, 8, 5)]
+        self.tensor_ids = {n: i for i, n in enumerate(canon)}
+        self.all_specs = base + extra + adapters
+        self.hf_order = [n for n, _, _ in self.all_specs]
+        self.trainable_names = self._select_trainable()
+        tset = set(self.trainable_names)
+
+        def mk(specs):
+            ps = [Piece(n, tuple(s), self.tensor_ids[n], g) for n, s, g in specs]
+            ps.sort(key=lambda p: _arena_sort_key(p.name, p.group))
+            return ps
+
+        self.arena = ParamArena(mk([s for s in self.all_specs if s[0] in tset]), self.device, dtype)
+        self.frozen = ParamArena(mk([s for s in self.all_specs if s[0] not in tset]), self.device, dtype)
+        self._where = {p.name: self.arena for p in self.arena.pieces}
+        self._where.update({p.name: self.frozen for p in self.frozen.pieces})
+        self._staging: dict = {}
+        self._side = None
+        self._merge_buf: dict = {}
+        self.kv_capture: list | None = None      # set to [] to record per-layer qkv (generation)
+
+    # ------------------------------------------------------------------ parameter sets
+    def _select_trainable(self) -> list[str]:
+        names = self.hf_order
+        if self.mode == "full":
+            out = [n for n in names if n != _P + "embed_tokens.weight"]
+        elif self.mode == "head":
+            out = ["lm_head.weight"]
+        else:
+            out = [n for n in names if ("lora_" in n and self.use_lora) or ("prefix_" in n and self.use_prefix)]
+        if not out:
+            raise ValueError(f"mode {self.mode!r} selects no trainable tensor")
+        return out
+
+    def named_parameters(self) -> Iterable[tuple[str, torch.Tensor]]:
+        for n in self.hf_order:
+            yield n, self.param(n)
+
+    def param(self, name: str) -> torch.Tensor:
+        return self._where[name].view(name)
+
+    def num_parameters(self, trainable_only: bool = False) -> int:
+        n = self.arena.trainable_numel()
+        return n if trainable_only else n + self.frozen.trainable_numel()
+
+    def dizo_include_names(self) -> list[str]:
+        """Tensors that get a DiZO constraint: each layer's k_proj/v_proj weight under full
+        fine-tuning, the LoRA factors under LoRA, nothing for prefix-only runs
+        (large_models/trainer.py:1147-1160)."""
+        if self.mode == "full":
+            return [n for n in self.hf_order if n in self._where and self._where[n] is self.arena and
+                    ("self_attn.k_proj.weight" in n or "self_attn.v_proj.weight" in n)]
+        return [n for n in self.trainable_names if "lora" in n]
+
+    # ------------------------------------------------------------------ init / state dict
+    @torch.no_grad()
+    def init_random(self, seed: int = 0, std: float = 0.02) -> "OPTModel":
+        """Hugging Face style init: N(0, std) matrices and embeddings, zero biases, unit LN."""
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        for n, shape, _ in self.all_specs:
+            t = self.param(n)
+            if "lora_A" in n:
+                bound = (1.0 / shape[1]) ** 0.5          # kaiming_uniform(a=sqrt(5)) on [r, in]
+                v = (torch.rand(shape, generator=g) * 2 - 1) * bound
+            elif "lora_B" in n:
+                v = torch.zeros(shape)
+            elif "prefix_" in n:
+                v = torch.randn(shape, generator=g)
+            elif "layer_norm.weight" in n:
+                v = torch.ones(shape)
+            elif n.endswith(".bias"):
+                v = torch.zeros(shape)
+            else:
+                v = torch.randn(shape, generator=g) * std
+                if n == _P + "embed_tokens.weight" or n == _P + "embed_positions.weight":
+                    if n == _P + "embed_tokens.weight":
+                        v[self.config.pad_token_id].zero_()
+            t.copy_(v.to(self.dtype))
+        if self.untied and "lm_head.weight" in self._where:
+            self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
+        return self
+
+    @torch.no_grad()
+    def init_random_fast(self, seed: int = 0, std: float = 0.02) -> "OPTModel":
+        """Same distributions as :meth:`init_random`, generated on the device (large models)."""
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        for n, shape, _ in self.all_specs:
+            t = self.param(n)
+            if "lora_B" in n or n.endswith(".bias"):
+                t.zero_()
+            elif "layer_norm.weight" in n:
+                t.fill_(1.0)
+            elif "lora_A" in n:
+                t.copy_(((torch.rand(shape, generator=g, device=self.device) * 2 - 1) *
+                         (1.0 / shape[1]) ** 0.5).to(self.dtype))
+            elif "prefix_" in n:
+                t.copy_(torch.randn(shape, generator=g, device=self.device).to(self.dtype))
+            else:
+                # in blocks, so a 50272 x 5120 fp32 temporary never exists for bigger tables
+                flat = t.view(-1)
+                step = 1 << 26
+                for s in range(0, flat.numel(), step):
+                    e = min(s + step, flat.numel())
+                    flat[s:e].copy_((torch.randn(e - s, generator=g, device=self.device) * std).to(self.dtype))
+        if self.untied and "lm_head.weight" in self._where:
+            self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
+        return self
+
+    def state_dict(self) -> dict[str, torch.Tensor]:
+        """Hugging Face OPT names (plus ``lora_A/B`` and ``prefix_keys/values``)."""
+        sd = {n: self.param(n).detach().clone() for n in self.hf_order}
+        if not self.untied:
+            sd["lm_head.weight"] = sd[_P + "embed_tokens.weight"]
+        return sd
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
+        missing = []
+        for n in self.hf_order:
+            src = sd.get(n)
+            if src is None and n.startswith("model."):
+                src = sd.get(n[len("model."):])          # OPTModel-prefixed checkpoints
+            if src is None:
+                if n == "lm_head.weight" and (_P + "embed_tokens.weight") in sd:
+                    src = sd[_P + "embed_tokens.weight"]
+                elif "lora_" in n or "prefix_" in n:
+                    missing.append(n)
+                    continue
+                else:
+                    missing.append(n)
+                    if strict:
+                        raise KeyError(f"state dict lacks {n}")
+                    continue
+            self.param(n).copy_(src.to(self.dtype))
+        return missing
+
+    # ------------------------------------------------------------------ weight resolution
+    def _staging_for(self, key, numel: int) -> torch.Tensor:
+        buf = self._staging.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(numel, dtype=self.dtype, device=self.device)
+            self._staging[key] = buf
+        return buf
+
+    def _fused(self, tensors: list[torch.Tensor]) -> torch.Tensor:
+        """View adjacent tensors as one (rows stacked) when they are contiguous in memory."""
+        t0 = tensors[0]
+        esz = t0.element_size()
+        ptr = t0.data_ptr()
+        ok = True
+        for t in tensors:
+            if t.data_ptr() != ptr or not t.is_contiguous():
+                ok = False
+                break
+            ptr += t.numel() * esz
+        if not ok:
+            return torch.cat(tensors, dim=0)
+        rows = sum(t.shape[0] for t in tensors)
+        shape = (rows,) + tuple(t0.shape[1:])
+        return torch.as_strided(t0, shape, t0.stride())
+
+    def _resolver(self, group: int, transform: Transform | None, staged: torch.Tensor | None,
+                  shift: int) -> Callable[[str], torch.Tensor]:
+        def get(name: str) -> torch.Tensor:
+            ar = self._where[name]
+            if ar is self.arena and staged is not None:
+                return ar.view(name, base=staged, shift=shift)
+            return ar.view(name)
+        return get
+
+    def _sweep_group(self, group: int, transform: Transform, dst: torch.Tensor) -> int:
+        lo, hi = self.arena.group_range(group)
+        self.arena.sweep(t_begin=lo, t_end=hi, dst=dst, seed1=transform.seed, c1=transform.coef,
+                         c1_dev=transform.coef_dev, alpha=transform.alpha)
+        return self.arena.span(lo, hi)[0]
+
+    def _layer_weights(self, i: int, get: Callable[[str], torch.Tensor]) -> SimpleNamespace:
+        lp = layer_prefix(i)
+        a = lp + "self_attn."
+        w = SimpleNamespace()
+        qw, kw, vw = get(a + "q_proj.weight"), get(a + "k_proj.weight"), get(a + "v_proj.weight")
+        if self.use_lora:
+            d = self.config.hidden_size
+            buf = self._merge_buf.get("qkv")
+            if buf is None:
+                buf = torch.empty((3 * d, d), dtype=self.dtype, device=self.device)
+                self._merge_buf["qkv"] = buf
+            peft_ops.lora_merge(qw, get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"),
+                                self.lora_scaling, out=buf[:d])
+            buf[d:2 * d].copy_(kw)
+            peft_ops.lora_merge(vw, get(a + "v_proj.lora_A"), get(a + "v_proj.lora_B"),
+                                self.lora_scaling, out=buf[2 * d:])
+            w.qkv_w = buf
+        else:
+            w.qkv_w = self._fused([qw, kw, vw])
+        w.qkv_b = self._fused([get(a + "q_proj.bias"), get(a + "k_proj.bias"), get(a + "v_proj.bias")])
+        w.out_w, w.out_b = get(a + "out_proj.weight"), get(a + "out_proj.bias")
+        w.ln1_w, w.ln1_b = get(lp + "self_attn_layer_norm.weight"), get(lp + "self_attn_layer_norm.bias")
+        w.fc1_w, w.fc1_b = get(lp + "fc1.weight"), get(lp + "fc1.bias")
+        w.fc2_w, w.fc2_b = get(lp + "fc2.weight"), get(lp + "fc2.bias")
+        w.ln2_w, w.ln2_b = get(lp + "final_layer_norm.weight"), get(lp + "final_layer_norm.bias")
+        w.prefix_k = get(a + "prefix_keys") if self.use_prefix else None
+        w.prefix_v = get(a + "prefix_values") if self.use_prefix else None
+        return w
+
+    # ------------------------------------------------------------------ forward
+    def _layer_forward(self, h: torch.Tensor, w: SimpleNamespace, batch: Batch) -> torch.Tensor:
+        cfg = self.config
+        B, L, d = h.shape
+        pre = cfg.do_layer_norm_before
+        x = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps) if pre else h
+        qkv = gemm.linear(x, w.qkv_w, w.qkv_b)
+        if self.kv_capture is not None:
+            self.kv_capture.append(qkv)
+        ctx = attn_ops.attention(qkv.view(B, L, 3 * d), cfg.num_attention_heads, batch.pad_left,
+                                 w.prefix_k, w.prefix_v)
+        h = gemm.linear(ctx, w.out_w, w.out_b, residual=h)
+        if not pre:
+            h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
+        x = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps) if pre else h
+        f = gemm.linear(x, w.fc1_w, w.fc1_b, act=cfg.activation_function)
+        h = gemm.linear(f, w.fc2_w, w.fc2_b, residual=h)
+        if not pre:
+            h = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
+        return h
+
+    @torch.no_grad()
+    def hidden_states(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
+        """Decoder output before the final LayerNorm / project_out: [B, L, d]."""
+        cfg = self.config
+        nl = cfg.num_hidden_layers
+        use_t = transform is not None and len(self.arena.pieces) > 0
+        has_group = {g: True for g in self.arena.groups()}
+        overlap = use_t and self.overlap_transform
+        if overlap and self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        # ---- globals
+        g_staged, g_shift = None, 0
+        if use_t and has_group.get(-1):
+            g_staged = self._staging_for("globals", self.arena.group_numel(-1))
+            g_shift = self._sweep_group(-1, transform, g_staged)
+        self._gget = self._resolver(-1, transform, g_staged, g_shift)
+        gget = self._gget
+        positions = batch.positions
+        tok = gget(_P + "embed_tokens.weight")
+        pos = gget(_P + "embed_positions.weight")
+        if cfg.word_embed_proj_dim != cfg.hidden_size:
+            e = norm.embed(batch.input_ids, None, tok, None)
+            e = gemm.linear(e, gget(_P + "project_in.weight"))
+            h = norm.add_rows(e, positions.reshape(-1), pos)
+        else:
+            h = norm.embed(batch.input_ids, positions, tok, pos)
+        # ---- layers, with the transform of layer i+1 running beside the GEMMs of layer i
+        main = torch.cuda.current_stream(self.device) if overlap else None
+        ready = [None, None]
+        free = [None, None]
+        layer_numel = max((self.arena.group_numel(g) for g in self.arena.groups() if g >= 0), default=0)
+
+        def launch_transform(i: int):
+            k = i % 2
+            buf = self._staging_for(("layer", k), layer_numel)
+            if overlap:
+                with torch.cuda.stream(self._side):
+                    if free[k] is not None:
+                        self._side.wait_event(free[k])
+                    shift = self._sweep_group(i, transform, buf)
+                    ev = torch.cuda.Event()
+                    ev.record(self._side)
+                ready[k] = ev
+            else:
+                shift = self._sweep_group(i, transform, buf)
+            return buf, shift
+
+        pending = None
+        if use_t and nl > 0 and has_group.get(0):
+            if overlap:
+                start = torch.cuda.Event()
+                start.record(main)
+                self._side.wait_event(start)
+            pending = launch_transform(0)
+        for i in range(nl):
+            staged, shift = None, 0
+            if use_t and has_group.get(i):
+                staged, shift = pending
+                if overlap:
+                    main.wait_event(ready[i % 2])
+            # queue the next layer's sweep first: it runs beside this layer's GEMMs
+            if use_t and i + 1 < nl and has_group.get(i + 1):
+                pending = launch_transform(i + 1)
+            w = self._layer_weights(i, self._resolver(i, transform, staged, shift))
+            h = self._layer_forward(h, w, batch)
+            if overlap and has_group.get(i):
+                ev = torch.cuda.Event()
+                ev.record(main)
+                free[i % 2] = ev
+        if overlap:
+            main.wait_stream(self._side)
+        return h
+
+    @torch.no_grad()
+    def final_rows(self, h: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """Final LayerNorm (+ project_out) applied to the selected rows of h only."""
+        cfg = self.config
+        d = cfg.hidden_size
+        x = norm.gather_rows(h.reshape(-1, d), rows)
+        gget = self._gget
+        if cfg.do_layer_norm_before:
+            x = norm.layernorm(x, gget(_P + "final_layer_norm.weight"),
+                               gget(_P + "final_layer_norm.bias"), cfg.layer_norm_eps)
+        if cfg.word_embed_proj_dim != d:
+            x = gemm.linear(x, gget(_P + "project_out.weight"))
+        return x
+
+    def lm_head_weight(self) -> torch.Tensor:
+        return self._gget("lm_head.weight") if self.untied else self._gget(_P + "embed_tokens.weight")
+
+    @torch.no_grad()
+    def loss(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
+        """One fp32 loss (1-element tensor on the device) for the batch."""
+        h = self.hidden_states(batch, transform)
+        x = self.final_rows(h, batch.rows)
+        table = self.lm_head_weight()
+        if batch.cand_ids is not None:
+            _, loss = loss_ops.verbalizer_ce(x, table, batch.cand_ids, batch.labels)
+            return loss
+        lp = loss_ops.token_logprobs(x, table, batch.targets)
+        return loss_ops.option_ce(lp, batch.seq_start, batch.ex_start, batch.labels, batch.classification)
+
+    @torch.no_grad()
+    def row_logprobs(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
+        """log p(target) for every (row, target) pair of the batch (evaluation path)."""
+        h = self.hidden_states(batch, transform)
+        x = self.final_rows(h, batch.rows)
+        return loss_ops.token_logprobs(x, self.lm_head_weight(), batch.targets)
+
+    @torch.no_grad()
+    def logits(self, batch: Batch, rows: torch.Tensor | None = None) -> torch.Tensor:
+        """Full-vocabulary fp32 logits for the selected rows (all rows when ``rows`` is None)."""
+        h = self.hidden_states(batch)
+        B, L, _ = h.shape
+        if rows is None:
+            rows = torch.arange(B * L, dtype=torch.int32, device=h.device)
+        x = self.final_rows(h, rows)
+        return gemm.linear(x, self.lm_head_weight(), out_dtype=torch.float32)
+
+
+def make_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None, **kw) -> Batch:
+    """Build a :class:`Batch` from left-padded ids and a 0/1 mask (positions, pad_left derived)."""
+    ids = input_ids.to(torch.int32)
+    if attention_mask is None:
+        attention_mask = torch.ones_like(ids)
+    m = attention_mask.to(torch.int32)
+    pad_left = (m.shape[1] - m.sum(dim=1)).to(torch.int32)
+    return Batch(input_ids=ids, pad_left=pad_left, positions=norm.opt_positions(m), **kw)

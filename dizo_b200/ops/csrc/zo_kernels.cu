@@ -2,9 +2,11 @@
 //
 // All trainable tensors of a model live in one bf16 buffer.  A table describes them:
 // {offset, numel, tensor id (RNG stream), DiZO slot or -1, offset of the anchor copy}.
-// Tensor starts are aligned to ZO_CHUNK (2048) elements, so every 2048-element chunk of
-// the arena belongs to exactly one tensor, and one launch sweeps any contiguous range
-// of the arena (one layer, or the whole model).
+// Tensor starts are aligned to ZO_CHUNK (256) elements, so every 256-element chunk (one
+// warp x 16 bytes per lane) belongs to exactly one tensor, and one launch sweeps any
+// contiguous range of the arena (one layer, or the whole model).  256 divides every OPT
+// hidden size, so q/k/v weights (and biases) packed back to back stay contiguous and can
+// be read as one fused [3d, d] operand.
 //
 // dz_zo_sweep computes, per element of every tensor in the range,
 //     v   = theta                                   (bf16 -> fp32)
@@ -26,8 +28,8 @@
 
 namespace dz {
 
-constexpr int ZO_CHUNK = 2048;   // elements; tensor starts are aligned to this
-constexpr int ZO_THREADS = 256;  // x 8 elements = one chunk per block iteration
+constexpr int ZO_CHUNK = 256;    // elements; tensor starts are aligned to this (one warp pass)
+constexpr int ZO_THREADS = 256;  // 8 warps = 8 consecutive chunks per block iteration
 
 struct ZoTensor {
   long long offset;         // first element in the arena
@@ -40,6 +42,7 @@ struct ZoTensor {
   // of the `full_cols` columns of every row, starting at column `col0` (all multiples of
   // 8).  local_cols == 0 means the piece is contiguous inside the full tensor.
   long long local_cols, full_cols, col0;
+  long long sq_base;        // index of this piece's first chunk in the norm partials, or -1
 };
 
 __device__ __forceinline__ uint32_t zo_group(const ZoTensor& t, long long e0) {
@@ -64,7 +67,7 @@ struct ZoSweepArgs {
   const float* c1_ptr;          // if set: c1 = c1 * *c1_ptr
   const float* c2_ptr;
   const float* alpha;           // [slots] blend ratios
-  float* chunk_sq;              // [chunks of the arena] partial sums (indexed by absolute chunk)
+  float* chunk_sq;              // norm partials: [sq_base + chunk inside the piece]
   unsigned long long sr_seed;   // stochastic rounding stream
 };
 
@@ -80,22 +83,24 @@ __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, 
 template <bool Z2, bool BLEND, bool NORM, bool SR>
 __global__ void __launch_bounds__(ZO_THREADS)
 zo_sweep_kernel(const ZoSweepArgs a) {
-  __shared__ float s_red[ZO_THREADS / 32];
   float c1 = a.c1, c2 = a.c2;
   if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
   if (Z2 && a.c2_ptr) c2 *= __ldg(a.c2_ptr);
 
   int cur = -1;
-  for (long long chunk = a.chunk_begin + blockIdx.x; chunk < a.chunk_end; chunk += gridDim.x) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int WARPS = ZO_THREADS / 32;
+  for (long long chunk = a.chunk_begin + (long long)blockIdx.x * WARPS + warp; chunk < a.chunk_end;
+       chunk += (long long)gridDim.x * WARPS) {
     const long long cpos = chunk * ZO_CHUNK;
     if (cur < 0 || cpos >= a.table[cur].offset + a.table[cur].numel ||
         (cur + 1 < a.t_end && cpos >= a.table[cur + 1].offset))
       cur = find_tensor(a.table, a.t_begin, a.t_end, cpos);
     const ZoTensor t = a.table[cur];
-    const long long e0 = cpos - t.offset + threadIdx.x * 8;  // element inside this piece
+    const long long e0 = cpos - t.offset + lane * 8;  // element inside this piece
     float sq = 0.f;
     if (e0 < t.numel) {
-      const long long pos = cpos + threadIdx.x * 8;
+      const long long pos = cpos + lane * 8;
       uint4 raw = *reinterpret_cast<const uint4*>(a.src + pos);
       float v[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
                     bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
@@ -165,18 +170,10 @@ zo_sweep_kernel(const ZoSweepArgs a) {
       }
     }
     if (NORM) {
-      // fixed-order block reduction -> one partial per chunk (deterministic)
+      // fixed-order warp reduction -> one partial per chunk (deterministic)
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = sq;
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < ZO_THREADS / 32; ++w) tot += s_red[w];
-        a.chunk_sq[chunk] = tot;
-      }
-      __syncthreads();
+      if (lane == 0 && t.sq_base >= 0) a.chunk_sq[t.sq_base + (cpos - t.offset) / ZO_CHUNK] = sq;
     }
   }
 }
@@ -189,7 +186,7 @@ __global__ void zo_reduce_chunks_kernel(const ZoTensor* table, int num_tensors,
   if (ti >= num_tensors) return;
   const ZoTensor t = table[ti];
   if (t.slot < 0) return;
-  const long long c0 = t.offset / ZO_CHUNK;
+  const long long c0 = t.sq_base;
   const long long nchunks = (t.numel + ZO_CHUNK - 1) / ZO_CHUNK;
   float acc = 0.f;
   for (long long c = threadIdx.x; c < nchunks; c += blockDim.x) acc += chunk_sq[c0 + c];
@@ -255,8 +252,9 @@ template <bool Z2, bool BLEND, bool NORM, bool SR>
 static int launch_sweep(const ZoSweepArgs& a, cudaStream_t stream) {
   long long chunks = a.chunk_end - a.chunk_begin;
   if (chunks <= 0) return DZ_OK;
+  long long blocks = (chunks + ZO_THREADS / 32 - 1) / (ZO_THREADS / 32);
   long long max_grid = (long long)sm_count() * 8;
-  int grid = (int)(chunks < max_grid ? chunks : max_grid);
+  int grid = (int)(blocks < max_grid ? blocks : max_grid);
   zo_sweep_kernel<Z2, BLEND, NORM, SR><<<grid, ZO_THREADS, 0, stream>>>(a);
   return cuda_rc(cudaGetLastError());
 }

@@ -23,7 +23,7 @@ import torch
 
 from . import _lib, philox
 
-CHUNK = 2048
+CHUNK = 256
 
 
 @dataclass
@@ -39,6 +39,7 @@ class Piece:
     local_cols: int = 0
     full_cols: int = 0
     col0: int = 0
+    sq_base: int = -1
 
     @property
     def numel(self) -> int:
@@ -108,15 +109,21 @@ class ParamArena:
     def set_dizo(self, names: list[str]) -> None:
         """Give every named piece a constraint slot and snapshot it as the anchor theta_0."""
         off = 0
+        sq = 0
         self.slot_names = []
         for p in self.pieces:
             p.slot = -1
+            p.sq_base = -1
         for n in names:
             p = self.pieces[self.index[n]]
             p.slot = len(self.slot_names)
             p.anchor_offset = off
+            p.sq_base = sq
             off += _round_up(p.numel, 8)
+            sq += _round_up(p.numel, CHUNK) // CHUNK
             self.slot_names.append(n)
+        self._n_sq_chunks = sq
+        self._chunk_sq = None
         self.n_slots = len(self.slot_names)
         self.anchor = torch.zeros(max(off, 8), dtype=self.dtype, device=self.device)
         self.snapshot_anchor()
@@ -138,11 +145,12 @@ class ParamArena:
         if self._table_dev is None:
             dt = np.dtype([("offset", "<i8"), ("numel", "<i8"), ("anchor_offset", "<i8"),
                            ("tensor_id", "<i4"), ("slot", "<i4"), ("elem_base", "<i8"),
-                           ("local_cols", "<i8"), ("full_cols", "<i8"), ("col0", "<i8")])
+                           ("local_cols", "<i8"), ("full_cols", "<i8"), ("col0", "<i8"),
+                           ("sq_base", "<i8")])
             arr = np.zeros(len(self.pieces), dtype=dt)
             for i, p in enumerate(self.pieces):
                 arr[i] = (p.offset, p.numel, p.anchor_offset, p.tensor_id, p.slot, p.elem_base,
-                          p.local_cols, p.full_cols, p.col0)
+                          p.local_cols, p.full_cols, p.col0, p.sq_base)
             if self.device.type == "cuda":
                 assert dt.itemsize == _lib.lib().dz_zo_tensor_struct_bytes()
             raw = torch.from_numpy(arr.view(np.uint8).copy())
@@ -197,7 +205,8 @@ class ParamArena:
         flags = (1 if use_z2 else 0) | (2 if blend else 0) | (4 if norm else 0) | \
                 (8 if stochastic_round_seed is not None else 0)
         if norm and self._chunk_sq is None:
-            self._chunk_sq = torch.zeros(self.total // CHUNK, dtype=torch.float32, device=self.device)
+            self._chunk_sq = torch.zeros(max(self._n_sq_chunks, 1), dtype=torch.float32,
+                                         device=self.device)
         rc = L.dz_zo_sweep(
             _lib.ptr(self.data), _lib.ptr(out), ctypes.c_longlong(shift), _lib.ptr(self.anchor),
             _lib.ptr(self.table()), t_begin, t_end, ctypes.c_longlong(begin // CHUNK),

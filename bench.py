@@ -1,0 +1,330 @@
+"""Headline benchmark: zeroth-order (DiZO) training throughput of OPT-13B in bf16.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference ...                     # the unmodified reference, if installable
+    python bench.py --impl baseline ...                      # stock-PyTorch statement of the reference loop
+
+Metric: ZO training tokens/s = (prompts per rank x sequence length x ranks) / step time.  A
+step is two forward passes (theta + eps z, theta - eps z), the scalar all-reduce of the
+projected gradient under data parallelism, and the parameter update; the DiZO gamma search
+(20 forwards + norms + projection, every 50 steps) is timed in the same run and charged to
+every step as 1/50 of its cost.  Data are synthetic (seeded uniform ids, Bernoulli labels),
+weights are random-init OPT-13B.  All times are CUDA-event times on the launching stream,
+max over ranks.  For N > 1 launch under ``python -m torch.distributed.run``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_PUBLISHED = None  # the reference publishes no tokens/s figure
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
+    ap.add_argument("--model", default="opt-13b")
+    ap.add_argument("--prompts", type=int, default=8, help="prompts per rank")
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--mode", default="full", help="full | lora | prefix | lora+prefix")
+    ap.add_argument("--zo-mode", default="inflight", choices=["inflight", "inplace"])
+    ap.add_argument("--enhanced", default="zo", choices=["none", "zo"])
+    ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--baseline-candidates", type=int, default=2)
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def dist_setup():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except (ValueError, IndexError):
+            return local
+    return local
+
+
+# ------------------------------------------------------------------------------- ours
+def run_ours(a, world, rank, local):
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import DiZOProjector, ZOEngine
+    from dizo_b200.models.opt import OPTModel, preset
+    from dizo_b200.ops import _lib
+
+    dev = torch.device("cuda", local)
+    cfg = preset(a.model)
+    model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=not a.no_overlap)
+    model.init_random_fast(seed=0)
+    engine = ZOEngine(model, eps=1e-3, mode=a.zo_mode)
+    projector = DiZOProjector(model) if a.enhanced == "zo" else None
+    lr0, max_steps = 1e-6, 20000
+    V = cfg.vocab_size
+
+    def host_batch(step):
+        return synthetic_batch(step, a.prompts, a.seq, V, seed=1, rank=rank, pin=True)
+
+    def lr_at(k):
+        return lr0 * (1 - k / (2 * max_steps))
+
+    # ---- device-timed region: inputs already resident
+    n_res = a.warmup + a.steps
+    resident = [host_batch(s).to(dev) for s in range(n_res)]
+    torch.cuda.synchronize()
+    for s in range(a.warmup):
+        engine.step(resident[s], lr_at(s), seed=1000 + s)
+    barrier(world)
+    _lib.check_device_errors()
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    l0 = _lib.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    e0.record()
+    for s in range(a.warmup, a.warmup + a.steps):
+        engine.step(resident[s], lr_at(s), seed=1000 + s)
+    e1.record()
+    barrier(world)
+    launches = _lib.launch_count - l0
+    step_ms = max_over_ranks(e0.elapsed_time(e1) / a.steps, world)
+
+    # ---- the gamma search (every 50 steps in training), timed once
+    search_ms = 0.0
+    if projector is not None:
+        it = iter(range(10 ** 9))
+        nb = lambda: resident[next(it) % n_res]
+        projector.search_zo(nb, seed=7)          # warm
+        barrier(world)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        projector.search_zo(nb, seed=8)
+        s1.record()
+        barrier(world)
+        search_ms = max_over_ranks(s0.elapsed_time(s1), world)
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_device_errors()
+    ms = step_ms + search_ms / 50.0
+    tokens = a.prompts * a.seq * world
+
+    # ---- end to end through the public trainer call: pinned H2D of each step's inputs,
+    #      the step, D2H read of its loss
+    e2e = None
+    if not a.skip_e2e:
+        from dizo_b200.trainer import OurTrainer
+        from dizo_b200.args import OurArguments
+        targs = OurArguments(trainer="zo", learning_rate=lr0, max_steps=max_steps, zo_eps=1e-3,
+                             enhanced=None, zo_mode=a.zo_mode)
+        tr = OurTrainer(model=model, args=targs, engine=engine)
+        hb = [host_batch(10_000 + s) for s in range(a.steps + 2)]
+        for s in range(2):
+            tr.training_step(hb[s])
+        barrier(world)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        last = 0.0
+        for s in range(2, 2 + a.steps):
+            last = tr.training_step(hb[s])        # float: includes the device->host read
+        t1.record()
+        barrier(world)
+        e2e_ms = max_over_ranks(t0.elapsed_time(t1) / a.steps, world) + search_ms / 50.0
+        e2e = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": hb[0].nbytes(), "d2h_bytes_per_step": 4, "last_loss": last}
+
+    nparam = model.arena.trainable_numel()
+    out = {
+        "metric": "zo_train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+        "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded uniform ids, Bernoulli labels); random-init weights",
+        "impl": "ours",
+        "config": {"model": a.model, "global_batch": a.prompts * world, "seq_len": a.seq,
+                   "parallelism": f"dp{world}", "trainable": a.mode, "zo_mode": a.zo_mode,
+                   "forwards_per_step": 2, "enhanced": a.enhanced,
+                   "zo_step_ms": step_ms, "gamma_search_ms": search_ms, "gamma_search_period": 50,
+                   "l2_policy": "per-step working set (parameters) far exceeds L2; no flush needed",
+                   "trainable_params": nparam},
+        "sweep_gbs_note": "see profiles/ for perturb+update GB/s",
+        "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
+    }
+    return out
+
+
+# ------------------------------------------------------------------------------- baseline
+def run_baseline(a, world, rank, local):
+    """Reference algorithm in stock PyTorch (HF model, torch.normal sweeps, full-vocab loss)."""
+    import numpy as np
+    from baseline.mezo_torch import TorchMeZO, build_hf_opt, synthetic_reference_batch
+    from dizo_b200.data.synthetic import DEFAULT_CANDS
+    from dizo_b200.models.opt import preset
+    dev = torch.device("cuda", local)
+    cfg = preset(a.model)
+    model = build_hf_opt(cfg.to_hf_dict(), dev, torch.bfloat16)
+    opt = TorchMeZO(model, eps=1e-3, dizo=(a.enhanced == "zo"))
+    np.random.seed(0)
+    mk = lambda s: synthetic_reference_batch(s, a.prompts, a.seq, cfg.vocab_size, 1, rank,
+                                             DEFAULT_CANDS, dev, a.baseline_candidates)
+    batches = [mk(s) for s in range(a.warmup + a.steps)]
+
+    def step(s):
+        l = opt.step(batches[s], 1e-6)
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(l)
+    for s in range(a.warmup):
+        step(s)
+    barrier(world)
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(a.warmup, a.warmup + a.steps):
+        step(s)
+    e1.record()
+    barrier(world)
+    step_ms = max_over_ranks(e0.elapsed_time(e1) / a.steps, world)
+    search_ms = 0.0
+    if a.enhanced == "zo":
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        opt.dizo_search([batches[i % len(batches)] for i in range(10)])
+        s1.record()
+        barrier(world)
+        search_ms = max_over_ranks(s0.elapsed_time(s1), world)
+    clocks = sampler.stop() if rank == 0 else None
+    ms = step_ms + search_ms / 50.0
+    tokens = a.prompts * a.seq * world
+    return {"metric": "zo_train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "baseline",
+            "config": {"model": a.model, "global_batch": a.prompts * world, "seq_len": a.seq,
+                       "parallelism": f"dp{world}", "candidates_per_prompt": a.baseline_candidates,
+                       "zo_step_ms": step_ms, "gamma_search_ms": search_ms},
+            "clocks": clocks}
+
+
+# ------------------------------------------------------------------------------- reference
+def run_reference(a):
+    """The unmodified reference from baseline/_ref, or the reason it cannot run here."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(ref) or not os.listdir(ref):
+        why = ("reference is not installable: it ships no setup.py/pyproject (pip install of "
+               "/root/reference fails) and its trainer imports symbols removed from transformers 5.x")
+    else:
+        sys.path.insert(0, ref)
+        try:
+            import trainer as _ref_trainer  # noqa: F401  (the reference's flat module layout)
+        except Exception as e:  # pragma: no cover - depends on the box
+            why = f"reference import fails under the installed libraries: {type(e).__name__}: {e}"[:300]
+    if why is None:
+        why = "reference imported but its ZO path pins CUDA_VISIBLE_DEVICES=0 and needs HF hub data"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        return run_reference(a)
+    world, rank, local = dist_setup()
+    out = run_ours(a, world, rank, local) if a.impl == "ours" else run_baseline(a, world, rank, local)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,205 @@
+"""The zeroth-order training step and the DiZO projection, on top of the parameter arena.
+
+``ZOEngine.step`` is the MeZO two-point SPSA estimator + ZO-SGD update of the reference
+(``zo_step``/``zo_update``, large_models/trainer.py:1570-1617):
+
+    seed k shared by every rank;  L+ = loss(theta + eps z_k);  L- = loss(theta - eps z_k)
+    g = (L+ - L-) / (2 eps)        (kept on the device; one scalar all-reduce under DP)
+    theta <- theta - lr * g * z_k  (one sweep; z regenerated, never stored)
+
+Two execution modes with the same mathematics:
+  * ``inflight`` (default): theta is never rewritten for a forward; each layer's perturbed
+    copy is produced on the fly (:class:`dizo_b200.models.opt.Transform`).  One parameter
+    sweep per step writes theta, instead of the reference's four.
+  * ``inplace``: the reference's order (+eps, -2eps, +eps, update) with in-place sweeps.
+
+``DiZOProjector`` is the divergence-driven projection (large_models/trainer.py:378-830):
+every ``interval`` steps it searches one gamma per constrained tensor (10 ZO iterations on
+fresh batches, or first-order steps through the gamma scalars) and projects
+theta <- theta_0 + gamma / ||theta - theta_0|| * (theta - theta_0).  The search forwards read
+``theta_0 + alpha (theta - theta_0)`` in flight, so the reference's apply/reverse passes
+(and their fp16 round-trip error) do not exist here.
+"""
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass
+from typing import Callable, Iterator
+
+import torch
+import torch.distributed as dist
+
+from .models.opt import Batch, OPTModel, Transform
+from .ops.zo import GammaState, scalar_diff
+
+logger = logging.getLogger(__name__)
+
+
+def _dist_on(group=None) -> bool:
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+
+class ZOEngine:
+    def __init__(self, model: OPTModel, eps: float = 1e-3, mode: str = "inflight",
+                 dp_group=None, stochastic_rounding: bool = False):
+        assert mode in ("inflight", "inplace")
+        self.model = model
+        self.eps = eps
+        self.mode = mode
+        self.dp_group = dp_group
+        self.stochastic_rounding = stochastic_rounding
+        dev = model.device
+        f = dict(dtype=torch.float32, device=dev)
+        self.loss1 = torch.zeros(1, **f)
+        self.loss2 = torch.zeros(1, **f)
+        self.projected_grad = torch.zeros(1, **f)   # g of the last step (device)
+        self.launches = 0
+
+    # -- pieces of a step, exposed because the trainer API names them ------------------
+    def perturb(self, seed: int, scaling: float) -> None:
+        """In-place theta += scaling * eps * z(seed) (``zo_perturb_parameters``)."""
+        self.model.arena.sweep(seed1=seed, c1=scaling * self.eps)
+
+    def forward(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
+        return self.model.loss(batch, transform)
+
+    def reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
+        """Mean over the data-parallel group of a 1-element device tensor (NCCL / gloo)."""
+        if _dist_on(self.dp_group):
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.dp_group)
+            t.div_(dist.get_world_size(self.dp_group))
+        return t
+
+    def update(self, seed: int, lr: float, sq_out: torch.Tensor | None = None) -> None:
+        """theta -= lr * g * z(seed) (``zo_update``); optionally also emit the DiZO norms of
+        the updated tensors from the same pass."""
+        sr = (seed * 0x9E3779B97F4A7C15 + 1) & (2 ** 64 - 1) if self.stochastic_rounding else None
+        self.model.arena.sweep(seed1=seed, c1=-lr, c1_dev=self.projected_grad, sq_out=sq_out,
+                               stochastic_round_seed=sr)
+
+    def step(self, batch: Batch, lr: float, seed: int, sq_out: torch.Tensor | None = None,
+             loss_fn: Callable[[Batch, Transform | None], torch.Tensor] | None = None) -> torch.Tensor:
+        """One ZO-SGD step; returns L+ (1-element device tensor, like the reference's loss1)."""
+        fwd = loss_fn or self.forward
+        eps = self.eps
+        if self.mode == "inflight":
+            l1 = fwd(batch, Transform(seed=seed, coef=eps))
+            l2 = fwd(batch, Transform(seed=seed, coef=-eps))
+        else:
+            self.perturb(seed, 1.0)
+            l1 = fwd(batch, None)
+            self.perturb(seed, -2.0)
+            l2 = fwd(batch, None)
+            self.perturb(seed, 1.0)
+        self.loss1.copy_(l1.reshape(1))
+        self.loss2.copy_(l2.reshape(1))
+        scalar_diff(self.loss1, self.loss2, 1.0 / (2.0 * eps), self.projected_grad)
+        self.reduce_scalar(self.projected_grad)
+        self.update(seed, lr, sq_out)
+        return self.loss1
+
+
+class DiZOProjector:
+    """gamma search + projection for the constrained tensors of ``model.arena``."""
+
+    def __init__(self, model: OPTModel, include: list[str] | None = None, tau: float = 0.2,
+                 zo_eps: float = 0.1, step_size: float = 2.0, max_iters: int = 10,
+                 proj_lr: float = 0.1, l1: float = 1e-3, norm_mode: str = "l2norm", dp_group=None):
+        if "l2" not in norm_mode:
+            raise NotImplementedError("only the l2 norm mode is reachable in the reference "
+                                      "(large_models/trainer.py:1168)")
+        self.model = model
+        self.include = list(model.dizo_include_names() if include is None else include)
+        self.max_iters = max_iters
+        self.proj_lr = proj_lr
+        self.l1 = l1
+        self.dp_group = dp_group
+        model.arena.set_dizo(self.include)
+        self.n = model.arena.n_slots
+        self.gs = GammaState(max(self.n, 1), model.device, tau, zo_eps, step_size)
+        self._l1 = torch.zeros(1, dtype=torch.float32, device=model.device)
+        self._l2 = torch.zeros(1, dtype=torch.float32, device=model.device)
+        self.searches = 0
+        # FO state persists across searches (large_models/trainer.py:401, :761)
+        self.fo_gamma: torch.Tensor | None = None
+        self.fo_opt = None
+
+    def _reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if _dist_on(self.dp_group):
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.dp_group)
+            t.div_(dist.get_world_size(self.dp_group))
+        return t
+
+    def measure(self) -> None:
+        """sq[i] = ||theta_i - theta_0i||^2 for every constrained tensor (one pass)."""
+        self.model.arena.sweep(sq_out=self.gs.sq)
+
+    def search_zo(self, next_batch: Callable[[], Batch], seed: int, norms_ready: bool = False) -> None:
+        """``dizo_zo_iters``: gamma_i initialised to ts_i, then ``max_iters`` two-point steps."""
+        if self.n == 0:
+            return
+        if not norms_ready:
+            self.measure()
+        gs = self.gs
+        gs.begin(reinit=True)
+        for it in range(self.max_iters):
+            batch = next_batch()
+            gs.perturb(+1.0, seed=seed, it=it)
+            self._l1.copy_(self.model.loss(batch, Transform(alpha=gs.alpha)).reshape(1))
+            gs.perturb(-2.0)
+            self._l2.copy_(self.model.loss(batch, Transform(alpha=gs.alpha)).reshape(1))
+            gs.perturb(+1.0)
+            self._reduce(self._l1)
+            self._reduce(self._l2)
+            gs.step(self._l1, self._l2)
+        self.project()
+        self.searches += 1
+
+    def project(self) -> None:
+        """theta_i <- theta_0i + alpha_i (theta_i - theta_0i), in place, one pass."""
+        if self.n:
+            self.model.arena.sweep(alpha=self.gs.alpha)
+
+    def search_fo(self, next_batch: Callable[[], Batch], fo_loss: Callable) -> None:
+        """``dizo_iters``: Adam on gamma through d loss / d gamma (gamma starts at 0 and, like
+        its Adam moments, persists across searches; L1 penalty ``l1 * sum |gamma|``)."""
+        if self.n == 0:
+            return
+        self.measure()
+        gs = self.gs
+        gs.begin(reinit=False)
+        if self.fo_gamma is None:
+            self.fo_gamma = torch.zeros(self.n, dtype=torch.float32, device=self.model.device,
+                                        requires_grad=True)
+            self.fo_opt = torch.optim.Adam([self.fo_gamma], lr=self.proj_lr)
+        for _ in range(self.max_iters):
+            batch = next_batch()
+            self.fo_opt.zero_grad(set_to_none=True)
+            alpha = self.fo_gamma / (gs.ts.detach() + 1e-8)
+            loss = fo_loss(batch, alpha) + self.l1 * self.fo_gamma.abs().sum()
+            loss.backward()
+            if _dist_on(self.dp_group):
+                dist.all_reduce(self.fo_gamma.grad, group=self.dp_group)
+                self.fo_gamma.grad.div_(dist.get_world_size(self.dp_group))
+            self.fo_opt.step()
+        with torch.no_grad():
+            gs.gamma.copy_(self.fo_gamma.detach())
+            gs.alpha.copy_(gs.gamma / (gs.ts + 1e-8))
+        self.project()
+        self.searches += 1
+
+    def state_dict(self) -> dict:
+        sd = {"gamma": self.gs.gamma.cpu(), "ts": self.gs.ts.cpu(), "searches": self.searches}
+        if self.fo_gamma is not None:
+            sd["fo_gamma"] = self.fo_gamma.detach().cpu()
+            sd["fo_opt"] = self.fo_opt.state_dict()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.gs.gamma.copy_(sd["gamma"])
+        self.gs.ts.copy_(sd["ts"])
+        self.searches = int(sd.get("searches", 0))
+        if "fo_gamma" in sd:
+            self.fo_gamma = sd["fo_gamma"].to(self.model.device).requires_grad_(True)
+            self.fo_opt = torch.optim.Adam([self.fo_gamma], lr=self.proj_lr)
+            self.fo_opt.load_state_dict(sd["fo_opt"])

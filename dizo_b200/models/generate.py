@@ -1,0 +1,192 @@
+"""Autoregressive decoding with a KV cache: greedy, temperature / top-k / top-p sampling, beams.
+
+Stands in for the ``model.generate`` calls of the reference (large_models/run.py:277-290,
+large_models/trainer.py:1554-1561): same knobs (``do_sample``, ``temperature``, ``num_beams``,
+``top_p``, ``top_k``, ``max_new_tokens``, a list of end-of-sequence ids), left-padded batches.
+The prompt is one forward through the training kernels with the per-layer QKV activations
+captured as the cache; each new token then runs the same GEMM / LayerNorm kernels on a
+[batch, d] activation and a small attention over the cache.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..ops import attention as attn_ops
+from ..ops import gemm, norm
+from .opt import _P, Batch, OPTModel, make_batch
+
+
+def filter_logits(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] = None,
+                  top_p: Optional[float] = None) -> torch.Tensor:
+    """Temperature, then top-k, then nucleus filtering (filtered entries become -inf)."""
+    if temperature and temperature != 1.0:
+        logits = logits / temperature
+    if top_k is not None and top_k > 0:
+        k = min(int(top_k), logits.shape[-1])
+        kth = torch.topk(logits, k, dim=-1).values[..., -1:]
+        logits = logits.masked_fill(logits < kth, float("-inf"))
+    if top_p is not None and 0.0 < top_p < 1.0:
+        srt, idx = torch.sort(logits, dim=-1, descending=True)
+        cum = torch.softmax(srt, dim=-1).cumsum(dim=-1)
+        drop = cum - torch.softmax(srt, dim=-1) >= top_p      # keep the first token that crosses p
+        srt = srt.masked_fill(drop, float("-inf"))
+        logits = torch.full_like(logits, float("-inf")).scatter(-1, idx, srt)
+    return logits
+
+
+class _Decoder:
+    """Per-layer K/V caches and the single-token step."""
+
+    def __init__(self, model: OPTModel, B: int, max_len: int):
+        self.m = model
+        cfg = model.config
+        d = cfg.hidden_size
+        dev, dt = model.device, model.dtype
+        self.k = [torch.zeros(B, max_len, d, dtype=dt, device=dev) for _ in range(cfg.num_hidden_layers)]
+        self.v = [torch.zeros(B, max_len, d, dtype=dt, device=dev) for _ in range(cfg.num_hidden_layers)]
+        self.len = 0
+
+    def prefill(self, batch: Batch) -> torch.Tensor:
+        m = self.m
+        d = m.config.hidden_size
+        B, L = batch.input_ids.shape
+        m.kv_capture = []
+        try:
+            h = m.hidden_states(batch)
+        finally:
+            cap, m.kv_capture = m.kv_capture, None
+        for i, qkv in enumerate(cap):
+            q3 = qkv.view(B, L, 3 * d)
+            self.k[i][:, :L].copy_(q3[:, :, d:2 * d])
+            self.v[i][:, :L].copy_(q3[:, :, 2 * d:])
+        self.len = L
+        return h[:, -1, :]                                       # left padded: last column is real
+
+    def reorder(self, index: torch.Tensor) -> None:
+        for i in range(len(self.k)):
+            self.k[i] = self.k[i].index_select(0, index)
+            self.v[i] = self.v[i].index_select(0, index)
+
+    def step(self, tokens: torch.Tensor, positions: torch.Tensor, pad_left: torch.Tensor) -> torch.Tensor:
+        """tokens, positions: int32 [B]; returns the new last hidden state [B, d]."""
+        m, cfg = self.m, self.m.config
+        d = cfg.hidden_size
+        get = m._resolver(-1, None, None, 0)
+        tok, pos = get(_P + "embed_tokens.weight"), get(_P + "embed_positions.weight")
+        if cfg.word_embed_proj_dim != d:
+            e = norm.embed(tokens.view(-1, 1), None, tok, None).view(-1, cfg.word_embed_proj_dim)
+            h = norm.add_rows(gemm.linear(e, get(_P + "project_in.weight")), positions, pos)
+        else:
+            h = norm.embed(tokens.view(-1, 1), positions.view(-1, 1), tok, pos).view(-1, d)
+        t = self.len
+        pre = cfg.do_layer_norm_before
+        for i in range(cfg.num_hidden_layers):
+            w = m._layer_weights(i, m._resolver(i, None, None, 0))
+            x = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps) if pre else h
+            qkv = gemm.linear(x, w.qkv_w, w.qkv_b)
+            self.k[i][:, t].copy_(qkv[:, d:2 * d])
+            self.v[i][:, t].copy_(qkv[:, 2 * d:])
+            ctx = attn_ops.decode_attention_reference(qkv[:, :d], self.k[i], self.v[i], t + 1,
+                                                      cfg.num_attention_heads, pad_left,
+                                                      w.prefix_k, w.prefix_v)
+            h = gemm.linear(ctx.contiguous(), w.out_w, w.out_b, residual=h)
+            if not pre:
+                h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
+            x = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps) if pre else h
+            f = gemm.linear(x, w.fc1_w, w.fc1_b, act=cfg.activation_function)
+            h = gemm.linear(f, w.fc2_w, w.fc2_b, residual=h)
+            if not pre:
+                h = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
+        self.len = t + 1
+        return h
+
+
+def _head_logits(model: OPTModel, h_last: torch.Tensor) -> torch.Tensor:
+    cfg = model.config
+    get = model._resolver(-1, None, None, 0)
+    x = h_last
+    if cfg.do_layer_norm_before:
+        x = norm.layernorm(x, get(_P + "final_layer_norm.weight"), get(_P + "final_layer_norm.bias"),
+                           cfg.layer_norm_eps)
+    if cfg.word_embed_proj_dim != cfg.hidden_size:
+        x = gemm.linear(x, get(_P + "project_out.weight"))
+    table = get("lm_head.weight") if model.untied else get(_P + "embed_tokens.weight")
+    return gemm.linear(x.contiguous(), table, out_dtype=torch.float32).float()
+
+
+@torch.no_grad()
+def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+             max_new_tokens: int = 50, do_sample: bool = False, temperature: float = 1.0,
+             top_k: Optional[int] = None, top_p: Optional[float] = None, num_beams: int = 1,
+             eos_token_id: Optional[Sequence[int]] = None, pad_token_id: int = 1,
+             seed: Optional[int] = None, transform=None) -> List[List[int]]:
+    """Returns, per input row, prompt + generated token ids (generation stops at an EOS id,
+    which is kept, as Hugging Face does).  ``transform`` is accepted for API symmetry and must
+    be None: perturb in place around the call when decoding under a perturbation."""
+    assert transform is None, "decode under a perturbation by perturbing in place around generate()"
+    dev = model.device
+    ids = torch.as_tensor(input_ids).long()
+    B0, L0 = ids.shape
+    mask = torch.ones_like(ids) if attention_mask is None else torch.as_tensor(attention_mask).long()
+    max_new_tokens = max(0, int(max_new_tokens))
+    eos = set(int(e) for e in (eos_token_id or []))
+    nb = max(1, int(num_beams))
+    if nb > 1:
+        ids = ids.repeat_interleave(nb, 0)
+        mask = mask.repeat_interleave(nb, 0)
+    B = ids.shape[0]
+    batch = make_batch(ids, mask).to(dev)
+    dec = _Decoder(model, B, L0 + max_new_tokens)
+    h_last = dec.prefill(batch)
+    n_real = mask.sum(dim=1).to(dev)
+    pad_left = batch.pad_left
+    gen = torch.Generator(device=dev)
+    if seed is not None:
+        gen.manual_seed(seed)
+    out = [row[m.bool()].tolist() for row, m in zip(ids, mask)]
+    done = torch.zeros(B, dtype=torch.bool, device=dev)
+    beam_score = torch.zeros(B, device=dev)
+    if nb > 1:
+        beam_score.view(B0, nb)[:, 1:] = float("-inf")            # identical beams at step 0
+    for t in range(max_new_tokens):
+        logits = _head_logits(model, h_last)
+        if nb == 1:
+            if do_sample:
+                probs = torch.softmax(filter_logits(logits, temperature, top_k, top_p), dim=-1)
+                nxt = torch.multinomial(probs, 1, generator=gen).squeeze(1)
+            else:
+                nxt = logits.argmax(dim=-1)
+            nxt = torch.where(done, torch.full_like(nxt, pad_token_id), nxt)
+        else:
+            lp = torch.log_softmax(logits, dim=-1)
+            V = lp.shape[-1]
+            lp = torch.where(done[:, None], torch.full_like(lp, float("-inf")), lp)
+            lp[done, pad_token_id] = 0.0                           # finished beams carry their score
+            cand = (beam_score[:, None] + lp).view(B0, nb * V)
+            top, flat = cand.topk(nb, dim=-1)
+            src = flat // V + (torch.arange(B0, device=dev) * nb)[:, None]
+            nxt = (flat % V).reshape(-1)
+            src = src.reshape(-1)
+            beam_score = top.reshape(-1)
+            dec.reorder(src)
+            done = done[src]
+            n_real = n_real[src]
+            pad_left = pad_left[src]
+            out = [list(out[i]) for i in src.tolist()]
+        toks = nxt.tolist()
+        dl = done.tolist()
+        for i in range(B):
+            if not dl[i]:
+                out[i].append(toks[i])
+        done = done | torch.tensor([tk in eos for tk in toks], dtype=torch.bool, device=dev)
+        if bool(done.all()) or t + 1 == max_new_tokens:
+            break
+        pos = (n_real + 2).to(torch.int32)                         # OPT positions: index + 2
+        n_real = n_real + 1
+        h_last = dec.step(nxt.to(torch.int32), pos, pad_left)
+    if nb > 1:
+        best = beam_score.view(B0, nb).argmax(dim=-1) + torch.arange(B0, device=dev) * nb
+        out = [out[i] for i in best.tolist()]
+    return out

@@ -53,8 +53,13 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+launch_count = 0     # entry points called so far (each launches one kernel)
+
+
 def check(rc: int, what: str) -> None:
+    global launch_count
     if rc == 0:
+        launch_count += 1
         return
     if rc >= 1000:
         raise KernelError(f"{what}: CUDA error {rc - 1000} "

@@ -1,0 +1,178 @@
+"""Checkpoints: Hugging Face compatible weights + everything needed to resume a ZO run exactly.
+
+A checkpoint directory holds
+  * ``model.safetensors`` (``pytorch_model.bin`` when safetensors is missing) with Hugging Face
+    OPT parameter names, plus ``lora_A/B`` and ``prefix_keys/values`` entries, and ``config.json``
+    - loadable by ``transformers.OPTForCausalLM.from_pretrained`` for full fine-tuning runs;
+  * ``trainer_state.json`` (step, epoch, log history, best metric);
+  * ``zo_state.pt``: NumPy global RNG state (the per-step seeds are drawn from it, so restoring
+    it replays the same z stream), loss / accuracy curves, the DiZO gamma vector with its
+    first-order Adam moments, the projection seed generator, and the anchor theta_0 of the
+    constrained tensors;
+  * ``manifest.json``: byte sizes and SHA-256 of every file, checked on load, so a truncated or
+    corrupted checkpoint is detected instead of silently resumed.
+The reference only discovers checkpoints (large_models/run.py:466-479) and reloads
+``trainer_state.json`` (large_models/trainer.py:1072-1094); its ZO loop never writes any.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import logging
+import os
+import re
+from typing import Optional
+
+import numpy as np
+import torch
+
+logger = logging.getLogger(__name__)
+
+
+class CheckpointError(RuntimeError):
+    pass
+
+
+def _sha256(path: str) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for blk in iter(lambda: f.read(1 << 22), b""):
+            h.update(blk)
+    return h.hexdigest()
+
+
+def _write_manifest(out: str) -> None:
+    files = {}
+    for name in sorted(os.listdir(out)):
+        p = os.path.join(out, name)
+        if name != "manifest.json" and os.path.isfile(p):
+            files[name] = {"bytes": os.path.getsize(p), "sha256": _sha256(p)}
+    with open(os.path.join(out, "manifest.json"), "w") as f:
+        json.dump(files, f, indent=2)
+
+
+def verify_checkpoint(path: str) -> None:
+    man = os.path.join(path, "manifest.json")
+    if not os.path.exists(man):
+        raise CheckpointError(f"{path}: no manifest.json (incomplete checkpoint)")
+    with open(man) as f:
+        files = json.load(f)
+    for name, meta in files.items():
+        p = os.path.join(path, name)
+        if not os.path.exists(p):
+            raise CheckpointError(f"{path}: {name} is missing")
+        if os.path.getsize(p) != meta["bytes"]:
+            raise CheckpointError(f"{path}: {name} is truncated ({os.path.getsize(p)} of {meta['bytes']} bytes)")
+        if _sha256(p) != meta["sha256"]:
+            raise CheckpointError(f"{path}: {name} is corrupted (checksum mismatch)")
+
+
+def save_weights(out: str, state_dict: dict) -> str:
+    os.makedirs(out, exist_ok=True)
+    sd = {k: v.detach().cpu().contiguous() for k, v in state_dict.items()}
+    try:
+        from safetensors.torch import save_file
+        # tied tensors may not share storage inside a safetensors file
+        if "lm_head.weight" in sd and "model.decoder.embed_tokens.weight" in sd and \
+                sd["lm_head.weight"].data_ptr() == sd["model.decoder.embed_tokens.weight"].data_ptr():
+            sd = {k: v for k, v in sd.items() if k != "lm_head.weight"}
+        p = os.path.join(out, "model.safetensors")
+        save_file(sd, p, metadata={"format": "pt"})
+    except ImportError:  # pragma: no cover
+        p = os.path.join(out, "pytorch_model.bin")
+        torch.save(sd, p)
+    return p
+
+
+def load_weights(path: str) -> dict:
+    st = os.path.join(path, "model.safetensors")
+    if os.path.exists(st):
+        from safetensors.torch import load_file
+        return load_file(st)
+    idx = os.path.join(path, "model.safetensors.index.json")
+    if os.path.exists(idx):
+        from safetensors.torch import load_file
+        with open(idx) as f:
+            shards = sorted(set(json.load(f)["weight_map"].values()))
+        sd = {}
+        for s in shards:
+            sd.update(load_file(os.path.join(path, s)))
+        return sd
+    for name in ("pytorch_model.bin",):
+        p = os.path.join(path, name)
+        if os.path.exists(p):
+            return torch.load(p, map_location="cpu", weights_only=True)
+    idx = os.path.join(path, "pytorch_model.bin.index.json")
+    if os.path.exists(idx):
+        with open(idx) as f:
+            shards = sorted(set(json.load(f)["weight_map"].values()))
+        sd = {}
+        for s in shards:
+            sd.update(torch.load(os.path.join(path, s), map_location="cpu", weights_only=True))
+        return sd
+    raise CheckpointError(f"{path}: no model.safetensors / pytorch_model.bin")
+
+
+def save_checkpoint(out: str, model, trainer=None) -> None:
+    os.makedirs(out, exist_ok=True)
+    save_weights(out, model.state_dict())
+    with open(os.path.join(out, "config.json"), "w") as f:
+        json.dump(model.config.to_hf_dict(), f, indent=2)
+    if trainer is not None:
+        trainer.state.save_to_json(os.path.join(out, "trainer_state.json"))
+        zo = {"numpy_rng": np.random.get_state(), "loss_list": list(trainer.loss_list),
+              "accuracy": list(trainer.accuracy), "objective": trainer.objective,
+              "args": trainer.args.to_dict()}
+        if trainer.dizo_trainer is not None:
+            zo["dizo"] = trainer.dizo_trainer.projector.state_dict()
+            zo["dizo_i"] = trainer.dizo_trainer.i
+            zo["dizo_seed_rng"] = trainer._dizo_seed_rng.get_state()
+            ar = model.arena
+            zo["anchor"] = {n: ar.anchor_view(n).detach().cpu().clone() for n in ar.slot_names}
+        torch.save(zo, os.path.join(out, "zo_state.pt"))
+    _write_manifest(out)
+
+
+def load_checkpoint(path: str, model, trainer=None, verify: bool = True) -> None:
+    if verify:
+        verify_checkpoint(path)
+    model.load_state_dict(load_weights(path), strict=False)
+    if trainer is None:
+        return
+    from ..trainer import TrainerState
+    ts = os.path.join(path, "trainer_state.json")
+    if os.path.exists(ts):
+        keep_max = trainer.state.max_steps
+        trainer.state = TrainerState.load_from_json(ts)
+        trainer.state.max_steps = keep_max or trainer.state.max_steps
+    zp = os.path.join(path, "zo_state.pt")
+    if os.path.exists(zp):
+        zo = torch.load(zp, map_location="cpu", weights_only=False)
+        np.random.set_state(zo["numpy_rng"])
+        trainer.loss_list = list(zo.get("loss_list", []))
+        trainer.accuracy = list(zo.get("accuracy", []))
+        trainer.objective = zo.get("objective", 0.0)
+        if "dizo" in zo and trainer.dizo_trainer is not None:
+            trainer.dizo_trainer.projector.load_state_dict(zo["dizo"])
+            trainer.dizo_trainer.i = zo.get("dizo_i", 0)
+            trainer._dizo_seed_rng.set_state(zo["dizo_seed_rng"])
+            ar = model.arena
+            for n, t in zo.get("anchor", {}).items():
+                ar.anchor_view(n).copy_(t.to(ar.dtype))
+
+
+_CKPT_RE = re.compile(r"^checkpoint-(\d+)$")
+
+
+def get_last_checkpoint(folder: str) -> Optional[str]:
+    """Highest-numbered complete ``checkpoint-N`` directory under ``folder`` (or None)."""
+    if not os.path.isdir(folder):
+        return None
+    best = None
+    for name in os.listdir(folder):
+        m = _CKPT_RE.match(name)
+        p = os.path.join(folder, name)
+        if m and os.path.isdir(p) and os.path.exists(os.path.join(p, "manifest.json")):
+            if best is None or int(m.group(1)) > best[0]:
+                best = (int(m.group(1)), p)
+    return best[1] if best else None

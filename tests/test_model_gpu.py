@@ -1,0 +1,95 @@
+"""Whole-model checks on the GPU: kernel forward vs the fp32 CPU statement of the same model,
+in-flight transform vs in-place perturbation, a short ZO run."""
+import numpy as np
+import pytest
+import torch
+
+from dizo_b200.data.synthetic import synthetic_batch
+from dizo_b200.engine import DiZOProjector, ZOEngine
+from dizo_b200.models.opt import OPTModel, Transform, make_batch, preset
+from dizo_b200.ops import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(name="opt-125m", layers=2, mode="full", **kw):
+    cfg = preset(name, num_hidden_layers=layers, **kw)
+    cpu = OPTModel(cfg, "cpu", torch.float32, mode=mode).init_random(0)
+    gpu = OPTModel(cfg, "cuda", torch.bfloat16, mode=mode)
+    gpu.load_state_dict(cpu.state_dict())
+    # the CPU oracle holds the bf16-rounded weights, so only activations differ
+    cpu.load_state_dict({k: v.float() for k, v in gpu.state_dict().items()})
+    return cfg, cpu, gpu
+
+
+@pytest.mark.parametrize("name,kw", [("opt-125m", {}), ("opt-2.7b", {}),
+                                      ("opt-350m", {})])
+def test_logits_match_cpu_oracle(name, kw):
+    cfg, cpu, gpu = _pair(name, layers=2, **kw)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(4, cfg.vocab_size, (2, 72), generator=g)
+    mask = torch.ones(2, 72, dtype=torch.long)
+    mask[1, :9] = 0
+    rows = torch.tensor([71, 72 + 40, 72 + 71], dtype=torch.int32)
+    ref = cpu.logits(make_batch(ids, mask), rows)
+    out = gpu.logits(make_batch(ids, mask).to("cuda"), rows.cuda()).float().cpu()
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    err = (out - ref).abs().max().item()
+    assert err < 0.08 * max(1.0, ref.abs().max().item()), err
+    assert torch.equal(out.argmax(-1), ref.argmax(-1)) or err < 0.05
+
+
+def test_inflight_equals_inplace_perturbation():
+    cfg, _, gpu = _pair("opt-125m", layers=3)
+    b = synthetic_batch(0, 4, 64, cfg.vocab_size).to("cuda")
+    l_inflight = gpu.loss(b, Transform(seed=5, coef=1e-3)).item()
+    before = gpu.arena.data.clone()
+    gpu.arena.sweep(seed1=5, c1=1e-3)
+    l_inplace = gpu.loss(b).item()
+    gpu.arena.data.copy_(before)
+    assert l_inflight == l_inplace                       # same staged bits, same kernels
+    # and without the side stream
+    gpu.overlap_transform = False
+    assert gpu.loss(b, Transform(seed=5, coef=1e-3)).item() == l_inflight
+    # determinism of a forward
+    assert gpu.loss(b, Transform(seed=5, coef=1e-3)).item() == l_inflight
+
+
+@pytest.mark.parametrize("mode", ["lora", "prefix", "lora+prefix"])
+def test_peft_forward_matches_cpu(mode):
+    cfg, cpu, gpu = _pair("opt-125m", layers=2, mode=mode)
+    for m in (cpu, gpu):
+        for n in m.trainable_names:                      # make B non-zero so LoRA matters
+            if "lora_B" in n:
+                m.param(n).copy_((torch.randn(m.param(n).shape, generator=torch.Generator().manual_seed(1)) * 0.05)
+                                 .to(m.dtype))
+    cpu.load_state_dict({k: v.float() for k, v in gpu.state_dict().items()})
+    b = synthetic_batch(1, 3, 48, cfg.vocab_size, pad_left=5)
+    ref = cpu.loss(b).item()
+    out = gpu.loss(b.to("cuda")).item()
+    assert abs(out - ref) < 2e-2, (out, ref)
+    t = Transform(seed=9, coef=1e-2)
+    assert abs(gpu.loss(b.to("cuda"), t).item() - cpu.loss(b, t).item()) < 2e-2
+
+
+def test_zo_training_reduces_loss_and_dizo_bounds():
+    cfg = preset("opt-125m", num_hidden_layers=2)
+    model = OPTModel(cfg, "cuda", torch.bfloat16).init_random_fast(0)
+    eng = ZOEngine(model, eps=1e-3)
+    proj = DiZOProjector(model, max_iters=3)
+    fixed = synthetic_batch(0, 16, 32, cfg.vocab_size).to("cuda")
+    first = model.loss(fixed).item()
+    rng = np.random.RandomState(0)
+    for step in range(60):
+        eng.step(fixed, 2e-4, seed=int(rng.randint(1 << 30)))
+    last = model.loss(fixed).item()
+    assert last < first - 0.02, (first, last)
+    proj.search_zo(lambda: fixed, seed=3)
+    gs = proj.gs
+    assert (gs.gamma >= 0.8 * gs.ts - 1e-5).all() and (gs.gamma <= 1.2 * gs.ts + 1e-5).all()
+    # after the projection the distance to the anchor equals gamma
+    proj.measure()
+    assert torch.allclose(gs.sq.sqrt(), gs.gamma, rtol=2e-2)
+    torch.cuda.synchronize()
+    _lib.check_device_errors()

@@ -87,23 +87,55 @@ zo_sweep_kernel(const ZoSweepArgs a) {
   if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
   if (Z2 && a.c2_ptr) c2 *= __ldg(a.c2_ptr);
 
-  int cur = -1;
+  // Every warp owns a contiguous run of chunks, so the tensor descriptor is re-read only
+  // when the run crosses into the next tensor, and the next chunk's load is in flight while
+  // the current one is being transformed.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int WARPS = ZO_THREADS / 32;
-  for (long long chunk = a.chunk_begin + (long long)blockIdx.x * WARPS + warp; chunk < a.chunk_end;
-       chunk += (long long)gridDim.x * WARPS) {
+  const long long total = a.chunk_end - a.chunk_begin;
+  const long long nwarps = (long long)gridDim.x * WARPS;
+  const long long per = (total + nwarps - 1) / nwarps;
+  long long chunk = a.chunk_begin + ((long long)blockIdx.x * WARPS + warp) * per;
+  const long long chunk_stop = min(chunk + per, a.chunk_end);
+  if (chunk >= chunk_stop) return;
+
+  int cur = find_tensor(a.table, a.t_begin, a.t_end, chunk * ZO_CHUNK);
+  ZoTensor t = a.table[cur];
+  long long t_next = (cur + 1 < a.t_end) ? a.table[cur + 1].offset : (1ll << 62);
+  float alpha = 1.f;
+  if (BLEND && t.slot >= 0) alpha = __ldg(a.alpha + t.slot);
+
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  {
     const long long cpos = chunk * ZO_CHUNK;
-    if (cur < 0 || cpos >= a.table[cur].offset + a.table[cur].numel ||
-        (cur + 1 < a.t_end && cpos >= a.table[cur + 1].offset))
-      cur = find_tensor(a.table, a.t_begin, a.t_end, cpos);
-    const ZoTensor t = a.table[cur];
+    if (cpos - t.offset + lane * 8 < t.numel) raw = *reinterpret_cast<const uint4*>(a.src + cpos + lane * 8);
+  }
+  for (; chunk < chunk_stop; ++chunk) {
+    const long long cpos = chunk * ZO_CHUNK;
     const long long e0 = cpos - t.offset + lane * 8;  // element inside this piece
+    const bool active = e0 < t.numel;
+    const uint4 cur_raw = raw;
+    // ---- prefetch the next chunk (possibly of the next tensor)
+    const long long npos = cpos + ZO_CHUNK;
+    ZoTensor tn = t;
+    int ncur = cur;
+    long long tn_next = t_next;
+    bool have_next = chunk + 1 < chunk_stop;
+    if (have_next) {
+      if (npos >= t_next) {
+        ncur = cur + 1;
+        while (ncur + 1 < a.t_end && a.table[ncur + 1].offset <= npos) ++ncur;
+        tn = a.table[ncur];
+        tn_next = (ncur + 1 < a.t_end) ? a.table[ncur + 1].offset : (1ll << 62);
+      }
+      if (npos - tn.offset + lane * 8 < tn.numel)
+        raw = *reinterpret_cast<const uint4*>(a.src + npos + lane * 8);
+    }
     float sq = 0.f;
-    if (e0 < t.numel) {
+    if (active) {
       const long long pos = cpos + lane * 8;
-      uint4 raw = *reinterpret_cast<const uint4*>(a.src + pos);
-      float v[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
-                    bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
+      float v[8] = {bf16_lo(cur_raw.x), bf16_hi(cur_raw.x), bf16_lo(cur_raw.y), bf16_hi(cur_raw.y),
+                    bf16_lo(cur_raw.z), bf16_hi(cur_raw.z), bf16_lo(cur_raw.w), bf16_hi(cur_raw.w)};
       float an[8];
       const bool slotted = (BLEND || NORM) && t.slot >= 0;
       if (slotted) {
@@ -112,9 +144,8 @@ zo_sweep_kernel(const ZoSweepArgs a) {
         an[4] = bf16_lo(ar.z); an[5] = bf16_hi(ar.z); an[6] = bf16_lo(ar.w); an[7] = bf16_hi(ar.w);
       }
       if (BLEND && slotted) {
-        const float al = __ldg(a.alpha + t.slot);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = fmaf(al, v[j] - an[j], an[j]);
+        for (int j = 0; j < 8; ++j) v[j] = fmaf(alpha, v[j] - an[j], an[j]);
       }
       const uint32_t grp = zo_group(t, e0);
       if (c1 != 0.f) {
@@ -147,7 +178,7 @@ zo_sweep_kernel(const ZoSweepArgs a) {
       }
       if (e0 + 8 > t.numel) {
         // ragged tail of a tensor: keep the padding elements as they were
-        const uint32_t rawv[4] = {raw.x, raw.y, raw.z, raw.w};
+        const uint32_t rawv[4] = {cur_raw.x, cur_raw.y, cur_raw.z, cur_raw.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (e0 + j >= t.numel) {
@@ -174,6 +205,12 @@ zo_sweep_kernel(const ZoSweepArgs a) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
       if (lane == 0 && t.sq_base >= 0) a.chunk_sq[t.sq_base + (cpos - t.offset) / ZO_CHUNK] = sq;
+    }
+    if (have_next && ncur != cur) {
+      cur = ncur;
+      t = tn;
+      t_next = tn_next;
+      if (BLEND && t.slot >= 0) alpha = __ldg(a.alpha + t.slot);
     }
   }
 }

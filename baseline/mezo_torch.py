@@ -55,9 +55,16 @@ def loss_with_option_len(model, input_ids, attention_mask, option_len, num_optio
 class TorchMeZO:
     """Reference-pattern ZO-SGD (+ optional DiZO gamma search by ZO) on a HF model."""
 
-    def __init__(self, model, eps=1e-3, dizo=False):
+    def __init__(self, model, eps=1e-3, dizo=False, z_fn=None, seed_fn=None, gamma_z_fn=None, loss_fn=None):
+        """``z_fn(name, param, seed)``, ``seed_fn()``, ``gamma_z_fn(index, iteration)`` and
+        ``loss_fn(model, batch)`` let a test feed this loop the framework's random streams and
+        loss; by default it draws from torch / NumPy exactly as the reference does."""
         self.model = model
         self.eps = eps
+        self.z_fn = z_fn
+        self.seed_fn = seed_fn or (lambda: int(np.random.randint(1_000_000_000)))
+        self.gamma_z_fn = gamma_z_fn
+        self.loss_fn = loss_fn or (lambda m, b: loss_with_option_len(m, **b))
         self.named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         # the reference drops the (tied) token embedding from the ZO set in full fine-tuning
         if self.named and self.named[0][0] == "model.decoder.embed_tokens.weight":
@@ -70,25 +77,30 @@ class TorchMeZO:
             self.anchor = {n: p.detach().clone() for n, p in self.incl}
             self.gamma = [torch.zeros(1, device=p.device, dtype=p.dtype) for _, p in self.incl]
 
+    def _z(self, name, p, seed):
+        if self.z_fn is not None:
+            return self.z_fn(name, p, seed).to(p.dtype)
+        return torch.normal(mean=0, std=1, size=p.data.size(), device=p.data.device, dtype=p.data.dtype)
+
     def perturb(self, seed, scaling):
         torch.manual_seed(seed)
         for name, p in self.named:
-            z = torch.normal(mean=0, std=1, size=p.data.size(), device=p.data.device, dtype=p.data.dtype)
+            z = self._z(name, p, seed)
             p.data = p.data + scaling * z * self.eps
             self.random_vector[name] = z
 
     @torch.inference_mode()
     def step(self, batch, lr):
-        seed = int(np.random.randint(1_000_000_000))
+        seed = self.seed_fn()
         self.perturb(seed, 1)
-        l1 = loss_with_option_len(self.model, **batch)
+        l1 = self.loss_fn(self.model, batch)
         self.perturb(seed, -2)
-        l2 = loss_with_option_len(self.model, **batch)
+        l2 = self.loss_fn(self.model, batch)
         g = ((l1 - l2) / (2 * self.eps)).item()
         self.perturb(seed, 1)
         torch.manual_seed(seed)
-        for _, p in self.named:
-            z = torch.normal(mean=0, std=1, size=p.data.size(), device=p.data.device, dtype=p.data.dtype)
+        for name, p in self.named:
+            z = self._z(name, p, seed)
             p.data = p.data - lr * (g * z)
         return l1
 
@@ -109,24 +121,27 @@ class TorchMeZO:
     @torch.no_grad()
     def dizo_search(self, batches, tau=0.2, zo_eps=0.1, step_size=2):
         init = True
-        for batch in batches:
+        for it, batch in enumerate(batches):
             ts = [torch.norm(p.data - self.anchor[n]) for n, p in self.incl]
             if init:
                 self.gamma = [t.clone().reshape(1) for t in ts]
                 init = False
             zs = []
             for i, g in enumerate(self.gamma):
-                z = torch.normal(0, 1, size=(1,), device=g.device, dtype=g.dtype)
+                if self.gamma_z_fn is not None:
+                    z = torch.tensor([self.gamma_z_fn(i, it)], device=g.device, dtype=g.dtype)
+                else:
+                    z = torch.normal(0, 1, size=(1,), device=g.device, dtype=g.dtype)
                 z = torch.clip(z, (-tau / zo_eps) * ts[i], (tau / zo_eps) * ts[i])
                 zs.append(z)
                 self.gamma[i] = g + z * zo_eps
             al = self._ratios(); self._apply(al)
-            l1 = loss_with_option_len(self.model, **batch)
+            l1 = self.loss_fn(self.model, batch)
             self._reverse(al)
             for i in range(len(self.gamma)):
                 self.gamma[i] = self.gamma[i] - 2 * zs[i] * zo_eps
             al = self._ratios(); self._apply(al)
-            l2 = loss_with_option_len(self.model, **batch)
+            l2 = self.loss_fn(self.model, batch)
             self._reverse(al)
             grad = (l1 - l2) / (2 * zo_eps)
             for i in range(len(self.gamma)):

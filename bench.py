@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--mode", default="full", help="full | lora | prefix | lora+prefix")
     ap.add_argument("--zo-mode", default="inflight", choices=["inflight", "inplace"])
     ap.add_argument("--enhanced", default="zo", choices=["none", "zo"])
-    ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--overlap", action="store_true", help="sweep the next layer on a side stream")
     ap.add_argument("--baseline-candidates", type=int, default=2)
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
@@ -141,7 +141,7 @@ def run_ours(a, world, rank, local):
 
     dev = torch.device("cuda", local)
     cfg = preset(a.model)
-    model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=not a.no_overlap)
+    model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=a.overlap)
     model.init_random_fast(seed=0)
     engine = ZOEngine(model, eps=1e-3, mode=a.zo_mode)
     projector = DiZOProjector(model) if a.enhanced == "zo" else None

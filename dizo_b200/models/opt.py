@@ -217,7 +217,7 @@ class OPTModel:
 
     def __init__(self, config: OPTConfig, device="cpu", dtype=torch.float32, mode: str = "full",
                  lora_r: int = 8, lora_alpha: int = 16, num_prefix: int = 5, untie_emb: bool = False,
-                 overlap_transform: bool = True):
+                 overlap_transform: bool = False):
         self.config = config
         self.device = torch.device(device)
         self.dtype = dtype

@@ -1,0 +1,453 @@
+// Two-SM variant of the bf16 GEMM:  out[M,N] = epilogue( A[M,K] * W[N,K]^T ).
+//
+// A thread-block cluster of two CTAs (one per SM of a pair) computes one 256 x 256 output
+// tile with tcgen05.mma.cta_group::2: CTA r of the pair stages rows [128r, 128r+128) of the
+// A tile and rows [128r, 128r+128) of the W tile, so each SM fills 32 KB per 64-wide K block
+// instead of the 48 KB of the one-SM kernel (gemm_sm100.cu) while the pair issues
+// 256 x 256 x 16 instructions that read both halves from both shared memories.  The
+// accumulator of CTA r (its 128 rows x 256 columns, fp32) lives in that CTA's TMEM, double
+// buffered, and is drained by that CTA's own epilogue warps.
+//
+//   warp 0   : TMA producer of this CTA (loads carry .cta_group::2 and complete on the
+//              LEADER's "full" barrier; no multicast anywhere)
+//   warp 1   : TMEM allocation (both CTAs); in the leader, one lane issues the MMAs and
+//              commits to the ring's "empty" barriers and the accumulator "full" barriers of
+//              BOTH CTAs (tcgen05.commit ... multicast::cluster)
+//   warps 2-5: epilogue of this CTA's 128 rows; hands the accumulator back by arriving on
+//              the leader's "accumulator empty" barrier (count 8 = 4 warps x 2 CTAs)
+// Every wait is bounded (see common.cuh); both CTAs meet at a cluster barrier before TMEM is
+// released, so neither exits while the other may still read its shared memory.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace dz {
+
+constexpr int G2_BM = 256;   // per cluster
+constexpr int G2_BN = 256;
+constexpr int G2_BK = 64;
+constexpr int G2_STAGES = 6;
+constexpr int G2_THREADS = 192;
+constexpr int G2_A_BYTES = 128 * G2_BK * 2;          // this CTA's half of A
+constexpr int G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;  // this CTA's half of W
+constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 1024;
+constexpr uint32_t G2_TMEM_COLS = 2 * G2_BN;
+
+struct Gemm2Args {
+  int M, N, K;
+  int num_m, num_n, group_m;
+  void* out;
+  long long ldo;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  int act;
+  int out_fp32;
+  float out_scale;
+  uint32_t* err;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P1;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P1;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag, uint32_t* err_word,
+                                                  uint32_t code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > DZ_WAIT_TIMEOUT_NS) {
+        *abort_flag = 1;
+        if (err_word) atomicCAS(err_word, 0u, code | (blockIdx.x << 8));
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// 2-D tiled load into this CTA's shared memory whose completion bytes are credited to an
+// mbarrier that may live in the peer CTA (cluster address).  Not a multicast.
+__device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap* m,
+                                                uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2sm() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ss_2sm(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at the same offset in every CTA of `mask` once the MMAs issued so
+// far have completed.
+__device__ __forceinline__ void umma_commit_2sm(uint32_t bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;"
+      ::"r"(bar), "h"(mask)
+      : "memory");
+}
+
+__device__ __forceinline__ void tile_coords2(int tile, const Gemm2Args& p, int& mb, int& nb) {
+  int tiles_per_group = p.group_m * p.num_n;
+  int g = tile / tiles_per_group;
+  int first_m = g * p.group_m;
+  int gm = min(p.group_m, p.num_m - first_m);
+  int r = tile - g * tiles_per_group;
+  mb = first_m + r % gm;
+  nb = r / gm;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const Gemm2Args p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[G2_STAGES];    // used in the leader only
+  __shared__ __align__(8) uint64_t bar_empty[G2_STAGES];   // one per CTA
+  __shared__ __align__(8) uint64_t bar_acc_full[2];        // one per CTA
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];       // used in the leader only
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_tiles = p.num_m * p.num_n;
+  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < G2_STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 8);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(smem_u32(&s_tmem_base), G2_TMEM_COLS);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // peer barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (each CTA)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int mb, nb;
+        tile_coords2(tile, p, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &s_abort, p.err, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = smem_u32(&bar_full[stage]);
+          const uint32_t full_leader = map_to_cta(full_local, 0);
+          const uint32_t a_dst = smem_base + stage * G2_STAGE_BYTES;
+          const uint32_t b_dst = a_dst + G2_A_BYTES;
+          if (leader) mbar_arrive_expect_tx(full_local, 2 * G2_STAGE_BYTES);  // both CTAs' bytes
+          tma_load_2d_2sm(a_dst, &tmA, full_leader, kb * G2_BK, mb * G2_BM + (int)rank * 128);
+          tma_load_2d_2sm(b_dst, &tmB, full_leader, kb * G2_BK, nb * G2_BN + (int)rank * (G2_BN / 2));
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA)
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(G2_BM, G2_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (!mbar_wait_cluster(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1, &s_abort, p.err,
+                               ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * G2_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &s_abort, p.err, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * G2_STAGE_BYTES;
+          const uint32_t b_src = a_src + G2_A_BYTES;
+          const uint64_t a_desc = umma_desc_k_sw128(a_src);
+          const uint64_t b_desc = umma_desc_k_sw128(b_src);
+#pragma unroll
+          for (int k = 0; k < G2_BK / 16; ++k)
+            umma_bf16_ss_2sm(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_2sm(smem_u32(&bar_empty[stage]), 3);     // frees the stage in both CTAs
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_2sm(smem_u32(&bar_acc_full[acc]), 3);      // wakes both epilogues
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (each CTA)
+    const int quad = warp & 3;
+    const int row_in_tile = (int)rank * 128 + quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+      int mb, nb;
+      tile_coords2(tile, p, mb, nb);
+      if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &s_abort, p.err, ERR_WAIT_TMEM_FULL))
+        break;
+      tc_fence_after();
+      const long long row = (long long)mb * G2_BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < G2_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = nb * G2_BN + c * 32;
+        if (col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        const bool full_chunk = (col0 + 32 <= p.N);
+        if (p.bias) {
+          if (full_chunk) {
+            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 b = __ldg(bp + q);
+              v[q * 8 + 0] += bf16_lo(b.x); v[q * 8 + 1] += bf16_hi(b.x);
+              v[q * 8 + 2] += bf16_lo(b.y); v[q * 8 + 3] += bf16_hi(b.y);
+              v[q * 8 + 4] += bf16_lo(b.z); v[q * 8 + 5] += bf16_hi(b.z);
+              v[q * 8 + 6] += bf16_lo(b.w); v[q * 8 + 7] += bf16_hi(b.w);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+        }
+        if (p.out_scale != 1.0f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        } else if (p.act == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        }
+        if (row_ok) {
+          if (p.residual) {
+            const __nv_bfloat16* rp = p.residual + row * p.ldr + col0;
+            if (full_chunk) {
+              const uint4* rp4 = reinterpret_cast<const uint4*>(rp);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 b = __ldg(rp4 + q);
+                v[q * 8 + 0] += bf16_lo(b.x); v[q * 8 + 1] += bf16_hi(b.x);
+                v[q * 8 + 2] += bf16_lo(b.y); v[q * 8 + 3] += bf16_hi(b.y);
+                v[q * 8 + 4] += bf16_lo(b.z); v[q * 8 + 5] += bf16_hi(b.z);
+                v[q * 8 + 6] += bf16_lo(b.w); v[q * 8 + 7] += bf16_hi(b.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+            }
+          }
+          if (p.out_fp32) {
+            float* op = reinterpret_cast<float*>(p.out) + row * p.ldo + col0;
+            if (full_chunk) {
+              float4* op4 = reinterpret_cast<float4*>(op);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                op4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) op[j] = v[j];
+            }
+          } else {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
+            if (full_chunk) {
+              uint4* op4 = reinterpret_cast<uint4*>(op);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                op4[q] = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) op[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      }
+      // this CTA's half of the accumulator is drained: tell the leader's MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort && threadIdx.x == 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, G2_TMEM_COLS);
+  }
+}
+
+}  // namespace dz
+
+using namespace dz;
+
+// Same contract as dz_gemm_bf16_tn (gemm_sm100.cu); computed by pairs of SMs.
+extern "C" int dz_gemm2_bf16_tn(const void* A, long long lda, const void* W, long long ldw, void* out,
+                                long long ldo, const void* bias, const void* residual, long long ldr,
+                                int M, int N, int K, int act, int out_fp32, float out_scale,
+                                uint32_t* err, cudaStream_t stream) {
+  if (!A || !W || !out || M <= 0 || N <= 0 || K <= 0) return DZ_ERR_ARG;
+  if ((K & 7) || (lda & 7) || (ldw & 7)) return DZ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return DZ_ERR_ALIGN;
+  int esz = out_fp32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || ((ldo * esz) & 15)) return DZ_ERR_ALIGN;
+  if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) return DZ_ERR_ALIGN;
+  if (residual && ((reinterpret_cast<uintptr_t>(residual) & 15) || (ldr & 7))) return DZ_ERR_ALIGN;
+  Gemm2Args a{};
+  a.M = M; a.N = N; a.K = K;
+  a.out = out; a.ldo = ldo;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  a.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  a.ldr = ldr; a.act = act; a.out_fp32 = out_fp32; a.out_scale = out_scale; a.err = err;
+  a.num_m = (M + G2_BM - 1) / G2_BM;
+  a.num_n = (N + G2_BN - 1) / G2_BN;
+  a.group_m = a.num_m < 8 ? a.num_m : 8;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 128, G2_BK, true);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tmB, W, N, K, ldw, G2_BN / 2, G2_BK, true);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_tn_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM);
+    if (e != cudaSuccess) return cuda_rc(e);
+    configured = true;
+  }
+  int tiles = a.num_m * a.num_n;
+  static int max_clusters = 0;
+  if (!max_clusters) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() & ~1);
+    cfg.blockDim = dim3(G2_THREADS);
+    cfg.dynamicSmemBytes = G2_SMEM;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_tn_kernel, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_clusters = n < sm_count() / 2 ? n : sm_count() / 2;
+  }
+  int clusters = max_clusters;
+  if (tiles < clusters) clusters = tiles;
+  gemm2_bf16_tn_kernel<<<clusters * 2, G2_THREADS, G2_SMEM, stream>>>(tmA, tmB, a);
+  return cuda_rc(cudaGetLastError());
+}

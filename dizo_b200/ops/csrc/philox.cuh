@@ -1,16 +1,21 @@
 // Counter-based Gaussian stream shared by every kernel that needs the perturbation z.
 //
 // z for element e of tensor t under seed s is a pure function of (s, t, e):
-//   words  = Philox4x32-10(counter = (e >> 3, t, stream, 0), key = (s_lo, s_hi))
-//   word j = words[(e & 7) >> 1]; u1 = word & 0xffff, u2 = word >> 16
-//   r = sqrt(-2 ln((u1 + 0.5) / 65536)),  phi = 2 pi (u2 + 0.5) / 65536 - pi
-//   z = r cos(phi) if e is even, r sin(phi) if e is odd
+//   words = Philox4x32-10(counter = (e >> 3, t, stream, 0), key = (s_lo, s_hi))
+//   word  = words[(e & 7) >> 1];  u = word & 0xffff for even e, word >> 16 for odd e
+//   z     = T[u],  T[i] = fp16( Phi^-1((i + 0.5) / 65536) )     (65536-entry inverse-CDF table)
 // so one Philox call yields the 8 normals of one 16-byte group of bf16 parameters, z is
-// never stored, and any sharding of a tensor (data-, tensor- or fully-sharded-parallel)
-// sees the same values.  The reference instead re-seeds torch's generator and
-// materialises z per tensor (large_models/trainer.py:1438-1444, :1603-1608).
+// never stored, any sharding of a tensor (data-, tensor- or fully-sharded-parallel) sees
+// the same values, and the host oracle (same table, same integers) reproduces z bit for bit.
+// The table (128 KB) is built once on the host and staged into shared memory by the sweep
+// kernel; a lookup replaces the log / sqrt / sin / cos of a Box-Muller transform, which made
+// the sweep instruction-bound at half the HBM rate.  The reference instead re-seeds torch's
+// generator and materialises z per tensor (large_models/trainer.py:1438-1444, :1603-1608).
 #pragma once
 #include <stdint.h>
+#ifdef __CUDACC__
+#include <cuda_fp16.h>
+#endif
 
 namespace dz {
 
@@ -47,28 +52,18 @@ __host__ __device__ __forceinline__ Philox4 philox4x32(uint32_t c0, uint32_t c1,
 }
 
 #ifdef __CUDACC__
-// Two normals from one 32-bit word (Box-Muller on two 16-bit uniforms).
-__device__ __forceinline__ void gauss_pair(uint32_t word, float& z0, float& z1) {
-  const float u1 = (static_cast<float>(word & 0xffffu) + 0.5f) * (1.0f / 65536.0f);
-  const float u2 = static_cast<float>(word >> 16) + 0.5f;
-  // -2 ln(u1) = -2 ln2 * log2(u1)
-  const float r = sqrtf(-1.3862943611198906f * __log2f(u1));
-  const float phi = u2 * (6.283185307179586f / 65536.0f) - 3.141592653589793f;
-  float s, c;
-  __sincosf(phi, &s, &c);
-  z0 = r * c;
-  z1 = r * s;
-}
+constexpr int GAUSS_TABLE_SIZE = 65536;
 
-// The 8 normals of group `grp` (= element index >> 3) of tensor `tid`.
-__device__ __forceinline__ void gauss8(uint64_t seed, uint32_t tid, uint32_t grp, uint32_t stream,
-                                       float z[8]) {
+// The 8 normals of group `grp` (= element index >> 3) of tensor `tid`; `tab` may point to
+// shared or global memory.
+__device__ __forceinline__ void gauss8(const __half* tab, uint64_t seed, uint32_t tid, uint32_t grp,
+                                       uint32_t stream, float z[8]) {
   Philox4 p = philox4x32<10>(grp, tid, stream, 0u, static_cast<uint32_t>(seed),
                              static_cast<uint32_t>(seed >> 32));
-  gauss_pair(p.x, z[0], z[1]);
-  gauss_pair(p.y, z[2], z[3]);
-  gauss_pair(p.z, z[4], z[5]);
-  gauss_pair(p.w, z[6], z[7]);
+  z[0] = __half2float(tab[p.x & 0xffffu]); z[1] = __half2float(tab[p.x >> 16]);
+  z[2] = __half2float(tab[p.y & 0xffffu]); z[3] = __half2float(tab[p.y >> 16]);
+  z[4] = __half2float(tab[p.z & 0xffffu]); z[5] = __half2float(tab[p.z >> 16]);
+  z[6] = __half2float(tab[p.w & 0xffffu]); z[7] = __half2float(tab[p.w >> 16]);
 }
 #endif
 

@@ -29,7 +29,9 @@
 namespace dz {
 
 constexpr int ZO_CHUNK = 256;    // elements; tensor starts are aligned to this (one warp pass)
-constexpr int ZO_THREADS = 256;  // 8 warps = 8 consecutive chunks per block iteration
+constexpr int ZO_THREADS = 768;  // one persistent CTA (24 warps) per SM
+constexpr int ZO_UNROLL = 4;     // 16-byte loads in flight per lane
+constexpr int ZO_SMEM = 65536 * 2; // the fp16 inverse-CDF table
 
 struct ZoTensor {
   long long offset;         // first element in the arena
@@ -69,6 +71,7 @@ struct ZoSweepArgs {
   const float* alpha;           // [slots] blend ratios
   float* chunk_sq;              // norm partials: [sq_base + chunk inside the piece]
   unsigned long long sr_seed;   // stochastic rounding stream
+  const __half* gauss_table;    // [65536] fp16 inverse normal CDF (global memory)
 };
 
 __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, long long pos) {
@@ -80,16 +83,107 @@ __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, 
   return lo;
 }
 
+// One 256-element chunk: lane l owns elements [8l, 8l+8).  `raw` was loaded by the caller.
 template <bool Z2, bool BLEND, bool NORM, bool SR>
-__global__ void __launch_bounds__(ZO_THREADS)
+__device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t, float alpha,
+                                         long long cpos, int lane, const uint4 raw,
+                                         const __half* tab, float c1, float c2) {
+  const long long e0 = cpos - t.offset + lane * 8;  // element inside this piece
+  float sq = 0.f;
+  if (e0 < t.numel) {
+    const long long pos = cpos + lane * 8;
+    float v[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
+                  bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
+    float an[8];
+    const bool slotted = (BLEND || NORM) && t.slot >= 0;
+    if (slotted) {
+      uint4 ar = *reinterpret_cast<const uint4*>(a.anchor + t.anchor_offset + e0);
+      an[0] = bf16_lo(ar.x); an[1] = bf16_hi(ar.x); an[2] = bf16_lo(ar.y); an[3] = bf16_hi(ar.y);
+      an[4] = bf16_lo(ar.z); an[5] = bf16_hi(ar.z); an[6] = bf16_lo(ar.w); an[7] = bf16_hi(ar.w);
+    }
+    if (BLEND && slotted) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = fmaf(alpha, v[j] - an[j], an[j]);
+    }
+    const uint32_t grp = zo_group(t, e0);
+    if (c1 != 0.f) {
+      float z[8];
+      gauss8(tab, a.seed1, t.tensor_id, grp, 0u, z);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = fmaf(c1, z[j], v[j]);
+    }
+    if (Z2) {
+      float z[8];
+      gauss8(tab, a.seed2, t.tensor_id, grp, 0u, z);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = fmaf(c2, z[j], v[j]);
+    }
+    uint32_t o[4];
+    if (SR) {
+      // stochastic rounding: add 16 random bits below the bf16 mantissa, truncate
+      Philox4 rb = philox4x32<10>(grp, t.tensor_id, 1u, 0u, static_cast<uint32_t>(a.sr_seed),
+                                  static_cast<uint32_t>(a.sr_seed >> 32));
+      uint32_t rw[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t lo = __float_as_uint(v[2 * j]) + (rw[j] & 0xffffu);
+        uint32_t hi = __float_as_uint(v[2 * j + 1]) + (rw[j] >> 16);
+        o[j] = (lo >> 16) | (hi & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    }
+    if (e0 + 8 > t.numel) {
+      // ragged tail of a tensor: keep the padding elements as they were
+      const uint32_t rawv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (e0 + j >= t.numel) {
+          uint32_t keep = (j & 1) ? (rawv[j >> 1] & 0xffff0000u) : (rawv[j >> 1] & 0xffffu);
+          o[j >> 1] = (j & 1) ? ((o[j >> 1] & 0xffffu) | keep) : ((o[j >> 1] & 0xffff0000u) | keep);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(a.dst + (pos - a.dst_shift)) = make_uint4(o[0], o[1], o[2], o[3]);
+    if (NORM && slotted) {
+      // norm of what was stored (the bf16 values), so it equals a later re-read
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (e0 + j < t.numel) {
+          float w = (j & 1) ? bf16_hi(o[j >> 1]) : bf16_lo(o[j >> 1]);
+          float d = w - an[j];
+          sq = fmaf(d, d, sq);
+        }
+      }
+    }
+  }
+  if (NORM) {
+    // fixed-order warp reduction -> one partial per chunk (deterministic)
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+    if (lane == 0 && t.sq_base >= 0) a.chunk_sq[t.sq_base + (cpos - t.offset) / ZO_CHUNK] = sq;
+  }
+}
+
+// Persistent: one CTA of 32 warps per SM.  The inverse-CDF table sits in shared memory;
+// every warp owns a contiguous run of chunks and keeps ZO_UNROLL 16-byte loads per lane in
+// flight (64 KB per SM), which is what it takes to cover HBM latency at full bandwidth.
+template <bool Z2, bool BLEND, bool NORM, bool SR>
+__global__ void __launch_bounds__(ZO_THREADS, 1)
 zo_sweep_kernel(const ZoSweepArgs a) {
+  extern __shared__ __align__(16) uint8_t zo_smem[];
+  __half* tab = reinterpret_cast<__half*>(zo_smem);
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(a.gauss_table);
+    uint4* dst = reinterpret_cast<uint4*>(zo_smem);
+    for (int i = threadIdx.x; i < GAUSS_TABLE_SIZE * 2 / 16; i += ZO_THREADS) dst[i] = __ldg(src + i);
+  }
+  __syncthreads();
   float c1 = a.c1, c2 = a.c2;
   if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
   if (Z2 && a.c2_ptr) c2 *= __ldg(a.c2_ptr);
 
-  // Every warp owns a contiguous run of chunks, so the tensor descriptor is re-read only
-  // when the run crosses into the next tensor, and the next chunk's load is in flight while
-  // the current one is being transformed.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int WARPS = ZO_THREADS / 32;
   const long long total = a.chunk_end - a.chunk_begin;
@@ -105,112 +199,33 @@ zo_sweep_kernel(const ZoSweepArgs a) {
   float alpha = 1.f;
   if (BLEND && t.slot >= 0) alpha = __ldg(a.alpha + t.slot);
 
-  uint4 raw = make_uint4(0, 0, 0, 0);
-  {
+  while (chunk < chunk_stop) {
     const long long cpos = chunk * ZO_CHUNK;
-    if (cpos - t.offset + lane * 8 < t.numel) raw = *reinterpret_cast<const uint4*>(a.src + cpos + lane * 8);
-  }
-  for (; chunk < chunk_stop; ++chunk) {
-    const long long cpos = chunk * ZO_CHUNK;
-    const long long e0 = cpos - t.offset + lane * 8;  // element inside this piece
-    const bool active = e0 < t.numel;
-    const uint4 cur_raw = raw;
-    // ---- prefetch the next chunk (possibly of the next tensor)
-    const long long npos = cpos + ZO_CHUNK;
-    ZoTensor tn = t;
-    int ncur = cur;
-    long long tn_next = t_next;
-    bool have_next = chunk + 1 < chunk_stop;
-    if (have_next) {
-      if (npos >= t_next) {
-        ncur = cur + 1;
-        while (ncur + 1 < a.t_end && a.table[ncur + 1].offset <= npos) ++ncur;
-        tn = a.table[ncur];
-        tn_next = (ncur + 1 < a.t_end) ? a.table[ncur + 1].offset : (1ll << 62);
-      }
-      if (npos - tn.offset + lane * 8 < tn.numel)
-        raw = *reinterpret_cast<const uint4*>(a.src + npos + lane * 8);
-    }
-    float sq = 0.f;
-    if (active) {
-      const long long pos = cpos + lane * 8;
-      float v[8] = {bf16_lo(cur_raw.x), bf16_hi(cur_raw.x), bf16_lo(cur_raw.y), bf16_hi(cur_raw.y),
-                    bf16_lo(cur_raw.z), bf16_hi(cur_raw.z), bf16_lo(cur_raw.w), bf16_hi(cur_raw.w)};
-      float an[8];
-      const bool slotted = (BLEND || NORM) && t.slot >= 0;
-      if (slotted) {
-        uint4 ar = *reinterpret_cast<const uint4*>(a.anchor + t.anchor_offset + e0);
-        an[0] = bf16_lo(ar.x); an[1] = bf16_hi(ar.x); an[2] = bf16_lo(ar.y); an[3] = bf16_hi(ar.y);
-        an[4] = bf16_lo(ar.z); an[5] = bf16_hi(ar.z); an[6] = bf16_lo(ar.w); an[7] = bf16_hi(ar.w);
-      }
-      if (BLEND && slotted) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = fmaf(alpha, v[j] - an[j], an[j]);
-      }
-      const uint32_t grp = zo_group(t, e0);
-      if (c1 != 0.f) {
-        float z[8];
-        gauss8(a.seed1, t.tensor_id, grp, 0u, z);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = fmaf(c1, z[j], v[j]);
-      }
-      if (Z2) {
-        float z[8];
-        gauss8(a.seed2, t.tensor_id, grp, 0u, z);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = fmaf(c2, z[j], v[j]);
-      }
-      uint32_t o[4];
-      if (SR) {
-        // stochastic rounding: add 16 random bits below the bf16 mantissa, truncate
-        Philox4 rb = philox4x32<10>(grp, t.tensor_id, 1u, 0u, static_cast<uint32_t>(a.sr_seed),
-                                    static_cast<uint32_t>(a.sr_seed >> 32));
-        uint32_t rw[4] = {rb.x, rb.y, rb.z, rb.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t lo = __float_as_uint(v[2 * j]) + (rw[j] & 0xffffu);
-          uint32_t hi = __float_as_uint(v[2 * j + 1]) + (rw[j] >> 16);
-          o[j] = (lo >> 16) | (hi & 0xffff0000u);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
-      }
-      if (e0 + 8 > t.numel) {
-        // ragged tail of a tensor: keep the padding elements as they were
-        const uint32_t rawv[4] = {cur_raw.x, cur_raw.y, cur_raw.z, cur_raw.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (e0 + j >= t.numel) {
-            uint32_t keep = (j & 1) ? (rawv[j >> 1] & 0xffff0000u) : (rawv[j >> 1] & 0xffffu);
-            o[j >> 1] = (j & 1) ? ((o[j >> 1] & 0xffffu) | keep) : ((o[j >> 1] & 0xffff0000u) | keep);
-          }
-        }
-      }
-      *reinterpret_cast<uint4*>(a.dst + (pos - a.dst_shift)) = make_uint4(o[0], o[1], o[2], o[3]);
-      if (NORM && slotted) {
-        // norm of what was stored (the bf16 values), so it equals a later re-read
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (e0 + j < t.numel) {
-            float w = (j & 1) ? bf16_hi(o[j >> 1]) : bf16_lo(o[j >> 1]);
-            float d = w - an[j];
-            sq = fmaf(d, d, sq);
-          }
-        }
-      }
-    }
-    if (NORM) {
-      // fixed-order warp reduction -> one partial per chunk (deterministic)
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-      if (lane == 0 && t.sq_base >= 0) a.chunk_sq[t.sq_base + (cpos - t.offset) / ZO_CHUNK] = sq;
-    }
-    if (have_next && ncur != cur) {
-      cur = ncur;
-      t = tn;
-      t_next = tn_next;
+    if (cpos >= t_next) {
+      ++cur;
+      while (cur + 1 < a.t_end && a.table[cur + 1].offset <= cpos) ++cur;
+      t = a.table[cur];
+      t_next = (cur + 1 < a.t_end) ? a.table[cur + 1].offset : (1ll << 62);
       if (BLEND && t.slot >= 0) alpha = __ldg(a.alpha + t.slot);
+    }
+    const long long in_tensor = (min(t_next, t.offset + ((t.numel + ZO_CHUNK - 1) / ZO_CHUNK) * ZO_CHUNK) - cpos) / ZO_CHUNK;
+    if (chunk + ZO_UNROLL <= chunk_stop && in_tensor >= ZO_UNROLL &&
+        cpos - t.offset + ZO_UNROLL * ZO_CHUNK <= t.numel) {
+      // fast path: ZO_UNROLL full chunks of the same tensor, all loads issued first
+      uint4 raw[ZO_UNROLL];
+#pragma unroll
+      for (int u = 0; u < ZO_UNROLL; ++u)
+        raw[u] = *reinterpret_cast<const uint4*>(a.src + cpos + u * ZO_CHUNK + lane * 8);
+#pragma unroll
+      for (int u = 0; u < ZO_UNROLL; ++u)
+        zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos + u * ZO_CHUNK, lane, raw[u], tab, c1, c2);
+      chunk += ZO_UNROLL;
+    } else {
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (cpos - t.offset + lane * 8 < t.numel)
+        raw = *reinterpret_cast<const uint4*>(a.src + cpos + lane * 8);
+      zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos, lane, raw, tab, c1, c2);
+      chunk += 1;
     }
   }
 }
@@ -245,7 +260,8 @@ __global__ void zo_reduce_chunks_kernel(const ZoTensor* table, int num_tensors,
 __global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, float* gamma,
                                   float* zbuf, float* alpha, unsigned long long seed, int iter,
                                   float delta, float tau, float eps, float step_size,
-                                  const float* loss1, const float* loss2, int reinit) {
+                                  const float* loss1, const float* loss2, int reinit,
+                                  const __half* gauss_table) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float t;
@@ -262,8 +278,7 @@ __global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, f
     if (delta == 1.0f && iter >= 0) {
       Philox4 p = philox4x32<10>(static_cast<uint32_t>(i), static_cast<uint32_t>(iter), 2u, 0u,
                                  static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-      float z0, z1;
-      gauss_pair(p.x, z0, z1);
+      float z0 = __half2float(gauss_table[p.x & 0xffffu]);
       float lim = (tau / eps) * t;
       z = fminf(fmaxf(z0, -lim), lim);
       zbuf[i] = z;
@@ -289,10 +304,16 @@ template <bool Z2, bool BLEND, bool NORM, bool SR>
 static int launch_sweep(const ZoSweepArgs& a, cudaStream_t stream) {
   long long chunks = a.chunk_end - a.chunk_begin;
   if (chunks <= 0) return DZ_OK;
+  auto kern = zo_sweep_kernel<Z2, BLEND, NORM, SR>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ZO_SMEM);
+    if (e != cudaSuccess) return cuda_rc(e);
+    configured = true;
+  }
   long long blocks = (chunks + ZO_THREADS / 32 - 1) / (ZO_THREADS / 32);
-  long long max_grid = (long long)sm_count() * 8;
-  int grid = (int)(blocks < max_grid ? blocks : max_grid);
-  zo_sweep_kernel<Z2, BLEND, NORM, SR><<<grid, ZO_THREADS, 0, stream>>>(a);
+  int grid = (int)(blocks < sm_count() ? blocks : sm_count());
+  kern<<<grid, ZO_THREADS, ZO_SMEM, stream>>>(a);
   return cuda_rc(cudaGetLastError());
 }
 
@@ -311,8 +332,10 @@ extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, cons
                            long long chunk_end, unsigned long long seed1, float c1,
                            const float* c1_ptr, unsigned long long seed2, float c2,
                            const float* c2_ptr, const float* alpha, float* chunk_sq,
-                           unsigned long long sr_seed, int flags, cudaStream_t stream) {
-  if (!src || !dst || !table || t_end <= t_begin) return DZ_ERR_ARG;
+                           unsigned long long sr_seed, int flags, const void* gauss_table,
+                           cudaStream_t stream) {
+  if (!src || !dst || !table || !gauss_table || t_end <= t_begin) return DZ_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(gauss_table) & 15) return DZ_ERR_ALIGN;
   const bool z2 = flags & 1, blend = flags & 2, norm = flags & 4, sr = flags & 8;
   if ((blend || norm) && !anchor) return DZ_ERR_ARG;
   if (blend && !alpha) return DZ_ERR_ARG;
@@ -323,6 +346,7 @@ extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, cons
   a.t_begin = t_begin; a.t_end = t_end; a.chunk_begin = chunk_begin; a.chunk_end = chunk_end;
   a.seed1 = seed1; a.seed2 = seed2; a.c1 = c1; a.c2 = c2; a.c1_ptr = c1_ptr; a.c2_ptr = c2_ptr;
   a.alpha = alpha; a.chunk_sq = chunk_sq; a.sr_seed = sr_seed;
+  a.gauss_table = (const __half*)gauss_table;
   int key = (z2 ? 1 : 0) | (blend ? 2 : 0) | (norm ? 4 : 0) | (sr ? 8 : 0);
   switch (key) {
 #define DZ_CASE(K, A, B, C, D) case K: return launch_sweep<A, B, C, D>(a, stream);
@@ -350,11 +374,11 @@ extern "C" int dz_zo_reduce_chunks(const void* table, int num_tensors, const flo
 extern "C" int dz_gamma_step(int n, int mode, const float* sq, float* ts, float* gamma, float* zbuf,
                              float* alpha, unsigned long long seed, int iter, float delta, float tau,
                              float eps, float step_size, const float* loss1, const float* loss2,
-                             int reinit, cudaStream_t stream) {
-  if (n <= 0 || !ts || !gamma || !zbuf || !alpha) return DZ_ERR_ARG;
+                             int reinit, const void* gauss_table, cudaStream_t stream) {
+  if (n <= 0 || !ts || !gamma || !zbuf || !alpha || !gauss_table) return DZ_ERR_ARG;
   gamma_step_kernel<<<(n + 127) / 128, 128, 0, stream>>>(n, mode, sq, ts, gamma, zbuf, alpha, seed,
                                                          iter, delta, tau, eps, step_size, loss1,
-                                                         loss2, reinit);
+                                                         loss2, reinit, (const __half*)gauss_table);
   return cuda_rc(cudaGetLastError());
 }
 
@@ -367,19 +391,20 @@ extern "C" int dz_scalar_diff(const float* a, const float* b, float scale, float
 
 // z itself (fp32), for tests and for the CPU oracle that consumes the framework's stream.
 __global__ void zo_fill_z_kernel(float* out, long long numel, long long elem_base,
-                                 unsigned long long seed, int tensor_id) {
+                                 unsigned long long seed, int tensor_id, const __half* tab) {
   long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long e0 = g * 8;
   if (e0 >= numel) return;
   float z[8];
-  gauss8(seed, tensor_id, (uint32_t)((elem_base + e0) >> 3), 0u, z);
+  gauss8(tab, seed, tensor_id, (uint32_t)((elem_base + e0) >> 3), 0u, z);
   for (int j = 0; j < 8 && e0 + j < numel; ++j) out[e0 + j] = z[j];
 }
 extern "C" int dz_zo_fill_z(float* out, long long numel, long long elem_base,
-                            unsigned long long seed, int tensor_id, cudaStream_t stream) {
-  if (!out || numel <= 0 || (elem_base & 7)) return DZ_ERR_ARG;
+                            unsigned long long seed, int tensor_id, const void* gauss_table,
+                            cudaStream_t stream) {
+  if (!out || !gauss_table || numel <= 0 || (elem_base & 7)) return DZ_ERR_ARG;
   long long groups = (numel + 7) / 8;
   zo_fill_z_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(out, numel, elem_base, seed,
-                                                                        tensor_id);
+                                                                        tensor_id, (const __half*)gauss_table);
   return cuda_rc(cudaGetLastError());
 }

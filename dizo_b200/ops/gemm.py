@@ -8,6 +8,7 @@ Replaces the ``nn.Linear`` calls of the reference's OPT blocks
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.nn.functional as F
@@ -15,6 +16,8 @@ import torch.nn.functional as F
 from . import _lib
 
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
+# 0 = choose per shape, 1 = one-SM kernel, 2 = two-SM (cta_group::2) kernel
+_VARIANT = int(os.environ.get("DIZO_GEMM_VARIANT", "0"))
 
 
 def linear_reference(x, w, bias=None, act=None, residual=None, scale: float = 1.0,
@@ -38,7 +41,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
            residual: torch.Tensor | None = None, scale: float = 1.0,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
            tile_n: int = 0) -> torch.Tensor:
-    """x [..., K] (bf16), w [N, K] (bf16) -> [..., N] in ``out_dtype`` (bf16 or fp32)."""
+    """x [..., K] (bf16), w [N, K] (bf16) -> [..., N] in ``out_dtype`` (bf16 or fp32).
+
+    ``tile_n``: 0 = choose, 128 / 256 = one-SM kernel with that tile width, 512 = two-SM kernel."""
     if not x.is_cuda:
         y = linear_reference(x, w, bias, act, residual, scale, out_dtype)
         if out is not None:
@@ -64,6 +69,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, a
         assert res2.dtype == torch.bfloat16 and res2.stride(-1) == 1
     assert w.stride(-1) == 1 and out2.stride(-1) == 1
     if M == 0:
+        return out.reshape(*x.shape[:-1], N)
+    variant = _VARIANT
+    if tile_n == 512:
+        variant, tile_n = 2, 0
+    elif tile_n in (128, 256):
+        variant = 1
+    if variant == 0:
+        # pairs of SMs (256 x 256 tiles) once there is work for most of them
+        variant = 2 if (M >= 256 and ((M + 255) // 256) * ((N + 255) // 256) >= 48) else 1
+    if variant == 2:
+        rc = _lib.lib().dz_gemm2_bf16_tn(
+            _lib.ptr(x2), ctypes.c_longlong(x2.stride(0)), _lib.ptr(w), ctypes.c_longlong(w.stride(0)),
+            _lib.ptr(out2), ctypes.c_longlong(out2.stride(0)), _lib.ptr(bias), _lib.ptr(res2),
+            ctypes.c_longlong(res2.stride(0) if res2 is not None else 0),
+            M, N, K, ACT[act], int(out_dtype == torch.float32), ctypes.c_float(scale),
+            _lib.ptr(_lib.err_word(x.device)), _lib.stream_ptr())
+        _lib.check(rc, "dz_gemm2_bf16_tn")
         return out.reshape(*x.shape[:-1], N)
     rc = _lib.lib().dz_gemm_bf16_tn(
         _lib.ptr(x2), ctypes.c_longlong(x2.stride(0)), _lib.ptr(w), ctypes.c_longlong(w.stride(0)),

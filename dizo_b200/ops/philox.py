@@ -4,11 +4,12 @@
 element index ``e`` inside the *full* tensor:
 
     words = Philox4x32-10(counter=(e >> 3, tensor_id, stream, 0), key=(seed_lo, seed_hi))
-    w     = words[(e & 7) >> 1];  u1 = w & 0xffff;  u2 = w >> 16
-    r     = sqrt(-2 ln((u1 + .5) / 65536));  phi = 2 pi (u2 + .5) / 65536 - pi
-    z     = r cos(phi) for even e, r sin(phi) for odd e
+    w     = words[(e & 7) >> 1];  u = w & 0xffff for even e, w >> 16 for odd e
+    z     = T[u],   T[i] = float16(Phi^-1((i + 0.5) / 65536))
 
-The reference instead calls ``torch.manual_seed(seed)`` and ``torch.normal`` per tensor
+``T`` (:func:`gauss_table`) is the same 65536-entry inverse-normal-CDF table the CUDA kernels
+stage into shared memory, so the host stream equals the device stream bit for bit.  The
+reference instead calls ``torch.manual_seed(seed)`` and ``torch.normal`` per tensor
 (large_models/trainer.py:1438-1444); bit-matching that generator is not a goal.
 """
 from __future__ import annotations
@@ -48,16 +49,26 @@ def philox4x32(c0, c1, c2, c3, k0, k1, rounds: int = 10):
     return c0, c1, c2, c3
 
 
+_TABLE = None
+
+
+def gauss_table() -> np.ndarray:
+    """float16[65536]: T[i] = Phi^-1((i + 0.5) / 65536), computed in float64."""
+    global _TABLE
+    if _TABLE is None:
+        from scipy.special import ndtri
+        u = (np.arange(65536, dtype=np.float64) + 0.5) / 65536.0
+        _TABLE = ndtri(u).astype(np.float16)
+    return _TABLE
+
+
 def gauss_words(words: np.ndarray) -> np.ndarray:
-    """[..., 4] uint32 -> [..., 8] float32 normals (pair per word)."""
+    """[..., 4] uint32 -> [..., 8] float32 normals (two table look-ups per word)."""
     w = words.astype(np.uint32)
-    u1 = ((w & np.uint32(0xFFFF)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 65536.0)
-    u2 = (w >> np.uint32(16)).astype(np.float32) + np.float32(0.5)
-    r = np.sqrt(np.float32(-1.3862943611198906) * np.log2(u1)).astype(np.float32)
-    phi = u2 * np.float32(6.283185307179586 / 65536.0) - np.float32(3.141592653589793)
+    tab = gauss_table()
     out = np.empty(w.shape[:-1] + (8,), dtype=np.float32)
-    out[..., 0::2] = r * np.cos(phi)
-    out[..., 1::2] = r * np.sin(phi)
+    out[..., 0::2] = tab[w & np.uint32(0xFFFF)].astype(np.float32)
+    out[..., 1::2] = tab[w >> np.uint32(16)].astype(np.float32)
     return out
 
 

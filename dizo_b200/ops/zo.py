@@ -46,6 +46,20 @@ class Piece:
         return int(math.prod(self.shape))
 
 
+_tables: dict = {}
+
+
+def gauss_table_dev(device) -> torch.Tensor:
+    """The fp16 inverse-CDF table on ``device`` (uploaded once per device)."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index)
+    t = _tables.get(key)
+    if t is None:
+        t = torch.from_numpy(philox.gauss_table().copy()).to(dev)
+        _tables[key] = t
+    return t
+
+
 def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
@@ -214,7 +228,7 @@ class ParamArena:
             ctypes.c_float(c1), _lib.ptr(c1_dev), ctypes.c_uint64(seed2 & (2 ** 64 - 1)),
             ctypes.c_float(c2 if use_z2 else 0.0), _lib.ptr(c2_dev), _lib.ptr(alpha),
             _lib.ptr(self._chunk_sq), ctypes.c_uint64((stochastic_round_seed or 0) & (2 ** 64 - 1)),
-            flags, _lib.stream_ptr())
+            flags, _lib.ptr(gauss_table_dev(self.device)), _lib.stream_ptr())
         _lib.check(rc, "dz_zo_sweep")
         if norm:
             rc = L.dz_zo_reduce_chunks(
@@ -295,7 +309,7 @@ class GammaState:
                 _lib.ptr(self.z), _lib.ptr(self.alpha), ctypes.c_uint64(seed & (2 ** 64 - 1)), it,
                 ctypes.c_float(delta), ctypes.c_float(self.tau), ctypes.c_float(self.zo_eps),
                 ctypes.c_float(self.step_size), _lib.ptr(loss1), _lib.ptr(loss2), reinit,
-                _lib.stream_ptr())
+                _lib.ptr(gauss_table_dev(self.device)), _lib.stream_ptr())
             _lib.check(rc, "dz_gamma_step")
             return
         if mode == 0:
@@ -346,6 +360,7 @@ def fill_z(numel: int, seed: int, tensor_id: int, device, elem_base: int = 0) ->
         return torch.from_numpy(philox.gaussian(seed, tensor_id, numel, elem_base))
     out = torch.empty(numel, dtype=torch.float32, device=dev)
     rc = _lib.lib().dz_zo_fill_z(_lib.ptr(out), ctypes.c_longlong(numel), ctypes.c_longlong(elem_base),
-                                 ctypes.c_uint64(seed & (2 ** 64 - 1)), tensor_id, _lib.stream_ptr())
+                                 ctypes.c_uint64(seed & (2 ** 64 - 1)), tensor_id,
+                                 _lib.ptr(gauss_table_dev(dev)), _lib.stream_ptr())
     _lib.check(rc, "dz_zo_fill_z")
     return out

@@ -1,0 +1,50 @@
+"""Host-side failure detection: heartbeats through the rendezvous store.
+
+Each rank writes ``(step, wall time)`` under its own key after every step and, before it
+launches the next one, reads its peers' keys; a peer whose heartbeat is older than
+``stale_after`` seconds (or that is more than ``max_lag`` steps behind) raises
+:class:`PeerLost` on the host, before any kernel or collective that would wait for that peer is
+launched.  The reference has no failure detection at all (its only signal handling is the
+SIGUSR1 callback, large_models/utils.py:291-315).
+"""
+from __future__ import annotations
+
+import time
+
+
+class PeerLost(RuntimeError):
+    pass
+
+
+class Heartbeat:
+    def __init__(self, store, rank: int, world: int, stale_after: float = 60.0, max_lag: int | None = None,
+                 prefix: str = "dizo_hb"):
+        self.store, self.rank, self.world = store, rank, world
+        self.stale_after, self.max_lag, self.prefix = stale_after, max_lag, prefix
+
+    def _key(self, r: int) -> str:
+        return f"{self.prefix}/{r}"
+
+    def beat(self, step: int) -> None:
+        self.store.set(self._key(self.rank), f"{step}:{time.time():.3f}")
+
+    def peers(self) -> dict[int, tuple[int, float]]:
+        out = {}
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            try:
+                raw = self.store.get(self._key(r)).decode()
+                s, t = raw.split(":")
+                out[r] = (int(s), float(t))
+            except Exception:
+                out[r] = (-1, 0.0)
+        return out
+
+    def check(self, step: int) -> None:
+        now = time.time()
+        for r, (s, t) in self.peers().items():
+            if now - t > self.stale_after:
+                raise PeerLost(f"rank {r} has not reported for {now - t:.1f}s (last step {s})")
+            if self.max_lag is not None and step - s > self.max_lag:
+                raise PeerLost(f"rank {r} is {step - s} steps behind")

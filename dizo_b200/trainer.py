@@ -116,6 +116,7 @@ class OurTrainer:
         self.base_model = None
         self._train_iter = None
         self._pgm_iter = None
+        self._pgm_count = 0          # batches the gamma search has consumed (saved for resume)
         self._phase_ms: Dict[str, float] = {}
         self._metrics_f = None
         self._rank = dist.get_rank(dp_group) if (dist.is_available() and dist.is_initialized()) else 0
@@ -304,7 +305,8 @@ class OurTrainer:
         """The gamma search consumes batches from its OWN iterator over the training loader
         (large_models/trainer.py:762-763, :790-796)."""
         if self._pgm_iter is None:
-            self._pgm_iter = self._batches(salt=1)
+            self._pgm_iter = self._batches(salt=1, skip_steps=self._pgm_count)
+        self._pgm_count += 1
         return self._to_batch(next(self._pgm_iter)[3])
 
     # ------------------------------------------------------------------ evaluation inside the loop

@@ -126,6 +126,7 @@ def save_checkpoint(out: str, model, trainer=None) -> None:
         if trainer.dizo_trainer is not None:
             zo["dizo"] = trainer.dizo_trainer.projector.state_dict()
             zo["dizo_i"] = trainer.dizo_trainer.i
+            zo["pgm_count"] = trainer._pgm_count
             zo["dizo_seed_rng"] = trainer._dizo_seed_rng.get_state()
             ar = model.arena
             zo["anchor"] = {n: ar.anchor_view(n).detach().cpu().clone() for n in ar.slot_names}
@@ -155,6 +156,8 @@ def load_checkpoint(path: str, model, trainer=None, verify: bool = True) -> None
         if "dizo" in zo and trainer.dizo_trainer is not None:
             trainer.dizo_trainer.projector.load_state_dict(zo["dizo"])
             trainer.dizo_trainer.i = zo.get("dizo_i", 0)
+            trainer._pgm_count = zo.get("pgm_count", 0)
+            trainer._pgm_iter = None
             trainer._dizo_seed_rng.set_state(zo["dizo_seed_rng"])
             ar = model.arena
             for n, t in zo.get("anchor", {}).items():

@@ -20,6 +20,12 @@ def _rel_err(a, b):
     (77, 200, 72, 128),
     (1000, 2560, 2560, 0),
     (4096, 7680, 2560, 0),
+    (256, 256, 64, 512),       # two-SM kernel from here on
+    (512, 768, 512, 512),
+    (300, 776, 328, 512),
+    (77, 200, 72, 512),
+    (4096, 7680, 2560, 512),
+    (1000, 2560, 10240, 512),
 ])
 def test_gemm_plain(M, N, K, tile_n):
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
@@ -36,7 +42,8 @@ def test_gemm_plain(M, N, K, tile_n):
 
 @pytest.mark.parametrize("act", [None, "relu", "gelu"])
 @pytest.mark.parametrize("fp32_out", [False, True])
-def test_gemm_epilogues(act, fp32_out):
+@pytest.mark.parametrize("tile_n", [0, 512])
+def test_gemm_epilogues(act, fp32_out, tile_n):
     M, N, K = 517, 1032, 520
     g = torch.Generator(device="cuda").manual_seed(5)
     x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
@@ -44,7 +51,7 @@ def test_gemm_epilogues(act, fp32_out):
     b = torch.randn(N, device="cuda", generator=g).bfloat16()
     r = torch.randn(M, N, device="cuda", generator=g).bfloat16()
     od = torch.float32 if fp32_out else torch.bfloat16
-    y = linear(x, w, b, act=act, residual=r, scale=0.5, out_dtype=od)
+    y = linear(x, w, b, act=act, residual=r, scale=0.5, out_dtype=od, tile_n=tile_n)
     torch.cuda.synchronize()
     _lib.check_device_errors()
     ref = linear_reference(x, w, b, act=act, residual=r, scale=0.5, out_dtype=torch.float32)
@@ -56,6 +63,7 @@ def test_gemm_deterministic():
     g = torch.Generator(device="cuda").manual_seed(11)
     x = torch.randn(640, 1024, device="cuda", generator=g).bfloat16()
     w = torch.randn(768, 1024, device="cuda", generator=g).bfloat16()
-    a = linear(x, w)
-    b = linear(x, w)
-    assert torch.equal(a, b)
+    for tn in (256, 512):
+        a = linear(x, w, tile_n=tn)
+        b = linear(x, w, tile_n=tn)
+        assert torch.equal(a, b)

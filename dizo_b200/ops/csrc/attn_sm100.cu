@@ -15,18 +15,20 @@
 //   warps 4-7 : softmax for tile 1
 //   warp 8    : TMEM allocation; lane 0 issues tcgen05.mma
 //   warp 9    : lane 0 = TMA producer (Q once, then the K and V rings)
-// Per 64-key block: S_t = Q_t K^T (TMEM) -> softmax threads read S with tcgen05.ld, write
-// P (bf16) into shared memory in the K-major 128B-swizzled operand layout -> O_t += P V
-// accumulates in TMEM.  The running row maximum is only raised when it grows by more than
-// 2^8 (then O is rescaled in TMEM), so most blocks need no correction pass.  The two
-// tiles ping-pong: the tensor core works on one tile while the other does its exps.
+// Per 128-key block: S_t = Q_t K^T (TMEM) -> softmax threads read S with tcgen05.ld and write
+// P (bf16, two per 32-bit column) back into TMEM over the columns S occupied -> O_t += P V
+// with P as the TMEM A operand of tcgen05.mma, accumulating in TMEM.  P never touches shared
+// memory.  The running row maximum is only raised when it grows by more than 2^8 (then O is
+// rescaled in TMEM), so most blocks need no correction pass; blocks entirely below the
+// diagonal skip the mask arithmetic.  The two tiles ping-pong: the tensor core works on one
+// tile while the other does its exps.
 #include "common.cuh"
 #include "host_util.h"
 
 namespace dz {
 
 constexpr int A_BQ = 128;    // query rows per tile
-constexpr int A_BKV = 64;    // keys per block
+constexpr int A_BKV = 128;   // keys per block
 constexpr int A_THREADS = 320;
 constexpr int A_KV_STAGES = 2;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -46,12 +48,10 @@ template <int HDP>
 struct AttnSmem {
   static constexpr int Q_TILE = A_BQ * HDP * 2;     // per query tile
   static constexpr int KV_TILE = A_BKV * HDP * 2;   // per K or V stage
-  static constexpr int P_TILE = A_BQ * A_BKV * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + 2 * Q_TILE;
   static constexpr int OFF_V = OFF_K + A_KV_STAGES * KV_TILE;
-  static constexpr int OFF_P = OFF_V + A_KV_STAGES * KV_TILE;
-  static constexpr int USED = OFF_P + 2 * P_TILE + 1024;
+  static constexpr int USED = OFF_V + A_KV_STAGES * KV_TILE + 1024;
   // at least 120 KB so that two CTAs (each wanting all 512 TMEM columns) never share an SM
   static constexpr int TOTAL = USED < 120 * 1024 ? 120 * 1024 : USED;
 };
@@ -125,9 +125,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
-  // TMEM columns: S0 [0,64) S1 [64,128) O0 [128,128+HDP) O1 [256,256+HDP)
-  const uint32_t tm_s[2] = {tmem_base + 0u, tmem_base + 64u};
-  const uint32_t tm_o[2] = {tmem_base + 128u, tmem_base + 256u};
+  // TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O0 [256,256+HDP) O1 [384,384+HDP)
+  const uint32_t tm_s[2] = {tmem_base + 0u, tmem_base + 128u};
+  const uint32_t tm_o[2] = {tmem_base + 256u, tmem_base + 384u};
 
   if (warp == 9) {
     if (lane == 0 && nvb_max > 0) {
@@ -188,14 +188,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       auto issue_pv = [&](int t, int vb) {
         int st = vb % A_KV_STAGES;
-        uint32_t pa = smem_base + S::OFF_P + t * S::P_TILE;
         uint32_t va = smem_base + S::OFF_V + st * S::KV_TILE;
         for (int kk = 0; kk < A_BKV / 16; ++kk) {
-          uint64_t ad = umma_desc_k_sw128(pa + kk * 32);
-          // 16 keys = two 8-row groups of 1024 bytes; 64-column blocks of the head are
-          // A_BKV*128 bytes apart.
+          // A = P from TMEM: 16 keys = 8 packed 32-bit columns.  B = V, MN-major: 16 keys = two
+          // 8-row groups of 1024 bytes; 64-column blocks of the head are A_BKV*128 bytes apart.
           uint64_t bd = umma_desc_mn_sw128(va + kk * 2048, A_BKV * 128, 1024);
-          umma_bf16_ss(tm_o[t], ad, bd, idesc_o, (vb | kk) != 0);
+          umma_bf16_ts(tm_o[t], tm_s[t] + kk * 8, bd, idesc_o, (vb | kk) != 0);
         }
         umma_commit(smem_u32(&bar_pv[t]));
       };
@@ -243,33 +241,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
-    const uint32_t p_row = smem_base + S::OFF_P + t * S::P_TILE + (r >> 3) * 1024 + (r & 7) * 128;
 
     for (int vb = 0; vb < nvb[t] && ok; ++vb) {
       ok = mbar_wait(smem_u32(&bar_s[t]), vb & 1, &s_abort, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[64];
-      tmem_ld_32x32(tm_s[t] + lane_off, sv);
-      tmem_ld_32x32(tm_s[t] + lane_off + 32, sv + 32);
-      tmem_ld_wait();
-      // scale + mask, block maximum
-      float bmax = -INFINITY;
       const bool is_prefix = has_prefix && vb == 0;
       const int kv0 = (jb + vb - has_prefix) * A_BKV;
+      // blocks entirely below the diagonal and right of the padding need no mask (uniform)
+      const bool need_mask = is_prefix || !(kv0 + A_BKV - 1 <= q0[t] && kv0 >= pad);
+      auto visible = [&](int c) -> bool {
+        if (is_prefix) return c < p.n_prefix;
+        int kv = kv0 + c;
+        return (kv <= qi) && (kv >= pad || kv == qi) && (kv < p.L);
+      };
+      // ---- the whole score row of this block in registers: one TMEM round trip
+      uint32_t sv[A_BKV];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        bool vis;
-        if (is_prefix) {
-          vis = c < p.n_prefix;
-        } else {
-          int kv = kv0 + c;
-          vis = (kv <= qi) && (kv >= pad || kv == qi) && (kv < p.L);
+      for (int ch = 0; ch < A_BKV / 32; ++ch) tmem_ld_32x32(tm_s[t] + lane_off + ch * 32, sv + ch * 32);
+      tmem_ld_wait();
+      float bmax = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < A_BKV; ++c) {
+          if (!visible(c)) sv[c] = 0xff800000u;  // -inf
+          bmax = fmaxf(bmax, __uint_as_float(sv[c]));
         }
-        float x = vis ? __uint_as_float(sv[c]) * p.scale_log2 : -INFINITY;
-        sv[c] = __float_as_uint(x);
-        bmax = fmaxf(bmax, x);
+      } else {
+#pragma unroll
+        for (int c = 0; c < A_BKV; ++c) bmax = fmaxf(bmax, __uint_as_float(sv[c]));
       }
+      bmax *= p.scale_log2;       // scale > 0: max commutes with the scaling
       // lazily raised maximum
       float m_new = m_used;
       if (bmax > m_used + A_RESCALE_THRESHOLD || m_used == -INFINITY) m_new = fmaxf(m_used, bmax);
@@ -287,13 +289,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
-            asm volatile(
-                "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                ::"r"(tm_o[t] + lane_off + c0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]),
-                "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]), "r"(o[8]), "r"(o[9]), "r"(o[10]),
-                "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15])
-                : "memory");
+            tmem_st_32x16(tm_o[t] + lane_off + c0, o);
           }
           tmem_st_wait();
         }
@@ -302,26 +298,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (m_used != -INFINITY) l_sum *= exp2f(m_used - m_new);
         m_used = m_new;
       }
-      // probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle)
+      // ---- probabilities -> bf16 pairs (packed in place) -> TMEM, over the columns S occupied
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
       float psum = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        float e[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          e[j] = exp2f(__uint_as_float(sv[ch * 8 + j]) - mref);
-          psum += e[j];
-        }
-        uint32_t w0 = pack_bf16x2(e[0], e[1]), w1 = pack_bf16x2(e[2], e[3]);
-        uint32_t w2 = pack_bf16x2(e[4], e[5]), w3 = pack_bf16x2(e[6], e[7]);
-        uint32_t addr = p_row + ((ch ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1),
-                     "r"(w2), "r"(w3)
-                     : "memory");
+      for (int c = 0; c < A_BKV; c += 2) {
+        float e0 = exp2f(fmaf(__uint_as_float(sv[c]), p.scale_log2, -mref));
+        float e1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, -mref));
+        psum += e0 + e1;
+        sv[c >> 1] = pack_bf16x2(e0, e1);
       }
+#pragma unroll
+      for (int ch = 0; ch < A_BKV / 32; ++ch) tmem_st_32x16(tm_s[t] + lane_off + ch * 16, sv + ch * 16);
       l_sum += psum;
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_p[t]));
@@ -334,22 +324,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
         const bool row_ok = qi < p.L;
         __nv_bfloat16* orow = p.out + ((long long)b * p.L + qi) * p.ld_out + h * hd;
-        for (int c0 = 0; c0 < hd; c0 += 16) {
-          uint32_t o[16];
-          tmem_ld_32x16(tm_o[t] + lane_off + c0, o);
-          tmem_ld_wait();
-          if (row_ok) {
-            uint4 w0, w1;
-            w0.x = pack_bf16x2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
-            w0.y = pack_bf16x2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
-            w0.z = pack_bf16x2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
-            w0.w = pack_bf16x2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
-            w1.x = pack_bf16x2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
-            w1.y = pack_bf16x2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
-            w1.z = pack_bf16x2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
-            w1.w = pack_bf16x2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0) = w0;
-            *reinterpret_cast<uint4*>(orow + c0 + 8) = w1;
+        // all accumulator columns in one TMEM round trip (hd is a multiple of 16, <= 128)
+        uint32_t o[128];
+#pragma unroll
+        for (int c0 = 0; c0 < 128; c0 += 16)
+          if (c0 < hd) tmem_ld_32x16(tm_o[t] + lane_off + c0, o + c0);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int c0 = 0; c0 < 128; c0 += 8) {
+            if (c0 < hd) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[c0 + 0]) * inv, __uint_as_float(o[c0 + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(o[c0 + 2]) * inv, __uint_as_float(o[c0 + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(o[c0 + 4]) * inv, __uint_as_float(o[c0 + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(o[c0 + 6]) * inv, __uint_as_float(o[c0 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c0) = w;
+            }
           }
         }
       }
@@ -391,7 +382,7 @@ using namespace dz;
 
 // qkv: [B*L, ld_qkv] bf16 with Q at columns [q_col0, q_col0 + H*hd), K at k_col0, V at v_col0.
 // out: [B*L, ld_out] bf16.  prefix_k / prefix_v: [n_prefix, ld_prefix] bf16 or null.
-// hd in {64, 80, 96, 112, 128} (multiple of 16, at most 128).
+// hd in {64, 80, 96, 112, 128} (multiple of 16, at most 128); at most 128 prefix rows.
 extern "C" int dz_attn_fwd(const void* qkv, long long ld_qkv, int q_col0, int k_col0, int v_col0,
                            void* out, long long ld_out, const int* pad_left, const void* prefix_k,
                            const void* prefix_v, long long ld_prefix, int n_prefix, int B, int L,

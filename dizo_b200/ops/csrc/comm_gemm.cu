@@ -1,0 +1,557 @@
+// GEMM fused with its collective over peer memory (NVLink / NVSwitch), one launch:
+//
+//   out = epilogue( A[M,K] * W[N,K]^T )       tcgen05 / TMEM / TMA, as gemm_sm100.cu
+//
+// plus any of
+//   * PUSH role (the first n_push CTAs): copy a block of local rows into every peer's staging
+//     buffer with plain posted stores (all-gather by push), optionally transforming it on the
+//     way: theta + c * z(seed) regenerated from Philox for the pushed shard (FSDP parameter
+//     all-gather fused with the perturbation - the owner perturbs its shard once, nobody
+//     materialises z).  When a CTA has pushed its slice it fences at system scope; the last
+//     one raises the `ready` flag of this rank at every peer.
+//   * GATHERED OPERAND: rows of A (tensor parallel: sequence-sharded activations) or of W
+//     (FSDP: row-sharded weights) arrive from peers in this rank's staging buffer; the TMA
+//     producer polls the source rank's `ready` flag (bounded) before its first load of rows
+//     that rank owns, and tiles are visited own-rows-first, so math on what is already here
+//     overlaps the arrival of the rest.
+//   * PUSH EPILOGUE (GEMM -> reduce-scatter): every output tile is stored straight into the
+//     staging slot [this rank] of the rank that owns those rows; after the last tile the
+//     last CTA raises this rank's `partials ready` flag at every owner
+//     (dz_rs_reduce_layernorm in comm_kernels.cu is the owner side).
+//   * ACK: when the GEMM has consumed a gathered operand, the last CTA tells every peer that
+//     the staging buffer may be overwritten; a pusher waits (bounded) for those acks first.
+//
+// No load in this file uses cluster multicast and nothing is loaded from a peer: remote data
+// always arrives by the peer's stores into local memory, then is read with local TMA loads.
+// All waits are bounded and report through the error word.
+#include "common.cuh"
+#include "host_util.h"
+#include "philox.cuh"
+
+namespace dz {
+
+constexpr int CG_BM = 128;
+constexpr int CG_BN = 256;
+constexpr int CG_BK = 64;
+constexpr int CG_STAGES = 4;
+constexpr int CG_THREADS = 192;
+constexpr int CG_A_BYTES = CG_BM * CG_BK * 2;
+constexpr int CG_B_BYTES = CG_BN * CG_BK * 2;
+constexpr int CG_STAGE_BYTES = CG_A_BYTES + CG_B_BYTES;
+constexpr int CG_SMEM = CG_STAGES * CG_STAGE_BYTES + 1024;   // >= the 128 KB Gaussian table
+constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
+constexpr int CG_MAX_WORLD = 16;
+
+struct CommGemmArgs {
+  // ---- GEMM
+  int M, N, K;
+  int num_m, num_n;
+  void* out;                     // local output (ignored with push_out)
+  long long ldo;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  int act, out_fp32;
+  float out_scale;
+  // ---- gathered operand: 0 none, 1 = rows of A come from peers, 2 = rows of W come from peers
+  int gather;
+  int rows_per_src;              // rows owned by each source rank (multiple of the tile rows)
+  int wait_self;                 // own rows are also produced by this launch's push role
+  const uint32_t* ready_flags;   // local [world]: flag[s] >= ready_epoch once rank s has pushed
+  uint32_t ready_epoch;
+  // ---- ack of a consumed gathered operand
+  uint32_t* const* ack_ptrs;     // per rank: pointer to its [world] ack words
+  uint32_t ack_epoch;
+  // ---- push epilogue (reduce-scatter)
+  int push_out;
+  void* const* out_ptrs;         // per owner rank: base of its [world][rows_per_owner][ldo] staging
+  long long out_slot_stride;     // elements between the slots of two source ranks
+  int rows_per_owner;
+  uint32_t* const* rs_flag_ptrs; // per rank: its [world] "partials ready" words
+  uint32_t rs_epoch;
+  // ---- push role
+  int n_push;                    // CTAs doing the push (0 = none)
+  const __nv_bfloat16* push_src; // local rows [push_rows, push_cols], row stride push_ld
+  long long push_ld;
+  long long push_rows, push_cols;
+  void* const* push_dst_ptrs;    // per rank: base of the destination buffer
+  long long push_dst_ld;
+  long long push_dst_row0;       // first destination row (same in every peer)
+  int push_to_self;
+  uint32_t* const* push_flag_ptrs;   // per rank: its [world] ready words
+  uint32_t push_epoch;
+  const uint32_t* push_wait_acks;    // local [world] ack words to wait for before overwriting
+  uint32_t push_wait_epoch;          // (0 = do not wait)
+  // perturbation of the pushed rows
+  int push_perturb;
+  unsigned long long push_seed;
+  float push_coef;
+  int push_tensor_id;
+  long long push_elem_base;      // index of push_src[0,0] inside the full tensor
+  const __half* gauss_table;
+  // ---- bookkeeping
+  int rank, world;
+  unsigned int* counters;        // local [2]: pushers done, gemm CTAs done (monotonic)
+  unsigned int push_target, gemm_target;
+  uint32_t* err;
+};
+
+__device__ __forceinline__ void cg_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t cg_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool cg_wait_flag(const uint32_t* p, uint32_t epoch, volatile int* abort_flag,
+                                             uint32_t* err) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while ((int32_t)(cg_ld_acquire_sys(p) - epoch) < 0) {
+    if ((++spins & 0x3f) == 0) {
+      if (abort_flag && *abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > DZ_WAIT_TIMEOUT_NS) {
+        if (abort_flag) *abort_flag = 1;
+        if (err) atomicCAS(err, 0u, (uint32_t)ERR_WAIT_PEER | (blockIdx.x << 8));
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+  return true;
+}
+
+// Tiles are visited source by source, own rows first.
+__device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, int& mb, int& nb) {
+  if (p.gather == 1) {
+    const int mbs = p.rows_per_src / CG_BM;          // row tiles per source
+    const int per_src = mbs * p.num_n;
+    int s = tile / per_src, r = tile - s * per_src;
+    int src = (p.rank + s) % p.world;
+    mb = src * mbs + r / p.num_n;
+    nb = r % p.num_n;
+  } else if (p.gather == 2) {
+    const int nbs = p.rows_per_src / CG_BN;
+    const int per_src = nbs * p.num_m;
+    int s = tile / per_src, r = tile - s * per_src;
+    int src = (p.rank + s) % p.world;
+    nb = src * nbs + r / p.num_m;
+    mb = r % p.num_m;
+  } else {
+    int gm = p.num_m < 16 ? p.num_m : 16;
+    int tiles_per_group = gm * p.num_n;
+    int g = tile / tiles_per_group;
+    int first_m = g * gm;
+    int gmm = min(gm, p.num_m - first_m);
+    int r = tile - g * tiles_per_group;
+    mb = first_m + r % gmm;
+    nb = r / gmm;
+  }
+}
+
+__device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* smem_raw) {
+  __shared__ int s_go;
+  // stage the inverse-CDF table when the pushed rows are perturbed
+  const __half* tab = nullptr;
+  if (p.push_perturb) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.gauss_table);
+    uint4* dst = reinterpret_cast<uint4*>(smem_raw);
+    for (int i = threadIdx.x; i < GAUSS_TABLE_SIZE * 2 / 16; i += CG_THREADS) dst[i] = __ldg(src + i);
+    tab = reinterpret_cast<const __half*>(smem_raw);
+  }
+  if (threadIdx.x == 0) s_go = 1;
+  __syncthreads();
+  // the peers must have consumed what this buffer held before
+  if (p.push_wait_epoch != 0 && (int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+    if (!cg_wait_flag(p.push_wait_acks + threadIdx.x, p.push_wait_epoch, nullptr, p.err)) s_go = 0;
+  }
+  __syncthreads();
+  if (s_go) {
+    const long long vec_per_row = p.push_cols >> 3;
+    const long long total = p.push_rows * vec_per_row;
+    const long long per = (total + p.n_push - 1) / p.n_push;
+    const long long v0 = (long long)blockIdx.x * per;
+    const long long v1 = min(v0 + per, total);
+    for (long long v = v0 + threadIdx.x; v < v1; v += CG_THREADS) {
+      const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
+      uint4 raw = *reinterpret_cast<const uint4*>(p.push_src + r * p.push_ld + c);
+      if (p.push_perturb) {
+        float x[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
+                      bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
+        float z[8];
+        const long long e = p.push_elem_base + r * p.push_cols + c;
+        gauss8(tab, p.push_seed, (uint32_t)p.push_tensor_id, (uint32_t)(e >> 3), 0u, z);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = fmaf(p.push_coef, z[j], x[j]);
+        raw.x = pack_bf16x2(x[0], x[1]); raw.y = pack_bf16x2(x[2], x[3]);
+        raw.z = pack_bf16x2(x[4], x[5]); raw.w = pack_bf16x2(x[6], x[7]);
+      }
+      const long long doff = (p.push_dst_row0 + r) * p.push_dst_ld + c;
+      // nearest consumer first: rank d reads the rows of d+1, d+2, ... in that order
+      for (int s = 1; s <= p.world; ++s) {
+        int d = (p.rank - s + 2 * p.world) % p.world;
+        if (d == p.rank && !p.push_to_self) continue;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]) + doff) = raw;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int old = atomicAdd(p.counters + 0, 1u);
+    if (old + 1u == p.push_target && s_go) {
+      __threadfence_system();
+      for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.push_flag_ptrs[d] + p.rank, p.push_epoch);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(CG_THREADS, 1)
+comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const CommGemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[CG_STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[CG_STAGES];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+
+  if ((int)blockIdx.x < p.n_push) {
+    cg_push_role(p, smem_raw);
+    return;
+  }
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_tiles = p.num_m * p.num_n;
+  const int num_kb = (p.K + CG_BK - 1) / CG_BK;
+  const int cta = blockIdx.x - p.n_push;
+  const int n_cta = gridDim.x - p.n_push;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < CG_STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 4);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), CG_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t seen = 0;      // bit s set: source s is known to have arrived
+      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+        int mb, nb;
+        cg_tile_coords(tile, p, mb, nb);
+        if (p.gather) {
+          int src = (p.gather == 1 ? mb * CG_BM : nb * CG_BN) / p.rows_per_src;
+          if ((src != p.rank || p.wait_self) && !(seen & (1u << src))) {
+            if (!cg_wait_flag(p.ready_flags + src, p.ready_epoch, &s_abort, p.err)) { ok = false; break; }
+            seen |= 1u << src;
+            // the rows were written by a peer's ordinary stores; order them before TMA reads
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &s_abort, p.err, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint32_t full = smem_u32(&bar_full[stage]);
+          uint32_t a_dst = smem_base + stage * CG_STAGE_BYTES;
+          uint32_t b_dst = a_dst + CG_A_BYTES;
+          mbar_arrive_expect_tx(full, CG_STAGE_BYTES);
+          tma_load_2d(a_dst, &tmA, full, kb * CG_BK, mb * CG_BM);
+          tma_load_2d(b_dst, &tmB, full, kb * CG_BK, nb * CG_BN);
+          if (++stage == CG_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(CG_BM, CG_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+        if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1, &s_abort, p.err,
+                       ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * CG_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &s_abort, p.err, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t a_src = smem_base + stage * CG_STAGE_BYTES;
+          uint32_t b_src = a_src + CG_A_BYTES;
+          uint64_t a_desc = umma_desc_k_sw128(a_src);
+          uint64_t b_desc = umma_desc_k_sw128(b_src);
+#pragma unroll
+          for (int k = 0; k < CG_BK / 16; ++k)
+            umma_bf16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(smem_u32(&bar_empty[stage]));
+          if (++stage == CG_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&bar_acc_full[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cta; tile < num_tiles; tile += n_cta) {
+      int mb, nb;
+      cg_tile_coords(tile, p, mb, nb);
+      if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &s_abort, p.err, ERR_WAIT_TMEM_FULL))
+        break;
+      tc_fence_after();
+      const long long row = (long long)mb * CG_BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + acc * CG_BN + (static_cast<uint32_t>(quad * 32) << 16);
+      // destination of this row
+      __nv_bfloat16* orow_bf = nullptr;
+      float* orow_f32 = nullptr;
+      if (row_ok) {
+        if (p.push_out) {
+          int owner = (int)(row / p.rows_per_owner);
+          long long lr = row - (long long)owner * p.rows_per_owner;
+          orow_bf = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
+                    (long long)p.rank * p.out_slot_stride + lr * p.ldo;
+        } else if (p.out_fp32) {
+          orow_f32 = reinterpret_cast<float*>(p.out) + row * p.ldo;
+        } else {
+          orow_bf = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo;
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < CG_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = nb * CG_BN + c * 32;
+        if (col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        const bool full_chunk = (col0 + 32 <= p.N);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (p.out_scale != 1.0f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        } else if (p.act == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        }
+        if (row_ok) {
+          if (p.residual) {
+            const __nv_bfloat16* rp = p.residual + row * p.ldr + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+          }
+          if (orow_f32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full_chunk || col0 + j < p.N) orow_f32[col0 + j] = v[j];
+          } else if (full_chunk) {
+            uint4* op4 = reinterpret_cast<uint4*>(orow_bf + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              op4[q] = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) orow_bf[col0 + j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (p.push_out) __threadfence_system();     // this CTA's remote tile stores are ordered
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // the last GEMM CTA of this rank announces completion to the peers
+    __threadfence_system();
+    unsigned int old = atomicAdd(p.counters + 1, 1u);
+    if (old + 1u == p.gemm_target && !s_abort) {
+      __threadfence_system();
+      if (p.push_out)
+        for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.rs_flag_ptrs[d] + p.rank, p.rs_epoch);
+      if (p.gather && p.ack_ptrs)
+        for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.ack_ptrs[d] + p.rank, p.ack_epoch);
+    }
+  }
+  if (warp == 1) {
+    __syncwarp();
+    if (s_abort) {
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, CG_TMEM_COLS);
+  }
+}
+
+}  // namespace dz
+
+using namespace dz;
+
+// Plain-C mirror of the launch description (filled by Python through ctypes).
+struct DzCommGemmDesc {
+  // GEMM
+  const void* A; long long lda; const void* W; long long ldw;
+  void* out; long long ldo; const void* bias; const void* residual; long long ldr;
+  int M, N, K, act, out_fp32; float out_scale;
+  // gather
+  int gather, rows_per_src, wait_self; const void* ready_flags; unsigned int ready_epoch;
+  const void* ack_ptrs; unsigned int ack_epoch;
+  // push epilogue
+  int push_out; const void* out_ptrs; long long out_slot_stride; int rows_per_owner;
+  const void* rs_flag_ptrs; unsigned int rs_epoch;
+  // push role
+  int n_push; const void* push_src; long long push_ld, push_rows, push_cols;
+  const void* push_dst_ptrs; long long push_dst_ld, push_dst_row0; int push_to_self;
+  const void* push_flag_ptrs; unsigned int push_epoch;
+  const void* push_wait_acks; unsigned int push_wait_epoch;
+  int push_perturb; unsigned long long push_seed; float push_coef; int push_tensor_id;
+  long long push_elem_base; const void* gauss_table;
+  // bookkeeping
+  int rank, world; void* counters; unsigned int push_target, gemm_target;
+  int gemm_ctas;                 // 0 = all remaining SMs
+};
+
+extern "C" int dz_comm_gemm_desc_bytes() { return (int)sizeof(DzCommGemmDesc); }
+
+extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t stream) {
+  if (!d) return DZ_ERR_ARG;
+  const bool has_gemm = d->M > 0 && d->N > 0 && d->K > 0;
+  if (!has_gemm && d->n_push <= 0) return DZ_ERR_ARG;
+  if (d->world <= 0 || d->world > CG_MAX_WORLD || d->rank < 0 || d->rank >= d->world) return DZ_ERR_ARG;
+  CommGemmArgs a{};
+  CUtensorMap tmA{}, tmB{};
+  if (has_gemm) {
+    if (!d->A || !d->W) return DZ_ERR_ARG;
+    if ((d->K & 7) || (d->lda & 7) || (d->ldw & 7) || (d->ldo & 7)) return DZ_ERR_ALIGN;
+    if (d->gather && (d->rows_per_src <= 0 || !d->ready_flags)) return DZ_ERR_ARG;
+    if (d->gather == 1 && (d->rows_per_src % CG_BM)) return DZ_ERR_ALIGN;
+    if (d->gather == 2 && (d->rows_per_src % CG_BN)) return DZ_ERR_ALIGN;
+    if (d->push_out && (!d->out_ptrs || !d->rs_flag_ptrs || d->rows_per_owner <= 0 ||
+                        (d->rows_per_owner % CG_BM) || d->out_fp32))
+      return DZ_ERR_ARG;
+    if (!d->push_out && !d->out) return DZ_ERR_ARG;
+    int rc = make_tmap_bf16_2d(&tmA, d->A, d->M, d->K, d->lda, CG_BM, CG_BK, true);
+    if (rc) return rc;
+    rc = make_tmap_bf16_2d(&tmB, d->W, d->N, d->K, d->ldw, CG_BN, CG_BK, true);
+    if (rc) return rc;
+    a.M = d->M; a.N = d->N; a.K = d->K;
+    a.num_m = (d->M + CG_BM - 1) / CG_BM;
+    a.num_n = (d->N + CG_BN - 1) / CG_BN;
+  }
+  if (d->n_push > 0) {
+    if (!d->push_src || !d->push_dst_ptrs || !d->push_flag_ptrs || (d->push_cols & 7) ||
+        (d->push_ld & 7) || (d->push_dst_ld & 7))
+      return DZ_ERR_ARG;
+    if (d->push_perturb && (!d->gauss_table || (d->push_elem_base & 7))) return DZ_ERR_ARG;
+  }
+  a.out = d->out; a.ldo = d->ldo;
+  a.bias = (const __nv_bfloat16*)d->bias; a.residual = (const __nv_bfloat16*)d->residual; a.ldr = d->ldr;
+  a.act = d->act; a.out_fp32 = d->out_fp32; a.out_scale = d->out_scale;
+  a.gather = has_gemm ? d->gather : 0; a.rows_per_src = d->rows_per_src; a.wait_self = d->wait_self;
+  a.ready_flags = (const uint32_t*)d->ready_flags; a.ready_epoch = d->ready_epoch;
+  a.ack_ptrs = (uint32_t* const*)d->ack_ptrs; a.ack_epoch = d->ack_epoch;
+  a.push_out = d->push_out; a.out_ptrs = (void* const*)d->out_ptrs;
+  a.out_slot_stride = d->out_slot_stride; a.rows_per_owner = d->rows_per_owner;
+  a.rs_flag_ptrs = (uint32_t* const*)d->rs_flag_ptrs; a.rs_epoch = d->rs_epoch;
+  a.n_push = d->n_push > 0 ? d->n_push : 0;
+  a.push_src = (const __nv_bfloat16*)d->push_src; a.push_ld = d->push_ld;
+  a.push_rows = d->push_rows; a.push_cols = d->push_cols;
+  a.push_dst_ptrs = (void* const*)d->push_dst_ptrs; a.push_dst_ld = d->push_dst_ld;
+  a.push_dst_row0 = d->push_dst_row0; a.push_to_self = d->push_to_self;
+  a.push_flag_ptrs = (uint32_t* const*)d->push_flag_ptrs; a.push_epoch = d->push_epoch;
+  a.push_wait_acks = (const uint32_t*)d->push_wait_acks; a.push_wait_epoch = d->push_wait_epoch;
+  a.push_perturb = d->push_perturb; a.push_seed = d->push_seed; a.push_coef = d->push_coef;
+  a.push_tensor_id = d->push_tensor_id; a.push_elem_base = d->push_elem_base;
+  a.gauss_table = (const __half*)d->gauss_table;
+  a.rank = d->rank; a.world = d->world; a.counters = (unsigned int*)d->counters;
+  a.push_target = d->push_target; a.gemm_target = d->gemm_target; a.err = err;
+  if (!a.counters) return DZ_ERR_ARG;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         CG_SMEM);
+    if (e != cudaSuccess) return cuda_rc(e);
+    configured = true;
+  }
+  int gemm_ctas = 0;
+  if (has_gemm) {
+    int tiles = a.num_m * a.num_n;
+    int avail = sm_count() - a.n_push;
+    if (avail < 1) return DZ_ERR_ARG;
+    gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : avail;
+    if (gemm_ctas > avail) gemm_ctas = avail;
+    if (gemm_ctas > tiles) gemm_ctas = tiles;
+  }
+  // every CTA must be resident at once (the roles wait on one another through flags)
+  if (a.n_push + gemm_ctas > sm_count()) return DZ_ERR_TOO_LARGE;
+  comm_gemm_kernel<<<a.n_push + gemm_ctas, CG_THREADS, CG_SMEM, stream>>>(tmA, tmB, a);
+  return cuda_rc(cudaGetLastError());
+}
+
+extern "C" int dz_comm_gemm_ctas(int M, int N, int n_push) {
+  int tiles = ((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
+  int avail = sm_count() - n_push;
+  return tiles < avail ? tiles : avail;
+}

@@ -1,0 +1,99 @@
+"""Worker for tests/test_multigpu_fused.py: run under torchrun on >= 2 GPUs.
+
+Checks every fused compute+collective path against the composition of an NCCL collective and
+the single-GPU kernels.  NVLS is off and the kernels use plain peer stores (no multimem)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from dizo_b200.ops import _lib, philox  # noqa: E402
+from dizo_b200.ops.gemm import linear  # noqa: E402
+from dizo_b200.ops.norm import layernorm  # noqa: E402
+from dizo_b200.ops.zo import GammaState  # noqa: E402
+from dizo_b200.parallel.fused import FusedComm  # noqa: E402
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    M, d, F = 256 * world, 1024, 2048
+    fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2, n_push=8)
+    g = torch.Generator(device=dev).manual_seed(1234)          # same stream on every rank
+    rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
+
+    # ---- barrier + norm all-reduce fused with the gamma arithmetic
+    fc.barrier()
+    gs = GammaState(6, dev)
+    part = torch.arange(1, 7, device=dev, dtype=torch.float32) * (rank + 1)
+    for rep in range(2):
+        fc.norm_allreduce_gamma(part, gs, reinit=True)
+        want = part.clone()
+        dist.all_reduce(want)
+        torch.cuda.synchronize()
+        assert torch.allclose(gs.sq, want), (gs.sq, want)
+        assert torch.allclose(gs.ts, want.sqrt()) and torch.allclose(gs.gamma, want.sqrt())
+        assert torch.allclose(gs.alpha, torch.ones_like(gs.alpha), atol=1e-6)
+
+    # ---- tensor parallel: all-gather -> GEMM, GEMM -> reduce-scatter (+ residual + LayerNorm)
+    x_all = torch.randn(M, d, device=dev, generator=g).bfloat16()
+    w1 = (torch.randn(F, d, device=dev, generator=g) * 0.03).bfloat16()      # fc1, rows sharded
+    b1 = torch.randn(F, device=dev, generator=g).bfloat16()
+    w2 = (torch.randn(d, F, device=dev, generator=g) * 0.03).bfloat16()      # fc2, columns sharded
+    b2 = torch.randn(d, device=dev, generator=g).bfloat16()
+    lnw = torch.randn(d, device=dev, generator=g).bfloat16()
+    lnb = torch.randn(d, device=dev, generator=g).bfloat16()
+    rows, Fl = M // world, F // world
+    w1_l, b1_l = w1[rank * Fl:(rank + 1) * Fl].contiguous(), b1[rank * Fl:(rank + 1) * Fl].contiguous()
+    w2_l = w2[:, rank * Fl:(rank + 1) * Fl].contiguous()
+    for rep in range(3):
+        x_rep = (x_all.float() * (1 + 0.1 * rep)).bfloat16()
+        x_full, mine = fc.ag_input(M, d)
+        mine.copy_(x_rep[rank * rows:(rank + 1) * rows])
+        y = fc.ag_gemm(x_full, w1_l, b1_l, act="relu")                       # [M, F/world]
+        ref = linear(x_rep, w1_l, b1_l, act="relu")
+        torch.cuda.synchronize()
+        assert rel(y, ref) < 1e-3, ("ag_gemm", rep, rel(y, ref))
+        idx = fc.gemm_rs(y, w2_l)                                            # partial [M, d] -> owners
+        resid = x_rep[rank * rows:(rank + 1) * rows]
+        h, z = fc.rs_reduce_layernorm(idx, resid, b2, lnw, lnb)
+        part_ref = linear(ref, w2_l, out_dtype=torch.float32)
+        dist.all_reduce(part_ref)
+        h_ref = (part_ref[rank * rows:(rank + 1) * rows] + b2.float() + resid.float()).bfloat16()
+        z_ref = layernorm(h_ref, lnw, lnb)
+        torch.cuda.synchronize()
+        assert rel(h, h_ref) < 6e-3, ("gemm_rs", rep, rel(h, h_ref))
+        assert rel(z, z_ref) < 1e-2, ("rs_ln", rep, rel(z, z_ref))
+
+    # ---- FSDP: shard push fused with the perturbation and the consuming GEMM
+    xs = torch.randn(384, d, device=dev, generator=g).bfloat16()
+    shard = w1[rank * Fl:(rank + 1) * Fl].contiguous()
+    z_full = torch.from_numpy(philox.gaussian(77, 9, F * d)).view(F, d).to(dev)
+    w_pert = (w1.float() + 1e-2 * z_full).bfloat16()
+    for rep in range(3):
+        slot, out = fc.fsdp_launch(push=dict(w_shard=shard, N=F, tensor_id=9, seed=77, coef=1e-2),
+                                   gemm=None if rep == 2 else dict(slot=fc._calls["w"] % 2, N=F, x=xs, bias=b1))
+        if rep == 2:   # prefetch style: push first, consume in the next launch (with another push)
+            slot2, out = fc.fsdp_launch(push=dict(w_shard=shard, N=F, tensor_id=9, seed=77, coef=0.0),
+                                        gemm=dict(slot=slot, N=F, x=xs, bias=b1))
+        torch.cuda.synchronize()
+        ref = linear(xs, w_pert, b1)
+        assert torch.equal(fc.fsdp_weight(slot, F, d), w_pert), ("fsdp gather+perturb", rep)
+        assert rel(out, ref) < 1e-3, ("fsdp_gemm", rep, rel(out, ref))
+
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    dist.barrier()
+    if rank == 0:
+        print("FUSED_OK world", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -46,7 +46,7 @@ class ZOEngine:
         self.model = model
         self.eps = eps
         self.mode = mode
-        self.dp_group = dp_group
+        self.dp_group = dp_group          # None: the default group; False: no data parallelism
         self.stochastic_rounding = stochastic_rounding
         dev = model.device
         f = dict(dtype=torch.float32, device=dev)
@@ -65,7 +65,7 @@ class ZOEngine:
 
     def reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
         """Mean over the data-parallel group of a 1-element device tensor (NCCL / gloo)."""
-        if _dist_on(self.dp_group):
+        if self.dp_group is not False and _dist_on(self.dp_group):
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.dp_group)
             t.div_(dist.get_world_size(self.dp_group))
         return t
@@ -125,10 +125,19 @@ class DiZOProjector:
         self.fo_opt = None
 
     def _reduce(self, t: torch.Tensor) -> torch.Tensor:
-        if _dist_on(self.dp_group):
+        if self.dp_group is not False and _dist_on(self.dp_group):
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.dp_group)
             t.div_(dist.get_world_size(self.dp_group))
         return t
+
+    def _begin(self, reinit: bool) -> None:
+        """ts = ||theta - theta_0|| per constraint (+ gamma = ts when ``reinit``).  Sharded models
+        hold partial sums: their ``reduce_norms`` sums them over the shards and does the gamma
+        arithmetic in the same kernel."""
+        if hasattr(self.model, "reduce_norms"):
+            self.model.reduce_norms(self.gs, reinit)
+        else:
+            self.gs.begin(reinit=reinit)
 
     def measure(self) -> None:
         """sq[i] = ||theta_i - theta_0i||^2 for every constrained tensor (one pass)."""
@@ -141,7 +150,7 @@ class DiZOProjector:
         if not norms_ready:
             self.measure()
         gs = self.gs
-        gs.begin(reinit=True)
+        self._begin(reinit=True)
         for it in range(self.max_iters):
             batch = next_batch()
             gs.perturb(+1.0, seed=seed, it=it)
@@ -167,7 +176,7 @@ class DiZOProjector:
             return
         self.measure()
         gs = self.gs
-        gs.begin(reinit=False)
+        self._begin(reinit=False)
         if self.fo_gamma is None:
             self.fo_gamma = torch.zeros(self.n, dtype=torch.float32, device=self.model.device,
                                         requires_grad=True)

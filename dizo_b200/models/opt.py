@@ -245,7 +245,10 @@ class OPTModel:
         tset = set(self.trainable_names)
 
         def mk(specs):
-            ps = [Piece(n, tuple(s), self.tensor_ids[n], g) for n, s, g in specs]
+            ps = []
+            for n, s, g in specs:
+                ls, kw = self.shard_of(n, tuple(s))
+                ps.append(Piece(n, ls, self.tensor_ids[n], g, **kw))
             ps.sort(key=lambda p: _arena_sort_key(p.name, p.group))
             return ps
 
@@ -257,6 +260,16 @@ class OPTModel:
         self._side = None
         self._merge_buf: dict = {}
         self.kv_capture: list | None = None      # set to [] to record per-layer qkv (generation)
+
+    # ------------------------------------------------------------------ sharding hook
+    def shard_of(self, name: str, shape: tuple) -> tuple[tuple, dict]:
+        """(local shape, Piece keywords) of this rank's part of a parameter.  The base model
+        holds every parameter whole; tensor- and fully-sharded-parallel subclasses override."""
+        return shape, {}
+
+    def local_slice(self, name: str, full: torch.Tensor) -> torch.Tensor:
+        """This rank's part of a full parameter tensor (identity here)."""
+        return full
 
     # ------------------------------------------------------------------ parameter sets
     def _select_trainable(self) -> list[str]:
@@ -314,7 +327,7 @@ class OPTModel:
                 if n == _P + "embed_tokens.weight" or n == _P + "embed_positions.weight":
                     if n == _P + "embed_tokens.weight":
                         v[self.config.pad_token_id].zero_()
-            t.copy_(v.to(self.dtype))
+            t.copy_(self.local_slice(n, v).to(self.dtype))
         if self.untied and "lm_head.weight" in self._where:
             self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
         return self
@@ -370,7 +383,7 @@ class OPTModel:
                     if strict:
                         raise KeyError(f"state dict lacks {n}")
                     continue
-            self.param(n).copy_(src.to(self.dtype))
+            self.param(n).copy_(self.local_slice(n, src).to(self.dtype))
         return missing
 
     # ------------------------------------------------------------------ weight resolution

@@ -437,3 +437,79 @@ extern "C" int dz_gemm_bf16_tn_lse(const void* A, long long lda, const void* W, 
 }
 
 extern "C" int dz_gemm_lse_num_tiles(int N) { return (N + 255) / 256; }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free token log-probabilities (see dizo_noalloc.h).
+// ------------------------------------------------------------------------------------------
+#include "dizo_noalloc.h"
+
+namespace {
+
+constexpr int NA_TILES = (DZ_NOALLOC_MAX_VOCAB + 255) / 256;
+constexpr size_t NA_PART = (size_t)DZ_NOALLOC_MAX_ROWS * NA_TILES;       // floats per partial array
+constexpr size_t NA_FLOATS = 2 * NA_PART + DZ_NOALLOC_MAX_ROWS;          // max, sum, target logit
+
+// Scratch owned by the library.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a device address to hand to a kernel.
+static __device__ __align__(256) float g_noalloc_scratch[NA_FLOATS];
+
+constexpr int NA_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NA_MAX_DEVICES] = {};
+
+__global__ void noalloc_combine_kernel(const float* __restrict__ part_max,
+                                       const float* __restrict__ part_sum,
+                                       const float* __restrict__ tgt_logit, int num_tiles, int rows,
+                                       float* __restrict__ logprob) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const float* pm = part_max + (long long)r * num_tiles;
+  const float* ps = part_sum + (long long)r * num_tiles;
+  float m = -INFINITY;
+  for (int j = 0; j < num_tiles; ++j) m = fmaxf(m, pm[j]);
+  float s = 0.f;
+  for (int j = 0; j < num_tiles; ++j) s += ps[j] * expf(pm[j] - m);
+  logprob[r] = tgt_logit[r] - (m + logf(s));
+}
+
+}  // namespace
+
+extern "C" int dz_token_logprobs_noalloc(const void* A, long long lda, const void* W, long long ldw,
+                                         const int* targets, float* out_logprob, int M, int N, int K,
+                                         float scale, uint32_t* err, cudaStream_t stream) {
+  int rc = check_common(A, W, M, N, K, lda, ldw);
+  if (rc) return rc;
+  if (!targets || !out_logprob) return DZ_ERR_ARG;
+  if (M > DZ_NOALLOC_MAX_ROWS || N > DZ_NOALLOC_MAX_VOCAB) return DZ_ERR_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (dev < 0 || dev >= NA_MAX_DEVICES) return DZ_ERR_ARG;
+  if (!g_noalloc_ptr[dev]) {
+    // set-up, once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_rc(e);
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part_max = g_noalloc_ptr[dev];
+  float* part_sum = part_max + NA_PART;
+  float* tgt = part_sum + NA_PART;
+  // the gold logit of a row is only written when its target lies inside [0, N): start clean
+  e = cudaMemsetAsync(tgt, 0, sizeof(float) * M, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K;
+  a.targets = targets; a.part_max = part_max; a.part_sum = part_sum; a.tgt_logit = tgt;
+  a.out_scale = scale; a.err = err;
+  CUtensorMap tmA, tmB;
+  rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, G_BM, G_BK, true);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tmB, W, N, K, ldw, 256, G_BK, true);
+  if (rc) return rc;
+  rc = launch_gemm<256, 4, EPI_LSE>(tmA, tmB, a, stream);
+  if (rc) return rc;
+  const int tiles = (N + 255) / 256;
+  noalloc_combine_kernel<<<(M + 127) / 128, 128, 0, stream>>>(part_max, part_sum, tgt, tiles, M,
+                                                             out_logprob);
+  return cuda_rc(cudaGetLastError());
+}

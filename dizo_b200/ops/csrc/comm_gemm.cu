@@ -55,7 +55,9 @@ struct CommGemmArgs {
   float out_scale;
   // ---- gathered operand: 0 none, 1 = rows of A come from peers, 2 = rows of W come from peers
   int gather;
-  int rows_per_src;              // rows owned by each source rank (multiple of the tile rows)
+  int rows_per_src;              // rows owned by each source rank
+  int src_period;                // W rows repeat their ownership pattern every src_period rows
+                                 // (fused q|k|v: d); 0 = no repetition
   int wait_self;                 // own rows are also produced by this launch's push role
   const uint32_t* ready_flags;   // local [world]: flag[s] >= ready_epoch once rank s has pushed
   uint32_t ready_epoch;
@@ -71,12 +73,13 @@ struct CommGemmArgs {
   uint32_t rs_epoch;
   // ---- push role
   int n_push;                    // CTAs doing the push (0 = none)
-  const __nv_bfloat16* push_src; // local rows [push_rows, push_cols], row stride push_ld
+  int push_nseg;                 // 1..3 row segments of equal shape (e.g. the q, k, v shards)
+  const __nv_bfloat16* push_src[3]; // local rows [push_rows, push_cols], row stride push_ld
   long long push_ld;
   long long push_rows, push_cols;
   void* const* push_dst_ptrs;    // per rank: base of the destination buffer
   long long push_dst_ld;
-  long long push_dst_row0;       // first destination row (same in every peer)
+  long long push_dst_row0[3];    // first destination row of each segment (same in every peer)
   int push_to_self;
   uint32_t* const* push_flag_ptrs;   // per rank: its [world] ready words
   uint32_t push_epoch;
@@ -86,8 +89,8 @@ struct CommGemmArgs {
   int push_perturb;
   unsigned long long push_seed;
   float push_coef;
-  int push_tensor_id;
-  long long push_elem_base;      // index of push_src[0,0] inside the full tensor
+  int push_tensor_id[3];
+  long long push_elem_base[3];   // index of push_src[s][0,0] inside the full tensor
   const __half* gauss_table;
   // ---- bookkeeping
   int rank, world;
@@ -133,13 +136,6 @@ __device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, 
     int src = (p.rank + s) % p.world;
     mb = src * mbs + r / p.num_n;
     nb = r % p.num_n;
-  } else if (p.gather == 2) {
-    const int nbs = p.rows_per_src / CG_BN;
-    const int per_src = nbs * p.num_m;
-    int s = tile / per_src, r = tile - s * per_src;
-    int src = (p.rank + s) % p.world;
-    nb = src * nbs + r / p.num_m;
-    mb = r % p.num_m;
   } else {
     int gm = p.num_m < 16 ? p.num_m : 16;
     int tiles_per_group = gm * p.num_n;
@@ -171,25 +167,28 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
   __syncthreads();
   if (s_go) {
     const long long vec_per_row = p.push_cols >> 3;
-    const long long total = p.push_rows * vec_per_row;
+    const long long seg_total = p.push_rows * vec_per_row;
+    const long long total = seg_total * p.push_nseg;
     const long long per = (total + p.n_push - 1) / p.n_push;
     const long long v0 = (long long)blockIdx.x * per;
     const long long v1 = min(v0 + per, total);
-    for (long long v = v0 + threadIdx.x; v < v1; v += CG_THREADS) {
+    for (long long vv = v0 + threadIdx.x; vv < v1; vv += CG_THREADS) {
+      const int seg = (int)(vv / seg_total);
+      const long long v = vv - seg * seg_total;
       const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
-      uint4 raw = *reinterpret_cast<const uint4*>(p.push_src + r * p.push_ld + c);
+      uint4 raw = *reinterpret_cast<const uint4*>(p.push_src[seg] + r * p.push_ld + c);
       if (p.push_perturb) {
         float x[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
                       bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
         float z[8];
-        const long long e = p.push_elem_base + r * p.push_cols + c;
-        gauss8(tab, p.push_seed, (uint32_t)p.push_tensor_id, (uint32_t)(e >> 3), 0u, z);
+        const long long e = p.push_elem_base[seg] + r * p.push_cols + c;
+        gauss8(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3), 0u, z);
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = fmaf(p.push_coef, z[j], x[j]);
         raw.x = pack_bf16x2(x[0], x[1]); raw.y = pack_bf16x2(x[2], x[3]);
         raw.z = pack_bf16x2(x[4], x[5]); raw.w = pack_bf16x2(x[6], x[7]);
       }
-      const long long doff = (p.push_dst_row0 + r) * p.push_dst_ld + c;
+      const long long doff = (p.push_dst_row0[seg] + r) * p.push_dst_ld + c;
       // nearest consumer first: rank d reads the rows of d+1, d+2, ... in that order
       for (int s = 1; s <= p.world; ++s) {
         int d = (p.rank - s + 2 * p.world) % p.world;
@@ -265,13 +264,24 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int mb, nb;
         cg_tile_coords(tile, p, mb, nb);
         if (p.gather) {
-          int src = (p.gather == 1 ? mb * CG_BM : nb * CG_BN) / p.rows_per_src;
-          if ((src != p.rank || p.wait_self) && !(seen & (1u << src))) {
-            if (!cg_wait_flag(p.ready_flags + src, p.ready_epoch, &s_abort, p.err)) { ok = false; break; }
-            seen |= 1u << src;
-            // the rows were written by a peer's ordinary stores; order them before TMA reads
-            asm volatile("fence.proxy.async;" ::: "memory");
+          // every source rank that owns a row of this tile's gathered operand must have arrived
+          long long r0 = p.gather == 1 ? (long long)mb * CG_BM : (long long)nb * CG_BN;
+          long long r1 = p.gather == 1 ? min(r0 + CG_BM, (long long)p.M) : min(r0 + CG_BN, (long long)p.N);
+          bool fenced = true;
+          for (long long rr = r0; rr < r1 && ok;) {
+            long long q = p.src_period ? rr % p.src_period : rr;
+            int src = (int)(q / p.rows_per_src);
+            if (src >= p.world) src = p.world - 1;
+            if ((src != p.rank || p.wait_self) && !(seen & (1u << src))) {
+              if (!cg_wait_flag(p.ready_flags + src, p.ready_epoch, &s_abort, p.err)) { ok = false; break; }
+              seen |= 1u << src;
+              fenced = false;
+            }
+            rr += p.rows_per_src - (q % p.rows_per_src);      // first row of the next owner
           }
+          if (!ok) break;
+          // the rows were written by a peer's ordinary stores; order them before TMA reads
+          if (!fenced) asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &s_abort, p.err, ERR_WAIT_EMPTY)) {
@@ -456,18 +466,18 @@ struct DzCommGemmDesc {
   void* out; long long ldo; const void* bias; const void* residual; long long ldr;
   int M, N, K, act, out_fp32; float out_scale;
   // gather
-  int gather, rows_per_src, wait_self; const void* ready_flags; unsigned int ready_epoch;
+  int gather, rows_per_src, src_period, wait_self; const void* ready_flags; unsigned int ready_epoch;
   const void* ack_ptrs; unsigned int ack_epoch;
   // push epilogue
   int push_out; const void* out_ptrs; long long out_slot_stride; int rows_per_owner;
   const void* rs_flag_ptrs; unsigned int rs_epoch;
   // push role
-  int n_push; const void* push_src; long long push_ld, push_rows, push_cols;
-  const void* push_dst_ptrs; long long push_dst_ld, push_dst_row0; int push_to_self;
+  int n_push, push_nseg; const void* push_src[3]; long long push_ld, push_rows, push_cols;
+  const void* push_dst_ptrs; long long push_dst_ld, push_dst_row0[3]; int push_to_self;
   const void* push_flag_ptrs; unsigned int push_epoch;
   const void* push_wait_acks; unsigned int push_wait_epoch;
-  int push_perturb; unsigned long long push_seed; float push_coef; int push_tensor_id;
-  long long push_elem_base; const void* gauss_table;
+  int push_perturb; unsigned long long push_seed; float push_coef; int push_tensor_id[3];
+  long long push_elem_base[3]; const void* gauss_table;
   // bookkeeping
   int rank, world; void* counters; unsigned int push_target, gemm_target;
   int gemm_ctas;                 // 0 = all remaining SMs
@@ -487,7 +497,6 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
     if ((d->K & 7) || (d->lda & 7) || (d->ldw & 7) || (d->ldo & 7)) return DZ_ERR_ALIGN;
     if (d->gather && (d->rows_per_src <= 0 || !d->ready_flags)) return DZ_ERR_ARG;
     if (d->gather == 1 && (d->rows_per_src % CG_BM)) return DZ_ERR_ALIGN;
-    if (d->gather == 2 && (d->rows_per_src % CG_BN)) return DZ_ERR_ALIGN;
     if (d->push_out && (!d->out_ptrs || !d->rs_flag_ptrs || d->rows_per_owner <= 0 ||
                         (d->rows_per_owner % CG_BM) || d->out_fp32))
       return DZ_ERR_ARG;
@@ -501,29 +510,40 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
     a.num_n = (d->N + CG_BN - 1) / CG_BN;
   }
   if (d->n_push > 0) {
-    if (!d->push_src || !d->push_dst_ptrs || !d->push_flag_ptrs || (d->push_cols & 7) ||
-        (d->push_ld & 7) || (d->push_dst_ld & 7))
+    if (d->push_nseg < 1 || d->push_nseg > 3 || !d->push_dst_ptrs || !d->push_flag_ptrs ||
+        (d->push_cols & 7) || (d->push_ld & 7) || (d->push_dst_ld & 7))
       return DZ_ERR_ARG;
-    if (d->push_perturb && (!d->gauss_table || (d->push_elem_base & 7))) return DZ_ERR_ARG;
+    for (int sgi = 0; sgi < d->push_nseg; ++sgi) {
+      if (!d->push_src[sgi]) return DZ_ERR_ARG;
+      if (d->push_perturb && (d->push_elem_base[sgi] & 7)) return DZ_ERR_ARG;
+    }
+    if (d->push_perturb && !d->gauss_table) return DZ_ERR_ARG;
   }
   a.out = d->out; a.ldo = d->ldo;
   a.bias = (const __nv_bfloat16*)d->bias; a.residual = (const __nv_bfloat16*)d->residual; a.ldr = d->ldr;
   a.act = d->act; a.out_fp32 = d->out_fp32; a.out_scale = d->out_scale;
   a.gather = has_gemm ? d->gather : 0; a.rows_per_src = d->rows_per_src; a.wait_self = d->wait_self;
+  a.src_period = d->src_period;
   a.ready_flags = (const uint32_t*)d->ready_flags; a.ready_epoch = d->ready_epoch;
   a.ack_ptrs = (uint32_t* const*)d->ack_ptrs; a.ack_epoch = d->ack_epoch;
   a.push_out = d->push_out; a.out_ptrs = (void* const*)d->out_ptrs;
   a.out_slot_stride = d->out_slot_stride; a.rows_per_owner = d->rows_per_owner;
   a.rs_flag_ptrs = (uint32_t* const*)d->rs_flag_ptrs; a.rs_epoch = d->rs_epoch;
   a.n_push = d->n_push > 0 ? d->n_push : 0;
-  a.push_src = (const __nv_bfloat16*)d->push_src; a.push_ld = d->push_ld;
+  a.push_nseg = d->push_nseg;
+  for (int sgi = 0; sgi < 3; ++sgi) {
+    a.push_src[sgi] = (const __nv_bfloat16*)d->push_src[sgi];
+    a.push_dst_row0[sgi] = d->push_dst_row0[sgi];
+    a.push_tensor_id[sgi] = d->push_tensor_id[sgi];
+    a.push_elem_base[sgi] = d->push_elem_base[sgi];
+  }
+  a.push_ld = d->push_ld;
   a.push_rows = d->push_rows; a.push_cols = d->push_cols;
   a.push_dst_ptrs = (void* const*)d->push_dst_ptrs; a.push_dst_ld = d->push_dst_ld;
-  a.push_dst_row0 = d->push_dst_row0; a.push_to_self = d->push_to_self;
+  a.push_to_self = d->push_to_self;
   a.push_flag_ptrs = (uint32_t* const*)d->push_flag_ptrs; a.push_epoch = d->push_epoch;
   a.push_wait_acks = (const uint32_t*)d->push_wait_acks; a.push_wait_epoch = d->push_wait_epoch;
   a.push_perturb = d->push_perturb; a.push_seed = d->push_seed; a.push_coef = d->push_coef;
-  a.push_tensor_id = d->push_tensor_id; a.push_elem_base = d->push_elem_base;
   a.gauss_table = (const __half*)d->gauss_table;
   a.rank = d->rank; a.world = d->world; a.counters = (unsigned int*)d->counters;
   a.push_target = d->push_target; a.gemm_target = d->gemm_target; a.err = err;

@@ -44,16 +44,18 @@ class _Desc(ctypes.Structure):
         ("A", c_void), ("lda", c_ll), ("W", c_void), ("ldw", c_ll),
         ("out", c_void), ("ldo", c_ll), ("bias", c_void), ("residual", c_void), ("ldr", c_ll),
         ("M", c_int), ("N", c_int), ("K", c_int), ("act", c_int), ("out_fp32", c_int), ("out_scale", c_float),
-        ("gather", c_int), ("rows_per_src", c_int), ("wait_self", c_int), ("ready_flags", c_void),
+        ("gather", c_int), ("rows_per_src", c_int), ("src_period", c_int), ("wait_self", c_int),
+        ("ready_flags", c_void),
         ("ready_epoch", c_uint), ("ack_ptrs", c_void), ("ack_epoch", c_uint),
         ("push_out", c_int), ("out_ptrs", c_void), ("out_slot_stride", c_ll), ("rows_per_owner", c_int),
         ("rs_flag_ptrs", c_void), ("rs_epoch", c_uint),
-        ("n_push", c_int), ("push_src", c_void), ("push_ld", c_ll), ("push_rows", c_ll), ("push_cols", c_ll),
-        ("push_dst_ptrs", c_void), ("push_dst_ld", c_ll), ("push_dst_row0", c_ll), ("push_to_self", c_int),
+        ("n_push", c_int), ("push_nseg", c_int), ("push_src", c_void * 3), ("push_ld", c_ll),
+        ("push_rows", c_ll), ("push_cols", c_ll),
+        ("push_dst_ptrs", c_void), ("push_dst_ld", c_ll), ("push_dst_row0", c_ll * 3), ("push_to_self", c_int),
         ("push_flag_ptrs", c_void), ("push_epoch", c_uint), ("push_wait_acks", c_void),
         ("push_wait_epoch", c_uint),
         ("push_perturb", c_int), ("push_seed", ctypes.c_ulonglong), ("push_coef", c_float),
-        ("push_tensor_id", c_int), ("push_elem_base", c_ll), ("gauss_table", c_void),
+        ("push_tensor_id", c_int * 3), ("push_elem_base", c_ll * 3), ("gauss_table", c_void),
         ("rank", c_int), ("world", c_int), ("counters", c_void), ("push_target", c_uint),
         ("gemm_target", c_uint), ("gemm_ctas", c_int),
     ]
@@ -70,6 +72,7 @@ class _Channel:
         self.ready = rv.view(torch.int32)
         self.ack = av.view(torch.int32)
         self.epoch = 0          # pushes issued into this buffer
+        self.ack_epoch = 0      # consumptions of this buffer announced to the peers
         self.nbytes = nbytes
 
 
@@ -157,10 +160,11 @@ class FusedComm:
         d.gather, d.rows_per_src, d.wait_self = 1, rows, 0
         d.ready_flags, d.ready_epoch = ch.ready.data_ptr(), ch.epoch
         d.ack_ptrs, d.ack_epoch = ch.ack_ptrs.data_ptr(), ch.epoch
-        d.push_src, d.push_ld = x_full[self.rank * rows:].data_ptr(), x_full.stride(0)
+        d.push_nseg = 1
+        d.push_src[0], d.push_ld = x_full[self.rank * rows:].data_ptr(), x_full.stride(0)
         d.push_rows, d.push_cols = rows, K
-        d.push_dst_ptrs, d.push_dst_ld, d.push_dst_row0, d.push_to_self = ch.ptrs.data_ptr(), x_full.stride(0), \
-            self.rank * rows, 0
+        d.push_dst_ptrs, d.push_dst_ld, d.push_to_self = ch.ptrs.data_ptr(), x_full.stride(0), 0
+        d.push_dst_row0[0] = self.rank * rows
         d.push_flag_ptrs, d.push_epoch = ch.ready_ptrs.data_ptr(), ch.epoch
         d.push_wait_acks, d.push_wait_epoch = ch.ack.data_ptr(), prev
         self._launch(d, True, M, N)
@@ -210,39 +214,47 @@ class FusedComm:
     def fsdp_launch(self, push: dict | None = None, gemm: dict | None = None):
         """One launch doing either or both of
 
-        ``push = dict(w_shard=[N/world, K] rows owned by this rank, N=, tensor_id=, seed=, coef=)``:
-        perturb the shard (theta + coef * z, z regenerated for the shard's global element
-        indices) while storing it into every rank's staging copy of the weight (own copy
-        included); uses the next staging slot and returns its index;
+        ``push = dict(segments=[dict(w_shard=[rows, K] rows owned by this rank, dst_row0=first row
+        of that shard inside the staged full weight, tensor_id=, elem_base=index of the shard's
+        first element in its full tensor), ...up to 3 equal-shaped segments],
+        seed=, coef=, slot=None)``: perturb the shards (theta + coef * z, z regenerated for their
+        global element indices; coef 0 = plain copy) while storing them into every rank's staging
+        copy of the weight (own copy included).  Uses ``slot`` or the next staging slot; returns it.
 
-        ``gemm = dict(slot=, N=, x=[M, K], bias=, act=, residual=)``: out = act(x @ W_full.T + bias)
-        (+ residual) with W_full the staging copy in ``slot``; tiles are visited source by source
-        and poll that source's ready flag, so a weight pushed in this same launch is consumed as
-        it arrives, and one pushed by an earlier launch (prefetch) is consumed without waiting.
+        ``gemm = dict(slot=, N=, x=[M, K], rows_per_src=, src_period=0, bias=, act=, residual=, out=)``:
+        out = act(x @ W_full.T + bias) (+ residual) with W_full the staged weight in ``slot``.
+        Before the first load of a tile the producer polls the ready flags of the ranks that own
+        its rows, so a weight pushed in this same launch is consumed as it arrives and one pushed
+        by an earlier launch (prefetch) costs no wait.
 
         Returns (slot pushed into or None, GEMM output or None)."""
         d = _Desc()
         slot = None
         if push is not None:
-            slot = self._calls["w"] % 2
-            ch = self.wst[slot]
+            slot = push.get("slot")
+            if slot is None:
+                slot = self._calls["w"] % 2
             self._calls["w"] += 1
-            w_shard = push["w_shard"]
-            rows_w, K = w_shard.shape
-            assert rows_w * self.world == push["N"] and push["N"] * K * 2 <= ch.nbytes
-            prev = ch.epoch
+            ch = self.wst[slot]
+            segs = push["segments"]
+            rows_w, K = segs[0]["w_shard"].shape
+            prev_ack = ch.ack_epoch
             ch.epoch += 1
-            ch.rows_per_src = rows_w
-            d.push_src, d.push_ld, d.push_rows, d.push_cols = w_shard.data_ptr(), w_shard.stride(0), rows_w, K
+            d.push_nseg = len(segs)
+            for i, sg in enumerate(segs):
+                w = sg["w_shard"]
+                assert w.shape == (rows_w, K) and w.stride(0) == segs[0]["w_shard"].stride(0)
+                d.push_src[i] = w.data_ptr()
+                d.push_dst_row0[i] = int(sg["dst_row0"])
+                d.push_tensor_id[i] = int(sg.get("tensor_id", 0))
+                d.push_elem_base[i] = int(sg.get("elem_base", 0))
+            d.push_ld, d.push_rows, d.push_cols = segs[0]["w_shard"].stride(0), rows_w, K
             d.push_dst_ptrs, d.push_dst_ld = ch.ptrs.data_ptr(), K
-            d.push_dst_row0 = self.rank * rows_w
             d.push_to_self = 1
             d.push_flag_ptrs, d.push_epoch = ch.ready_ptrs.data_ptr(), ch.epoch
-            d.push_wait_acks, d.push_wait_epoch = ch.ack.data_ptr(), prev
+            d.push_wait_acks, d.push_wait_epoch = ch.ack.data_ptr(), prev_ack
             coef = float(push.get("coef", 0.0))
             d.push_perturb, d.push_seed, d.push_coef = int(coef != 0.0), int(push.get("seed", 0)), coef
-            d.push_tensor_id = int(push.get("tensor_id", 0))
-            d.push_elem_base = int(push.get("elem_base", self.rank * rows_w * K))
             d.gauss_table = gauss_table_dev(self.device).data_ptr()
         out = None
         M = Ng = 0
@@ -251,6 +263,7 @@ class FusedComm:
             x, N = gemm["x"], gemm["N"]
             M, K = x.shape
             Ng = N
+            assert N * K * 2 <= ch.nbytes, "staged weight larger than the staging slot"
             w_full = ch.view[:N * K * 2].view(torch.bfloat16).view(N, K)
             out = gemm.get("out")
             if out is None:
@@ -262,9 +275,12 @@ class FusedComm:
             if residual is not None:
                 d.residual, d.ldr = residual.data_ptr(), residual.stride(0)
             d.M, d.N, d.K, d.act, d.out_scale = M, N, K, ACT[gemm.get("act")], 1.0
-            d.gather, d.rows_per_src, d.wait_self = 2, ch.rows_per_src, 1
+            d.gather, d.rows_per_src, d.wait_self = 2, int(gemm["rows_per_src"]), 1
+            d.src_period = int(gemm.get("src_period", 0))
             d.ready_flags, d.ready_epoch = ch.ready.data_ptr(), ch.epoch
-            d.ack_ptrs, d.ack_epoch = ch.ack_ptrs.data_ptr(), ch.epoch
+            # acks count consumptions of the slot: the next pusher into it waits for this one
+            ch.ack_epoch += 1
+            d.ack_ptrs, d.ack_epoch = ch.ack_ptrs.data_ptr(), ch.ack_epoch
         self._launch(d, push is not None, M, Ng)
         return slot, out
 

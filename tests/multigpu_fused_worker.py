@@ -76,12 +76,16 @@ def main():
     shard = w1[rank * Fl:(rank + 1) * Fl].contiguous()
     z_full = torch.from_numpy(philox.gaussian(77, 9, F * d)).view(F, d).to(dev)
     w_pert = (w1.float() + 1e-2 * z_full).bfloat16()
+    seg = lambda: [dict(w_shard=shard, dst_row0=rank * Fl, tensor_id=9, elem_base=rank * Fl * d)]
     for rep in range(3):
-        slot, out = fc.fsdp_launch(push=dict(w_shard=shard, N=F, tensor_id=9, seed=77, coef=1e-2),
-                                   gemm=None if rep == 2 else dict(slot=fc._calls["w"] % 2, N=F, x=xs, bias=b1))
-        if rep == 2:   # prefetch style: push first, consume in the next launch (with another push)
-            slot2, out = fc.fsdp_launch(push=dict(w_shard=shard, N=F, tensor_id=9, seed=77, coef=0.0),
-                                        gemm=dict(slot=slot, N=F, x=xs, bias=b1))
+        nxt = fc._calls["w"] % 2
+        if rep < 2:      # push and consume in the same launch
+            slot, out = fc.fsdp_launch(push=dict(segments=seg(), seed=77, coef=1e-2),
+                                       gemm=dict(slot=nxt, N=F, x=xs, bias=b1, rows_per_src=Fl))
+        else:            # prefetch style: push first, consume in the next launch (with another push)
+            slot, _ = fc.fsdp_launch(push=dict(segments=seg(), seed=77, coef=1e-2))
+            _, out = fc.fsdp_launch(push=dict(segments=seg(), seed=77, coef=0.0),
+                                    gemm=dict(slot=slot, N=F, x=xs, bias=b1, rows_per_src=Fl))
         torch.cuda.synchronize()
         ref = linear(xs, w_pert, b1)
         got = fc.fsdp_weight(slot, F, d)
@@ -89,6 +93,21 @@ def main():
         # fma vs mul+add may flip the last bf16 bit of a few elements
         assert dw.max().item() <= 1e-3 and (dw > 0).float().mean().item() < 0.02, ("fsdp gather+perturb", rep)
         assert rel(out, ref) < 1e-3, ("fsdp_gemm", rep, rel(out, ref))
+    # fused q|k|v: three segments in one push, ownership repeating every d rows, tiles that
+    # straddle two owners (rows_per_src = d / world is not a multiple of the 256-row tile)
+    dq = 640
+    wq = [(torch.randn(dq, d, device=dev, generator=g) * 0.03).bfloat16() for _ in range(3)]
+    rq = dq // world
+    segs = [dict(w_shard=wq[j][rank * rq:(rank + 1) * rq].contiguous(), dst_row0=j * dq + rank * rq,
+                 tensor_id=20 + j, elem_base=rank * rq * d) for j in range(3)]
+    nxt = fc._calls["w"] % 2
+    slot, out = fc.fsdp_launch(push=dict(segments=segs, seed=5, coef=-1e-2),
+                               gemm=dict(slot=nxt, N=3 * dq, x=xs, rows_per_src=rq, src_period=dq))
+    torch.cuda.synchronize()
+    zq = [torch.from_numpy(philox.gaussian(5, 20 + j, dq * d)).view(dq, d).to(dev) for j in range(3)]
+    w_qkv = torch.cat([(wq[j].float() - 1e-2 * zq[j]).bfloat16() for j in range(3)])
+    assert rel(fc.fsdp_weight(slot, 3 * dq, d), w_qkv) < 1e-3
+    assert rel(out, linear(xs, w_qkv)) < 2e-3, rel(out, linear(xs, w_qkv))
 
     torch.cuda.synchronize()
     _lib.check_device_errors()

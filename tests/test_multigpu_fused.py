@@ -29,3 +29,13 @@ def test_tensor_parallel_model_matches_unsharded():
            os.path.join(ROOT, "tests", "multigpu_tp_worker.py")]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "TP_OK" in res.stdout, (res.stdout[-3000:], res.stderr[-3000:])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fsdp_model_matches_unsharded():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29535",
+           os.path.join(ROOT, "tests", "multigpu_fsdp_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "FSDP_OK" in res.stdout, (res.stdout[-3000:], res.stderr[-3000:])

@@ -43,6 +43,10 @@ def parse():
     ap.add_argument("--zo-mode", default="inflight", choices=["inflight", "inplace"])
     ap.add_argument("--enhanced", default="zo", choices=["none", "zo"])
     ap.add_argument("--overlap", action="store_true", help="sweep the next layer on a side stream")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "fsdp", "tp"],
+                    help="dp: replicated parameters, per-rank batches (default); fsdp: row-sharded weights, "
+                         "fused gather+perturb+GEMM; tp: tensor parallel with fused AG->GEMM / GEMM->RS "
+                         "(one global batch of --prompts x --seq)")
     ap.add_argument("--baseline-candidates", type=int, default=2)
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
@@ -141,15 +145,25 @@ def run_ours(a, world, rank, local):
 
     dev = torch.device("cuda", local)
     cfg = preset(a.model)
-    model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=a.overlap)
+    par = a.parallelism if world > 1 else "dp"
+    if par == "fsdp":
+        from dizo_b200.parallel.fsdp import FSDPOPTModel
+        model = FSDPOPTModel(cfg, dev)
+    elif par == "tp":
+        from dizo_b200.parallel.tp import TPOPTModel
+        model = TPOPTModel(cfg, dev, max_tokens=a.prompts * a.seq)
+    else:
+        model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=a.overlap)
     model.init_random_fast(seed=0)
-    engine = ZOEngine(model, eps=1e-3, mode=a.zo_mode)
-    projector = DiZOProjector(model) if a.enhanced == "zo" else None
+    dp_group = False if par == "tp" else None
+    engine = ZOEngine(model, eps=1e-3, mode=a.zo_mode, dp_group=dp_group)
+    projector = DiZOProjector(model, dp_group=dp_group) if a.enhanced == "zo" else None
+    data_rank = 0 if par == "tp" else rank            # tensor parallel: one global batch
     lr0, max_steps = 1e-6, 20000
     V = cfg.vocab_size
 
     def host_batch(step):
-        return synthetic_batch(step, a.prompts, a.seq, V, seed=1, rank=rank, pin=True)
+        return synthetic_batch(step, a.prompts, a.seq, V, seed=1, rank=data_rank, pin=True)
 
     def lr_at(k):
         return lr0 * (1 - k / (2 * max_steps))
@@ -192,7 +206,7 @@ def run_ours(a, world, rank, local):
     clocks = sampler.stop() if rank == 0 else None
     _lib.check_device_errors()
     ms = step_ms + search_ms / 50.0
-    tokens = a.prompts * a.seq * world
+    tokens = a.prompts * a.seq * (1 if par == "tp" else world)
 
     # ---- end to end through the public trainer call: pinned H2D of each step's inputs,
     #      the step, D2H read of its loss
@@ -202,7 +216,7 @@ def run_ours(a, world, rank, local):
         from dizo_b200.args import OurArguments
         targs = OurArguments(trainer="zo", learning_rate=lr0, max_steps=max_steps, zo_eps=1e-3,
                              enhanced=None, zo_mode=a.zo_mode)
-        tr = OurTrainer(model=model, args=targs, engine=engine)
+        tr = OurTrainer(model=model, args=targs, engine=engine, dp_group=dp_group)
         hb = [host_batch(10_000 + s) for s in range(a.steps + 2)]
         for s in range(2):
             tr.training_step(hb[s])
@@ -225,8 +239,8 @@ def run_ours(a, world, rank, local):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded uniform ids, Bernoulli labels); random-init weights",
         "impl": "ours",
-        "config": {"model": a.model, "global_batch": a.prompts * world, "seq_len": a.seq,
-                   "parallelism": f"dp{world}", "trainable": a.mode, "zo_mode": a.zo_mode,
+        "config": {"model": a.model, "global_batch": a.prompts * (1 if par == "tp" else world), "seq_len": a.seq,
+                   "parallelism": f"{par}{world}", "trainable": a.mode, "zo_mode": a.zo_mode,
                    "forwards_per_step": 2, "enhanced": a.enhanced,
                    "zo_step_ms": step_ms, "gamma_search_ms": search_ms, "gamma_search_period": 50,
                    "l2_policy": "per-step working set (parameters) far exceeds L2; no flush needed",

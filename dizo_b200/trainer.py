@@ -119,8 +119,9 @@ class OurTrainer:
         self._pgm_count = 0          # batches the gamma search has consumed (saved for resume)
         self._phase_ms: Dict[str, float] = {}
         self._metrics_f = None
-        self._rank = dist.get_rank(dp_group) if (dist.is_available() and dist.is_initialized()) else 0
-        self._world = dist.get_world_size(dp_group) if (dist.is_available() and dist.is_initialized()) else 1
+        on = dist.is_available() and dist.is_initialized() and dp_group is not False
+        self._rank = dist.get_rank(dp_group) if on else 0
+        self._world = dist.get_world_size(dp_group) if on else 1
 
     # ------------------------------------------------------------------ small API
     @property

@@ -57,6 +57,7 @@ class FSDPOPTModel(OPTModel):
         kw.setdefault("mode", "full")
         assert kw["mode"] == "full", "the sharded layout is built for full-parameter ZO"
         super().__init__(config, device, dtype, **kw)
+        self.push_perturb_limit = 24 * 1024 * 1024      # shard elements above which the push only copies
         self.comm = FusedComm(self.group, self.device, w_bytes=max(3 * d * d, F * d) * 2, n_push=n_push,
                               norm_slots=max(256, 2 * config.num_hidden_layers))
 
@@ -169,11 +170,16 @@ class FSDPOPTModel(OPTModel):
             buf = self._staging_for(("layer", i % 2), layer_numel)
             return self._resolver(i, transform, buf, self._sweep_group(i, transform, buf))
 
+        # The push CTAs regenerate z for the rows they send.  That is the cheapest place while a
+        # shard is small (8 ranks: 1/8 of a matrix); with few ranks the shard is large and the few
+        # push CTAs would become the bottleneck, so the whole-GPU sweep perturbs the shard into the
+        # local staging area first and the push is a plain copy (the path blends always take).
+        d_, F_ = cfg.hidden_size, cfg.ffn_dim
+        staged_push = blend or (transform is not None and F_ * d_ // self.n > self.push_perturb_limit)
+
         def push_of(i, which, staged_get):
-            # +-eps z: pushed straight from the arena shard and perturbed inside the push;
-            # blends: pushed from the locally blended shard, coefficient 0
-            segs, N, rps, period = self._push_spec(i, which, staged_get if blend else direct, transform)
-            return dict(segments=segs, seed=seed, coef=coef), N, rps, period
+            segs, N, rps, period = self._push_spec(i, which, staged_get if staged_push else direct, transform)
+            return dict(segments=segs, seed=seed, coef=0.0 if staged_push else coef), N, rps, period
 
         get = stage(0)
         p, N, rps, period = push_of(0, "qkv", get)

@@ -1,7 +1,7 @@
 """Timing of the fused compute+collective kernels against the NCCL + GEMM composition.
 
     python -m torch.distributed.run --nproc-per-node N -m dizo_b200.parallel.microbench \
-        [--m 8192 --d 9216 --ffn 36864] [--iters 10]
+        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas 16]
 
 For every path, device time (CUDA events, max over ranks) of the fused launch and of the
 composition it replaces (NCCL all-gather or reduce-scatter plus the framework's own GEMM), and
@@ -43,11 +43,11 @@ def timed(fn, iters, world):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=8192, help="token rows (global for TP, per rank for FSDP)")
-    ap.add_argument("--d", type=int, default=9216)
-    ap.add_argument("--ffn", type=int, default=36864)
+    ap.add_argument("--rows", dest="m", type=int, default=8192, help="token rows (global for TP, per rank for FSDP)")
+    ap.add_argument("--hidden", dest="d", type=int, default=9216)
+    ap.add_argument("--ffn-dim", dest="ffn", type=int, default=36864)
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--n-push", type=int, default=16)
+    ap.add_argument("--push-ctas", dest="n_push", type=int, default=16)
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)

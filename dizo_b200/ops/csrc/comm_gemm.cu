@@ -41,6 +41,7 @@ constexpr int CG_STAGE_BYTES = CG_A_BYTES + CG_B_BYTES;
 constexpr int CG_SMEM = CG_STAGES * CG_STAGE_BYTES + 1024;   // >= the 128 KB Gaussian table
 constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
 constexpr int CG_MAX_WORLD = 16;
+constexpr int CG_PUSH_UNROLL = 8;
 
 struct CommGemmArgs {
   // ---- GEMM
@@ -172,28 +173,51 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
     const long long per = (total + p.n_push - 1) / p.n_push;
     const long long v0 = (long long)blockIdx.x * per;
     const long long v1 = min(v0 + per, total);
-    for (long long vv = v0 + threadIdx.x; vv < v1; vv += CG_THREADS) {
-      const int seg = (int)(vv / seg_total);
-      const long long v = vv - seg * seg_total;
-      const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
-      uint4 raw = *reinterpret_cast<const uint4*>(p.push_src[seg] + r * p.push_ld + c);
-      if (p.push_perturb) {
-        float x[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
-                      bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
-        float z[8];
-        const long long e = p.push_elem_base[seg] + r * p.push_cols + c;
-        gauss8(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3), 0u, z);
+    // CG_PUSH_UNROLL independent 16-byte loads per thread are in flight before the first store:
+    // a copy loop with one load at a time is bound by local-memory latency, not by NVLink.
+    for (long long base = v0; base < v1; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
+      uint4 raw[CG_PUSH_UNROLL];
+      long long doff[CG_PUSH_UNROLL];
+      bool live[CG_PUSH_UNROLL];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[j] = fmaf(p.push_coef, z[j], x[j]);
-        raw.x = pack_bf16x2(x[0], x[1]); raw.y = pack_bf16x2(x[2], x[3]);
-        raw.z = pack_bf16x2(x[4], x[5]); raw.w = pack_bf16x2(x[6], x[7]);
+      for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
+        const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
+        live[u] = vv < v1;
+        if (live[u]) {
+          const int seg = (int)(vv / seg_total);
+          const long long v = vv - seg * seg_total;
+          const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
+          raw[u] = *reinterpret_cast<const uint4*>(p.push_src[seg] + r * p.push_ld + c);
+          doff[u] = (p.push_dst_row0[seg] + r) * p.push_dst_ld + c;
+        }
       }
-      const long long doff = (p.push_dst_row0[seg] + r) * p.push_dst_ld + c;
+      if (p.push_perturb) {
+#pragma unroll
+        for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
+          if (!live[u]) continue;
+          const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
+          const int seg = (int)(vv / seg_total);
+          const long long v = vv - seg * seg_total;
+          const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
+          float x[8] = {bf16_lo(raw[u].x), bf16_hi(raw[u].x), bf16_lo(raw[u].y), bf16_hi(raw[u].y),
+                        bf16_lo(raw[u].z), bf16_hi(raw[u].z), bf16_lo(raw[u].w), bf16_hi(raw[u].w)};
+          float z[8];
+          const long long e = p.push_elem_base[seg] + r * p.push_cols + c;
+          gauss8(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3), 0u, z);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = fmaf(p.push_coef, z[j], x[j]);
+          raw[u].x = pack_bf16x2(x[0], x[1]); raw[u].y = pack_bf16x2(x[2], x[3]);
+          raw[u].z = pack_bf16x2(x[4], x[5]); raw[u].w = pack_bf16x2(x[6], x[7]);
+        }
+      }
       // nearest consumer first: rank d reads the rows of d+1, d+2, ... in that order
       for (int s = 1; s <= p.world; ++s) {
         int d = (p.rank - s + 2 * p.world) % p.world;
         if (d == p.rank && !p.push_to_self) continue;
-        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]) + doff) = raw;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]);
+#pragma unroll
+        for (int u = 0; u < CG_PUSH_UNROLL; ++u)
+          if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
       }
     }
   }

@@ -293,3 +293,25 @@ def test_gamma_state_matches_cpu():
     out = torch.zeros(1, device=DEV)
     scalar_diff(l1.to(DEV), l2.to(DEV), 500.0, out)
     assert abs(out.item() - 10.0) < 1e-3
+
+
+# ------------------------------------------------------------------ bounded waits
+def test_peer_wait_times_out_with_error_status_instead_of_hanging():
+    """A flag that nothing ever sets: the kernel gives up after its time limit, records
+    ERR_WAIT_PEER in the error word and returns; the context stays usable."""
+    import ctypes
+    import time
+    flags = torch.zeros(2, dtype=torch.int32, device=DEV)          # "rank 1" never writes flags[1]
+    ptrs = torch.tensor([flags.data_ptr(), flags.data_ptr()], dtype=torch.int64, device=DEV)
+    t0 = time.time()
+    rc = _lib.lib().dz_peer_barrier(_lib.ptr(ptrs), 0, 2, ctypes.c_uint(1), _lib.ptr(_lib.err_word(DEV)),
+                                    _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert 1.0 < time.time() - t0 < 10.0
+    with pytest.raises(_lib.KernelError, match="peer"):
+        _lib.check_device_errors()
+    # the device still works and the error word is clear again
+    x = torch.ones(8, device=DEV)
+    assert x.sum().item() == 8
+    _lib.check_device_errors()

@@ -14,6 +14,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from ..ops import attention as attn_ops
+from ..ops import decode as decode_ops
 from ..ops import gemm, norm
 from .opt import _P, Batch, OPTModel, make_batch
 
@@ -88,9 +89,8 @@ class _Decoder:
             qkv = gemm.linear(x, w.qkv_w, w.qkv_b)
             self.k[i][:, t].copy_(qkv[:, d:2 * d])
             self.v[i][:, t].copy_(qkv[:, 2 * d:])
-            ctx = attn_ops.decode_attention_reference(qkv[:, :d], self.k[i], self.v[i], t + 1,
-                                                      cfg.num_attention_heads, pad_left,
-                                                      w.prefix_k, w.prefix_v)
+            ctx = decode_ops.decode_attention(qkv[:, :d], self.k[i], self.v[i], t + 1,
+                                              cfg.num_attention_heads, pad_left, w.prefix_k, w.prefix_v)
             h = gemm.linear(ctx.contiguous(), w.out_w, w.out_b, residual=h)
             if not pre:
                 h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
@@ -153,11 +153,12 @@ def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[
     for t in range(max_new_tokens):
         logits = _head_logits(model, h_last)
         if nb == 1:
-            if do_sample:
+            if do_sample and dev.type != "cuda":
                 probs = torch.softmax(filter_logits(logits, temperature, top_k, top_p), dim=-1)
                 nxt = torch.multinomial(probs, 1, generator=gen).squeeze(1)
             else:
-                nxt = logits.argmax(dim=-1)
+                nxt = decode_ops.sample(logits.contiguous(), temperature, top_k, top_p, do_sample,
+                                        seed=seed or 0, offset=t)
             nxt = torch.where(done, torch.full_like(nxt, pad_token_id), nxt)
         else:
             lp = torch.log_softmax(logits, dim=-1)

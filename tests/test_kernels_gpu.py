@@ -315,3 +315,50 @@ def test_peer_wait_times_out_with_error_status_instead_of_hanging():
     x = torch.ones(8, device=DEV)
     assert x.sum().item() == 8
     _lib.check_device_errors()
+
+
+# ------------------------------------------------------------------ decoding
+def test_decode_attention_matches_reference():
+    from dizo_b200.ops.attention import decode_attention_reference
+    from dizo_b200.ops.decode import decode_attention
+    for H, hd, Lmax, kv_len in ((12, 64, 96, 70), (32, 80, 300, 300), (40, 128, 64, 1)):
+        B, d = 3, H * hd
+        g = torch.Generator(device=DEV).manual_seed(hd)
+        q = torch.randn(B, d, device=DEV, generator=g).bfloat16()
+        kc = torch.randn(B, Lmax, d, device=DEV, generator=g).bfloat16()
+        vc = torch.randn(B, Lmax, d, device=DEV, generator=g).bfloat16()
+        pad = torch.tensor([0, min(5, kv_len - 1), 0], dtype=torch.int32, device=DEV)
+        pk = torch.randn(5, d, device=DEV, generator=g).bfloat16()
+        pv = torch.randn(5, d, device=DEV, generator=g).bfloat16()
+        for pre in (False, True):
+            out = decode_attention(q, kc, vc, kv_len, H, pad, pk if pre else None, pv if pre else None)
+            ref = decode_attention_reference(q.float(), kc.float(), vc.float(), kv_len, H, pad,
+                                             pk.float() if pre else None, pv.float() if pre else None)
+            assert (out.float() - ref).abs().max().item() < 3e-2
+
+
+def test_sampling_kernel_distribution_and_filters():
+    from dizo_b200.ops.decode import sample
+    V = 1000
+    g = torch.Generator(device=DEV).manual_seed(0)
+    logits = torch.randn(1, V, device=DEV, generator=g) * 2
+    assert sample(logits, do_sample=False).item() == logits.argmax().item()
+    big = logits.repeat(4096, 1).contiguous()
+    # top-k: only the k most likely tokens may appear
+    toks = sample(big, temperature=0.7, top_k=5, top_p=1.0, seed=3)
+    top5 = set(logits[0].topk(5).indices.tolist())
+    assert set(toks.tolist()) <= top5 and len(set(toks.tolist())) >= 3
+    # nucleus: the sampled set is the smallest prefix of the sorted distribution reaching p
+    p = torch.softmax(logits[0].float(), -1)
+    srt, idx = p.sort(descending=True)
+    n_keep = int((srt.cumsum(0) < 0.5).sum().item()) + 1
+    toks = sample(big, top_p=0.5, seed=4)
+    assert set(toks.tolist()) <= set(idx[:n_keep].tolist())
+    # frequencies follow the renormalised probabilities
+    counts = torch.bincount(toks, minlength=V).float() / toks.numel()
+    want = torch.zeros(V, device=DEV)
+    want[idx[:n_keep]] = srt[:n_keep] / srt[:n_keep].sum()
+    assert (counts - want).abs().max().item() < 0.04
+    # different steps draw differently, same (seed, offset) repeats
+    a, b, c = sample(big, seed=9, offset=0), sample(big, seed=9, offset=0), sample(big, seed=9, offset=1)
+    assert torch.equal(a, b) and not torch.equal(a, c)

@@ -33,12 +33,13 @@ namespace dz {
 constexpr int CG_BM = 128;
 constexpr int CG_BN = 256;
 constexpr int CG_BK = 64;
-constexpr int CG_STAGES = 4;
+constexpr int CG_STAGES = 3;
 constexpr int CG_THREADS = 192;
 constexpr int CG_A_BYTES = CG_BM * CG_BK * 2;
 constexpr int CG_B_BYTES = CG_BN * CG_BK * 2;
 constexpr int CG_STAGE_BYTES = CG_A_BYTES + CG_B_BYTES;
-constexpr int CG_SMEM = CG_STAGES * CG_STAGE_BYTES + 1024;   // >= the 128 KB Gaussian table
+constexpr int CG_OUT_STAGE_BYTES = CG_BM * CG_BN * 2;           // bf16 tile staged for coalesced remote stores
+constexpr int CG_SMEM = CG_STAGES * CG_STAGE_BYTES + CG_OUT_STAGE_BYTES + 1024;   // >= the 128 KB Gaussian table
 constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
 constexpr int CG_MAX_WORLD = 16;
 constexpr int CG_PUSH_UNROLL = 8;
@@ -95,7 +96,8 @@ struct CommGemmArgs {
   const __half* gauss_table;
   // ---- bookkeeping
   int rank, world;
-  unsigned int* counters;        // local [2]: pushers done, gemm CTAs done (monotonic)
+  unsigned int* counters;        // local [2 + world]: pushers done, gemm CTAs done, pushers done per
+                                 // destination (all monotonic)
   unsigned int push_target, gemm_target;
   uint32_t* err;
 };
@@ -173,6 +175,47 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
     const long long per = (total + p.n_push - 1) / p.n_push;
     const long long v0 = (long long)blockIdx.x * per;
     const long long v1 = min(v0 + per, total);
+    if (!p.push_perturb) {
+      // Plain copy: one destination after the other, nearest consumer first (rank d consumes the
+      // rows of d+1, d+2, ... in that order), and each destination's ready flag goes up as soon
+      // as ITS copy is complete, so consumers start on the first source while the rest travels.
+      // The source is re-read per destination; it sits in L2.
+      for (int sdst = 1; sdst <= p.world; ++sdst) {
+        const int d = (p.rank - sdst + 2 * p.world) % p.world;
+        const bool skip = (d == p.rank && !p.push_to_self);   // counters advance all the same
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]);
+        for (long long base = v0; base < v1 && !skip; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
+          uint4 raw[CG_PUSH_UNROLL];
+          long long doff[CG_PUSH_UNROLL];
+          bool live[CG_PUSH_UNROLL];
+#pragma unroll
+          for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
+            const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
+            live[u] = vv < v1;
+            if (live[u]) {
+              const int seg = (int)(vv / seg_total);
+              const long long v = vv - seg * seg_total;
+              const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
+              raw[u] = *reinterpret_cast<const uint4*>(p.push_src[seg] + r * p.push_ld + c);
+              doff[u] = (p.push_dst_row0[seg] + r) * p.push_dst_ld + c;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < CG_PUSH_UNROLL; ++u)
+            if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          unsigned int old = atomicAdd(p.counters + 2 + d, 1u);
+          if (old + 1u == p.push_target) {
+            __threadfence_system();
+            cg_st_release_sys(p.push_flag_ptrs[d] + p.rank, p.push_epoch);
+          }
+        }
+      }
+    } else {
+    // Perturbed push: z is generated once per element, then stored to every destination.
     // CG_PUSH_UNROLL independent 16-byte loads per thread are in flight before the first store:
     // a copy loop with one load at a time is bound by local-memory latency, not by NVLink.
     for (long long base = v0; base < v1; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
@@ -220,12 +263,16 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
           if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
       }
     }
+    }
   }
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned int old = atomicAdd(p.counters + 0, 1u);
-    if (old + 1u == p.push_target && s_go) {
+    // the per-destination counters of the copy path stay in step with the common one
+    if (p.push_perturb || !s_go)
+      for (int d = 0; d < p.world; ++d) atomicAdd(p.counters + 2 + d, 1u);
+    if (old + 1u == p.push_target && s_go && p.push_perturb) {
       __threadfence_system();
       for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.push_flag_ptrs[d] + p.rank, p.push_epoch);
     }
@@ -363,6 +410,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
+    const uint32_t out_stage = smem_base + CG_STAGES * CG_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = cta; tile < num_tiles; tile += n_cta) {
@@ -427,6 +475,18 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (full_chunk || col0 + j < p.N) orow_f32[col0 + j] = v[j];
+          } else if (p.push_out) {
+            // stage the tile in shared memory (16-byte units XOR-swizzled by the row so that
+            // neither this row-per-thread fill nor the row-per-warp drain conflicts on banks)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t unit = (uint32_t)(c * 4 + q) ^ (uint32_t)(row_in_tile & 31);
+              const uint32_t addr = out_stage + row_in_tile * (CG_BN * 2) + unit * 16;
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1])), "r"(pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3])),
+                           "r"(pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5])), "r"(pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]))
+                           : "memory");
+            }
           } else if (full_chunk) {
             uint4* op4 = reinterpret_cast<uint4*>(orow_bf + col0);
 #pragma unroll
@@ -450,6 +510,27 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+      if (p.push_out) {
+        // drain: every warp sends whole rows (512 contiguous bytes per store instruction) to the
+        // rank that owns them, so the NVLink writes are full-width instead of 16-byte fragments
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const long long row0 = (long long)mb * CG_BM;
+        const int owner = (int)(row0 / p.rows_per_owner);
+        __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
+                               (long long)p.rank * p.out_slot_stride +
+                               (row0 - (long long)owner * p.rows_per_owner) * p.ldo + (long long)nb * CG_BN;
+        const int colu = nb * CG_BN + lane * 8;
+        for (int rr = quad; rr < CG_BM; rr += 4) {
+          if (row0 + rr < p.M && colu < p.N) {
+            const uint32_t addr = out_stage + rr * (CG_BN * 2) + (((uint32_t)lane ^ (uint32_t)(rr & 31)) * 16);
+            uint4 o;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(addr) : "memory");
+            *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + lane * 8) = o;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
     }
     if (p.push_out) __threadfence_system();     // this CTA's remote tile stores are ordered
   }
@@ -525,6 +606,7 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
                         (d->rows_per_owner % CG_BM) || d->out_fp32))
       return DZ_ERR_ARG;
     if (!d->push_out && !d->out) return DZ_ERR_ARG;
+    if (d->push_out && (d->N & 7)) return DZ_ERR_ALIGN;
     int rc = make_tmap_bf16_2d(&tmA, d->A, d->M, d->K, d->lda, CG_BM, CG_BK, true);
     if (rc) return rc;
     rc = make_tmap_bf16_2d(&tmB, d->W, d->N, d->K, d->ldw, CG_BN, CG_BK, true);

@@ -98,7 +98,7 @@ class FusedComm:
         self.norm_mc_local = mv.view(torch.float32)
         _, fv, self.norm_flag_ptrs = self.region.alloc(4 * self.world)
         self.norm_epoch = 0
-        self.counters = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros(2 + self.world, dtype=torch.int32, device=self.device)
         self._push_total = 0
         self._gemm_total = 0
         self._calls = {"ag": 0, "rs": 0, "w": 0}

@@ -33,13 +33,15 @@ namespace dz {
 constexpr int CG_BM = 128;
 constexpr int CG_BN = 256;
 constexpr int CG_BK = 64;
-constexpr int CG_STAGES = 3;
+constexpr int CG_STAGES_PUSH = 3;   // ring depth when a tile is staged for the reduce-scatter epilogue
+constexpr int CG_STAGES_PLAIN = 4;
 constexpr int CG_THREADS = 192;
 constexpr int CG_A_BYTES = CG_BM * CG_BK * 2;
 constexpr int CG_B_BYTES = CG_BN * CG_BK * 2;
 constexpr int CG_STAGE_BYTES = CG_A_BYTES + CG_B_BYTES;
 constexpr int CG_OUT_STAGE_BYTES = CG_BM * CG_BN * 2;           // bf16 tile staged for coalesced remote stores
-constexpr int CG_SMEM = CG_STAGES * CG_STAGE_BYTES + CG_OUT_STAGE_BYTES + 1024;   // >= the 128 KB Gaussian table
+constexpr int CG_SMEM_PUSH = CG_STAGES_PUSH * CG_STAGE_BYTES + CG_OUT_STAGE_BYTES + 1024;
+constexpr int CG_SMEM_PLAIN = CG_STAGES_PLAIN * CG_STAGE_BYTES + 1024;   // both >= the 128 KB Gaussian table
 constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
 constexpr int CG_MAX_WORLD = 16;
 constexpr int CG_PUSH_UNROLL = 8;
@@ -279,6 +281,7 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
   }
 }
 
+template <int CG_STAGES>
 __global__ void __launch_bounds__(CG_THREADS, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const CommGemmArgs p) {
@@ -656,8 +659,11 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   if (!a.counters) return DZ_ERR_ARG;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         CG_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<CG_STAGES_PUSH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, CG_SMEM_PUSH);
+    if (e != cudaSuccess) return cuda_rc(e);
+    e = cudaFuncSetAttribute(comm_gemm_kernel<CG_STAGES_PLAIN>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, CG_SMEM_PLAIN);
     if (e != cudaSuccess) return cuda_rc(e);
     configured = true;
   }
@@ -672,7 +678,10 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   }
   // every CTA must be resident at once (the roles wait on one another through flags)
   if (a.n_push + gemm_ctas > sm_count()) return DZ_ERR_TOO_LARGE;
-  comm_gemm_kernel<<<a.n_push + gemm_ctas, CG_THREADS, CG_SMEM, stream>>>(tmA, tmB, a);
+  if (a.push_out)
+    comm_gemm_kernel<CG_STAGES_PUSH><<<a.n_push + gemm_ctas, CG_THREADS, CG_SMEM_PUSH, stream>>>(tmA, tmB, a);
+  else
+    comm_gemm_kernel<CG_STAGES_PLAIN><<<a.n_push + gemm_ctas, CG_THREADS, CG_SMEM_PLAIN, stream>>>(tmA, tmB, a);
   return cuda_rc(cudaGetLastError());
 }
 

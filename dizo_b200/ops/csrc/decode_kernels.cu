@@ -37,11 +37,14 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
   // scores: one key per half-warp pass (16 lanes x 8 elements cover hd <= 128)
   const int sub = lane >> 4, l16 = lane & 15;
   float lmax = -INFINITY;
-  for (int j = warp * 2 + sub; j < total; j += (DA_THREADS / 32) * 2) {
-    const __nv_bfloat16* krow = j < n_prefix ? pk + (long long)j * ldp + h * hd
-                                             : kc + (long long)b * ld_seq + (long long)(j - n_prefix) * ld_row + h * hd;
+  // the trip count is the same for every lane of a warp (the shuffles below need all 32 lanes)
+  for (int jb = warp * 2; jb < total; jb += (DA_THREADS / 32) * 2) {
+    const int j = jb + sub;
+    const bool in_range = j < total;
     float acc = 0.f;
-    if (l16 * 8 < hd) {
+    if (in_range && l16 * 8 < hd) {
+      const __nv_bfloat16* krow = j < n_prefix ? pk + (long long)j * ldp + h * hd
+                                               : kc + (long long)b * ld_seq + (long long)(j - n_prefix) * ld_row + h * hd;
       uint4 kv = *reinterpret_cast<const uint4*>(krow + l16 * 8);
       const float* qq = s_q + l16 * 8;
       acc = qq[0] * bf16_lo(kv.x) + qq[1] * bf16_hi(kv.x) + qq[2] * bf16_lo(kv.y) + qq[3] * bf16_hi(kv.y) +
@@ -49,10 +52,12 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
     }
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    const bool vis = j < n_prefix || (j - n_prefix) >= pad;
-    if (!vis) acc = -INFINITY;
-    if (l16 == 0) s_score[j] = acc;
-    lmax = fmaxf(lmax, acc);
+    if (in_range) {
+      const bool vis = j < n_prefix || (j - n_prefix) >= pad;
+      if (!vis) acc = -INFINITY;
+      if (l16 == 0) s_score[j] = acc;
+      lmax = fmaxf(lmax, acc);
+    }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));

@@ -44,6 +44,7 @@ constexpr int CG_SMEM_PUSH = CG_STAGES_PUSH * CG_STAGE_BYTES + CG_OUT_STAGE_BYTE
 constexpr int CG_SMEM_PLAIN = CG_STAGES_PLAIN * CG_STAGE_BYTES + 1024;   // both >= the 128 KB Gaussian table
 constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
 constexpr int CG_MAX_WORLD = 16;
+constexpr int CG_MAXC = 16;            // progress chunks per source in a gathered operand
 constexpr int CG_PUSH_UNROLL = 8;
 
 struct CommGemmArgs {
@@ -63,7 +64,9 @@ struct CommGemmArgs {
   int src_period;                // W rows repeat their ownership pattern every src_period rows
                                  // (fused q|k|v: d); 0 = no repetition
   int wait_self;                 // own rows are also produced by this launch's push role
-  const uint32_t* ready_flags;   // local [world]: flag[s] >= ready_epoch once rank s has pushed
+  int chunk_tiles;               // gather 1: row tiles per progress chunk of a source (0 = one chunk)
+  const uint32_t* ready_flags;   // local [world][CG_MAXC]: flag[s][c] >= ready_epoch once rank s has
+                                 // pushed chunk c of its rows (unchunked pushes use c = 0 only)
   uint32_t ready_epoch;
   // ---- ack of a consumed gathered operand
   uint32_t* const* ack_ptrs;     // per rank: pointer to its [world] ack words
@@ -85,7 +88,8 @@ struct CommGemmArgs {
   long long push_dst_ld;
   long long push_dst_row0[3];    // first destination row of each segment (same in every peer)
   int push_to_self;
-  uint32_t* const* push_flag_ptrs;   // per rank: its [world] ready words
+  long long push_chunk_rows;     // plain copies: rows per progress chunk (0 = the whole push)
+  uint32_t* const* push_flag_ptrs;   // per rank: its [world][CG_MAXC] ready words
   uint32_t push_epoch;
   const uint32_t* push_wait_acks;    // local [world] ack words to wait for before overwriting
   uint32_t push_wait_epoch;          // (0 = do not wait)
@@ -98,8 +102,8 @@ struct CommGemmArgs {
   const __half* gauss_table;
   // ---- bookkeeping
   int rank, world;
-  unsigned int* counters;        // local [2 + world]: pushers done, gemm CTAs done, pushers done per
-                                 // destination (all monotonic)
+  unsigned int* counters;        // local [2 + CG_MAXC]: pushers done, gemm CTAs done, pushers done per
+                                 // progress chunk (all monotonic)
   unsigned int push_target, gemm_target;
   uint32_t* err;
 };
@@ -135,12 +139,27 @@ __device__ __forceinline__ bool cg_wait_flag(const uint32_t* p, uint32_t epoch, 
 // Tiles are visited source by source, own rows first.
 __device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, int& mb, int& nb) {
   if (p.gather == 1) {
+    // own rows first; then chunk by chunk, and inside a chunk source by source in the order
+    // rank+1, rank+2, ...: every source pushes its chunk c to all ranks before chunk c+1, so
+    // this is the order in which the rows arrive
     const int mbs = p.rows_per_src / CG_BM;          // row tiles per source
     const int per_src = mbs * p.num_n;
-    int s = tile / per_src, r = tile - s * per_src;
-    int src = (p.rank + s) % p.world;
-    mb = src * mbs + r / p.num_n;
-    nb = r % p.num_n;
+    if (tile < per_src) {
+      mb = p.rank * mbs + tile / p.num_n;
+      nb = tile % p.num_n;
+    } else {
+      const int ct = p.chunk_tiles > 0 ? p.chunk_tiles : mbs;
+      const int per_cs = ct * p.num_n;               // tiles of one (chunk, source)
+      const int per_c = per_cs * (p.world - 1);
+      int t = tile - per_src;
+      int c = t / per_c;
+      t -= c * per_c;
+      int s = t / per_cs + 1;
+      t -= (s - 1) * per_cs;
+      int src = (p.rank + s) % p.world;
+      mb = src * mbs + c * ct + t / p.num_n;
+      nb = t % p.num_n;
+    }
   } else {
     int gm = p.num_m < 16 ? p.num_m : 16;
     int tiles_per_group = gm * p.num_n;
@@ -155,6 +174,7 @@ __device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, 
 
 __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* smem_raw) {
   __shared__ int s_go;
+  __shared__ int s_first_idle;     // first chunk counter this launch leaves untouched
   // stage the inverse-CDF table when the pushed rows are perturbed
   const __half* tab = nullptr;
   if (p.push_perturb) {
@@ -163,7 +183,7 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
     for (int i = threadIdx.x; i < GAUSS_TABLE_SIZE * 2 / 16; i += CG_THREADS) dst[i] = __ldg(src + i);
     tab = reinterpret_cast<const __half*>(smem_raw);
   }
-  if (threadIdx.x == 0) s_go = 1;
+  if (threadIdx.x == 0) { s_go = 1; s_first_idle = 0; }
   __syncthreads();
   // the peers must have consumed what this buffer held before
   if (p.push_wait_epoch != 0 && (int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
@@ -178,44 +198,57 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
     const long long v0 = (long long)blockIdx.x * per;
     const long long v1 = min(v0 + per, total);
     if (!p.push_perturb) {
-      // Plain copy: one destination after the other, nearest consumer first (rank d consumes the
-      // rows of d+1, d+2, ... in that order), and each destination's ready flag goes up as soon
-      // as ITS copy is complete, so consumers start on the first source while the rest travels.
-      // The source is re-read per destination; it sits in L2.
-      for (int sdst = 1; sdst <= p.world; ++sdst) {
-        const int d = (p.rank - sdst + 2 * p.world) % p.world;
-        const bool skip = (d == p.rank && !p.push_to_self);   // counters advance all the same
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]);
-        for (long long base = v0; base < v1 && !skip; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
+      // Plain copy, chunk by chunk: `push_chunk_rows` rows of every segment go to all destinations
+      // (each 16-byte vector is loaded once and stored to every peer, nearest consumer first:
+      // rank d reads the rows of d+1, d+2, ... in that order), then that chunk's ready flag goes up
+      // everywhere, so consumers multiply chunk c while chunk c+1 travels.
+      const long long crows = p.push_chunk_rows > 0 ? p.push_chunk_rows : p.push_rows;
+      const int nchunks = (int)((p.push_rows + crows - 1) / crows);
+      for (int c = 0; c < nchunks; ++c) {
+        const long long row_lo = (long long)c * crows;
+        const long long rows_c = min(crows, p.push_rows - row_lo);
+        const long long seg_c = rows_c * vec_per_row;
+        const long long total_c = seg_c * p.push_nseg;
+        const long long per_c = (total_c + p.n_push - 1) / p.n_push;
+        const long long c0 = (long long)blockIdx.x * per_c;
+        const long long c1 = min(c0 + per_c, total_c);
+        for (long long base = c0; base < c1; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
           uint4 raw[CG_PUSH_UNROLL];
           long long doff[CG_PUSH_UNROLL];
           bool live[CG_PUSH_UNROLL];
 #pragma unroll
           for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
             const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
-            live[u] = vv < v1;
+            live[u] = vv < c1;
             if (live[u]) {
-              const int seg = (int)(vv / seg_total);
-              const long long v = vv - seg * seg_total;
-              const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
-              raw[u] = *reinterpret_cast<const uint4*>(p.push_src[seg] + r * p.push_ld + c);
-              doff[u] = (p.push_dst_row0[seg] + r) * p.push_dst_ld + c;
+              const int seg = (int)(vv / seg_c);
+              const long long v = vv - seg * seg_c;
+              const long long r = row_lo + v / vec_per_row, cc = (v % vec_per_row) << 3;
+              raw[u] = *reinterpret_cast<const uint4*>(p.push_src[seg] + r * p.push_ld + cc);
+              doff[u] = (p.push_dst_row0[seg] + r) * p.push_dst_ld + cc;
             }
           }
+          for (int sdst = 1; sdst <= p.world; ++sdst) {
+            const int d = (p.rank - sdst + 2 * p.world) % p.world;
+            if (d == p.rank && !p.push_to_self) continue;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]);
 #pragma unroll
-          for (int u = 0; u < CG_PUSH_UNROLL; ++u)
-            if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
+            for (int u = 0; u < CG_PUSH_UNROLL; ++u)
+              if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
+          }
         }
         __threadfence_system();
         __syncthreads();
         if (threadIdx.x == 0) {
-          unsigned int old = atomicAdd(p.counters + 2 + d, 1u);
+          unsigned int old = atomicAdd(p.counters + 2 + c, 1u);
           if (old + 1u == p.push_target) {
             __threadfence_system();
-            cg_st_release_sys(p.push_flag_ptrs[d] + p.rank, p.push_epoch);
+            for (int d = 0; d < p.world; ++d)
+              cg_st_release_sys(p.push_flag_ptrs[d] + p.rank * CG_MAXC + c, p.push_epoch);
           }
         }
       }
+      s_first_idle = nchunks;
     } else {
     // Perturbed push: z is generated once per element, then stored to every destination.
     // CG_PUSH_UNROLL independent 16-byte loads per thread are in flight before the first store:
@@ -271,12 +304,12 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned int old = atomicAdd(p.counters + 0, 1u);
-    // the per-destination counters of the copy path stay in step with the common one
-    if (p.push_perturb || !s_go)
-      for (int d = 0; d < p.world; ++d) atomicAdd(p.counters + 2 + d, 1u);
+    // the chunk counters this launch did not use stay in step with the common one
+    for (int c = s_first_idle; c < CG_MAXC; ++c) atomicAdd(p.counters + 2 + c, 1u);
     if (old + 1u == p.push_target && s_go && p.push_perturb) {
       __threadfence_system();
-      for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.push_flag_ptrs[d] + p.rank, p.push_epoch);
+      for (int d = 0; d < p.world; ++d)
+        cg_st_release_sys(p.push_flag_ptrs[d] + p.rank * CG_MAXC, p.push_epoch);
     }
   }
 }
@@ -346,9 +379,14 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             long long q = p.src_period ? rr % p.src_period : rr;
             int src = (int)(q / p.rows_per_src);
             if (src >= p.world) src = p.world - 1;
-            if ((src != p.rank || p.wait_self) && !(seen & (1u << src))) {
-              if (!cg_wait_flag(p.ready_flags + src, p.ready_epoch, &s_abort, p.err)) { ok = false; break; }
-              seen |= 1u << src;
+            const bool chunked = p.gather == 1 && p.chunk_tiles > 0;
+            const int chunk = chunked ? (int)((q % p.rows_per_src) / CG_BM) / p.chunk_tiles : 0;
+            if ((src != p.rank || p.wait_self) && (chunked || !(seen & (1u << src)))) {
+              if (!cg_wait_flag(p.ready_flags + src * CG_MAXC + chunk, p.ready_epoch, &s_abort, p.err)) {
+                ok = false;
+                break;
+              }
+              if (!chunked) seen |= 1u << src;
               fenced = false;
             }
             rr += p.rows_per_src - (q % p.rows_per_src);      // first row of the next owner
@@ -589,6 +627,7 @@ struct DzCommGemmDesc {
   // bookkeeping
   int rank, world; void* counters; unsigned int push_target, gemm_target;
   int gemm_ctas;                 // 0 = all remaining SMs
+  int chunk_rows;                // all-gather -> GEMM: rows per progress chunk of a source (0 = one chunk)
 };
 
 extern "C" int dz_comm_gemm_desc_bytes() { return (int)sizeof(DzCommGemmDesc); }
@@ -650,6 +689,16 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.push_rows = d->push_rows; a.push_cols = d->push_cols;
   a.push_dst_ptrs = (void* const*)d->push_dst_ptrs; a.push_dst_ld = d->push_dst_ld;
   a.push_to_self = d->push_to_self;
+  if (d->chunk_rows > 0) {
+    // chunks are whole row tiles, at most CG_MAXC of them per source
+    if (d->chunk_rows % CG_BM || d->push_perturb) return DZ_ERR_ARG;
+    if (d->n_push > 0 && (d->push_rows + d->chunk_rows - 1) / d->chunk_rows > CG_MAXC) return DZ_ERR_ARG;
+    if (has_gemm && d->gather == 1 &&
+        (d->rows_per_src % d->chunk_rows || d->rows_per_src / d->chunk_rows > CG_MAXC))
+      return DZ_ERR_ARG;
+    a.push_chunk_rows = d->chunk_rows;
+    a.chunk_tiles = d->chunk_rows / CG_BM;
+  }
   a.push_flag_ptrs = (uint32_t* const*)d->push_flag_ptrs; a.push_epoch = d->push_epoch;
   a.push_wait_acks = (const uint32_t*)d->push_wait_acks; a.push_wait_epoch = d->push_wait_epoch;
   a.push_perturb = d->push_perturb; a.push_seed = d->push_seed; a.push_coef = d->push_coef;

@@ -57,8 +57,11 @@ class _Desc(ctypes.Structure):
         ("push_perturb", c_int), ("push_seed", ctypes.c_ulonglong), ("push_coef", c_float),
         ("push_tensor_id", c_int * 3), ("push_elem_base", c_ll * 3), ("gauss_table", c_void),
         ("rank", c_int), ("world", c_int), ("counters", c_void), ("push_target", c_uint),
-        ("gemm_target", c_uint), ("gemm_ctas", c_int),
+        ("gemm_target", c_uint), ("gemm_ctas", c_int), ("chunk_rows", c_int),
     ]
+
+
+MAX_CHUNKS = 16      # progress chunks per source (CG_MAXC of comm_gemm.cu)
 
 
 class _Channel:
@@ -67,7 +70,7 @@ class _Channel:
     def __init__(self, region: SymmRegion, nbytes: int):
         self.region = region
         self.off, self.view, self.ptrs = region.alloc(nbytes)
-        _, rv, self.ready_ptrs = region.alloc(4 * region.world)
+        _, rv, self.ready_ptrs = region.alloc(4 * region.world * MAX_CHUNKS)
         _, av, self.ack_ptrs = region.alloc(4 * region.world)
         self.ready = rv.view(torch.int32)
         self.ack = av.view(torch.int32)
@@ -98,7 +101,7 @@ class FusedComm:
         self.norm_mc_local = mv.view(torch.float32)
         _, fv, self.norm_flag_ptrs = self.region.alloc(4 * self.world)
         self.norm_epoch = 0
-        self.counters = torch.zeros(2 + self.world, dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros(2 + MAX_CHUNKS, dtype=torch.int32, device=self.device)
         self._push_total = 0
         self._gemm_total = 0
         self._calls = {"ag": 0, "rs": 0, "w": 0}
@@ -106,6 +109,7 @@ class FusedComm:
     # ------------------------------------------------------------------ helpers
     def _launch(self, d: _Desc, push: bool, M: int, N: int) -> None:
         L = _lib.lib()
+        assert ctypes.sizeof(_Desc) == L.dz_comm_gemm_desc_bytes(), "launch descriptor out of step with the library"
         d.rank, d.world = self.rank, self.world
         d.counters = self.counters.data_ptr()
         if push:
@@ -167,6 +171,10 @@ class FusedComm:
         d.push_dst_row0[0] = self.rank * rows
         d.push_flag_ptrs, d.push_epoch = ch.ready_ptrs.data_ptr(), ch.epoch
         d.push_wait_acks, d.push_wait_epoch = ch.ack.data_ptr(), prev
+        # progress chunks: whole 128-row tiles, as fine as the flag words allow
+        tiles = rows // 128
+        ct = next(c for c in range(1, tiles + 1) if tiles % c == 0 and tiles // c <= MAX_CHUNKS)
+        d.chunk_rows = ct * 128 if self.world > 2 and tiles > 1 else 0
         self._launch(d, True, M, N)
         return out
 

@@ -52,9 +52,14 @@ def attention_reference(qkv: torch.Tensor, n_heads: int, pad_left: torch.Tensor 
 
 def attention(qkv: torch.Tensor, n_heads: int, pad_left: torch.Tensor | None = None,
               prefix_k: torch.Tensor | None = None, prefix_v: torch.Tensor | None = None,
-              scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """qkv [B, L, 3d] bf16 (row stride may exceed 3d) -> context [B, L, d] bf16."""
+              scale: float | None = None, out: torch.Tensor | None = None,
+              lse: torch.Tensor | None = None) -> torch.Tensor:
+    """qkv [B, L, 3d] bf16 (row stride may exceed 3d) -> context [B, L, d] bf16.
+
+    ``lse``: optional fp32 [B, H, L] that receives every query row's log-sum-exp (log2 domain of
+    the scaled scores), the statistic :func:`attention_backward` needs."""
     if not qkv.is_cuda:
+        assert lse is None, "the CPU statement differentiates through autograd instead"
         return attention_reference(qkv, n_heads, pad_left, prefix_k, prefix_v, scale)
     assert qkv.dtype == torch.bfloat16 and qkv.dim() == 3 and qkv.stride(-1) == 1
     B, L, d3 = qkv.shape
@@ -73,14 +78,58 @@ def attention(qkv: torch.Tensor, n_heads: int, pad_left: torch.Tensor | None = N
         assert prefix_v.stride(0) == ldp
     if pad_left is not None:
         assert pad_left.dtype == torch.int32 and pad_left.is_cuda
-    rc = _lib.lib().dz_attn_fwd(
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.is_contiguous() and lse.shape == (B, n_heads, L)
+    rc = _lib.lib().dz_attn_fwd_lse(
         _lib.ptr(qkv), ctypes.c_longlong(qkv.stride(1)), 0, d, 2 * d,
         _lib.ptr(out), ctypes.c_longlong(out.stride(1)), _lib.ptr(pad_left),
         _lib.ptr(prefix_k), _lib.ptr(prefix_v), ctypes.c_longlong(ldp), npre,
-        B, L, n_heads, hd, ctypes.c_float(scale), _lib.ptr(_lib.err_word(qkv.device)),
+        B, L, n_heads, hd, ctypes.c_float(scale), _lib.ptr(lse), _lib.ptr(_lib.err_word(qkv.device)),
         _lib.stream_ptr())
-    _lib.check(rc, "dz_attn_fwd")
+    _lib.check(rc, "dz_attn_fwd_lse")
     return out
+
+
+def attention_backward_reference(qkv: torch.Tensor, dout: torch.Tensor, n_heads: int,
+                                 pad_left: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
+    """d loss / d qkv for d loss / d context = ``dout``: autograd through the fp32 statement."""
+    with torch.enable_grad():
+        x = qkv.detach().float().requires_grad_(True)
+        o = attention_reference(x, n_heads, pad_left, None, None, scale)
+        (g,) = torch.autograd.grad(o, x, dout.float())
+    return g.to(qkv.dtype)
+
+
+def attention_backward(qkv: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor,
+                       n_heads: int, pad_left: torch.Tensor | None = None, scale: float | None = None,
+                       dqkv: torch.Tensor | None = None) -> torch.Tensor:
+    """Gradient of :func:`attention` (no prefix rows): qkv [B, L, 3d], its context ``out`` and
+    ``dout`` [B, L, d] (bf16), ``lse`` from the forward -> dqkv [B, L, 3d] bf16 (dQ | dK | dV).
+
+    CUDA: the two tcgen05 passes of ``csrc/attn_bwd_sm100.cu``.  Replaces the autograd pass over
+    the reference's eager attention (large_models/ht_opt.py:209-272) in the first-order gamma
+    search (large_models/trainer.py:714-741)."""
+    if not qkv.is_cuda:
+        return attention_backward_reference(qkv, dout, n_heads, pad_left, scale)
+    B, L, d3 = qkv.shape
+    d = d3 // 3
+    hd = d // n_heads
+    scale = scale if scale is not None else hd ** -0.5
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and dout.dtype == torch.bfloat16
+    assert qkv.stride(-1) == 1 and qkv.stride(0) == L * qkv.stride(1)
+    assert out.is_contiguous() and dout.is_contiguous() and out.shape == (B, L, d) == dout.shape
+    assert lse.dtype == torch.float32 and lse.is_contiguous() and lse.shape == (B, n_heads, L)
+    if dqkv is None:
+        dqkv = torch.empty((B, L, 3 * d), dtype=torch.bfloat16, device=qkv.device)
+    assert dqkv.stride(-1) == 1 and dqkv.stride(0) == L * dqkv.stride(1)
+    dsum = torch.empty((B, n_heads, L), dtype=torch.float32, device=qkv.device)
+    rc = _lib.lib().dz_attn_bwd(
+        _lib.ptr(qkv), ctypes.c_longlong(qkv.stride(1)), 0, d, 2 * d,
+        _lib.ptr(out), _lib.ptr(dout), ctypes.c_longlong(d), _lib.ptr(lse), _lib.ptr(dsum),
+        _lib.ptr(dqkv), ctypes.c_longlong(dqkv.stride(1)), _lib.ptr(pad_left),
+        B, L, n_heads, hd, ctypes.c_float(scale), _lib.ptr(_lib.err_word(qkv.device)), _lib.stream_ptr())
+    _lib.check(rc, "dz_attn_bwd")
+    return dqkv
 
 
 def decode_attention_reference(q, k_cache, v_cache, kv_len, n_heads, pad_left=None,

@@ -39,6 +39,7 @@ struct AttnArgs {
   long long ld_out;          // row stride of the context output (elements)
   __nv_bfloat16* out;        // [B*L, ld_out], head h at columns [h*hd, (h+1)*hd)
   const int* pad_left;       // [B] or null
+  float* lse;                // [B, H, L] or null: log2-domain log-sum-exp of every query row
   float scale_log2;          // softmax scale * log2(e)
   int q_col0, k_col0, v_col0;  // first column of the Q / K / V sections inside the QKV rows
   uint32_t* err;
@@ -323,6 +324,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
         const bool row_ok = qi < p.L;
+        if (p.lse && row_ok)
+          p.lse[((long long)b * p.H + h) * p.L + qi] = l_sum > 0.f ? m_used + log2f(l_sum) : 0.f;
         __nv_bfloat16* orow = p.out + ((long long)b * p.L + qi) * p.ld_out + h * hd;
         // all accumulator columns in one TMEM round trip (hd is a multiple of 16, <= 128)
         uint32_t o[128];
@@ -383,10 +386,12 @@ using namespace dz;
 // qkv: [B*L, ld_qkv] bf16 with Q at columns [q_col0, q_col0 + H*hd), K at k_col0, V at v_col0.
 // out: [B*L, ld_out] bf16.  prefix_k / prefix_v: [n_prefix, ld_prefix] bf16 or null.
 // hd in {64, 80, 96, 112, 128} (multiple of 16, at most 128); at most 128 prefix rows.
-extern "C" int dz_attn_fwd(const void* qkv, long long ld_qkv, int q_col0, int k_col0, int v_col0,
-                           void* out, long long ld_out, const int* pad_left, const void* prefix_k,
-                           const void* prefix_v, long long ld_prefix, int n_prefix, int B, int L,
-                           int H, int hd, float scale, uint32_t* err, cudaStream_t stream) {
+// lse: optional [B, H, L] fp32 output, m + log2(sum) of every query row in the log2 domain of the
+// scaled scores (what dz_attn_bwd reads).
+extern "C" int dz_attn_fwd_lse(const void* qkv, long long ld_qkv, int q_col0, int k_col0, int v_col0,
+                               void* out, long long ld_out, const int* pad_left, const void* prefix_k,
+                               const void* prefix_v, long long ld_prefix, int n_prefix, int B, int L,
+                               int H, int hd, float scale, float* lse, uint32_t* err, cudaStream_t stream) {
   if (!qkv || !out || B <= 0 || L <= 0 || H <= 0) return DZ_ERR_ARG;
   if (hd < 16 || hd > 128 || (hd & 15)) return DZ_ERR_ARG;
   if (n_prefix < 0 || n_prefix > A_BKV || (n_prefix > 0 && (!prefix_k || !prefix_v)))
@@ -413,9 +418,17 @@ extern "C" int dz_attn_fwd(const void* qkv, long long ld_qkv, int q_col0, int k_
   }
   AttnArgs a{};
   a.B = B; a.L = L; a.H = H; a.hd = hd; a.n_prefix = n_prefix; a.ld_out = ld_out;
-  a.out = (__nv_bfloat16*)out; a.pad_left = pad_left;
+  a.out = (__nv_bfloat16*)out; a.pad_left = pad_left; a.lse = lse;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.q_col0 = q_col0; a.k_col0 = k_col0; a.v_col0 = v_col0; a.err = err;
   if (hdp == 64) return launch_attn<64>(tmQ, tmKV, tmPK, tmPV, a, stream);
   return launch_attn<128>(tmQ, tmKV, tmPK, tmPV, a, stream);
+}
+
+extern "C" int dz_attn_fwd(const void* qkv, long long ld_qkv, int q_col0, int k_col0, int v_col0,
+                           void* out, long long ld_out, const int* pad_left, const void* prefix_k,
+                           const void* prefix_v, long long ld_prefix, int n_prefix, int B, int L,
+                           int H, int hd, float scale, uint32_t* err, cudaStream_t stream) {
+  return dz_attn_fwd_lse(qkv, ld_qkv, q_col0, k_col0, v_col0, out, ld_out, pad_left, prefix_k, prefix_v,
+                         ld_prefix, n_prefix, B, L, H, hd, scale, nullptr, err, stream);
 }

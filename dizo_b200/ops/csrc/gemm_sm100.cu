@@ -41,6 +41,8 @@ struct GemmArgs {
   const __nv_bfloat16* bias;      // [N] or null
   const __nv_bfloat16* residual;  // [M, ldr] or null
   long long ldr;
+  const __nv_bfloat16* mask;      // [M, ldm] or null: the result is zeroed where mask <= 0 (ReLU backward)
+  long long ldm;
   int act;
   int out_fp32;
   float out_scale;      // multiplies (acc + bias) before activation/residual
@@ -72,7 +74,10 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmArgs& p, int& mb
   nb = r / gm;
 }
 
-template <int BN, int STAGES, int EPI>
+// B_MN = false: W is [N, K] row-major (out = A W^T, both operands K-major).
+// B_MN = true : W is [K, N] row-major (out = A W, the data-gradient form dX = dY W of a linear
+//               layer): the B operand is MN-major, staged as 64-column panels of [64 k-rows][128 B].
+template <int BN, int STAGES, int EPI, bool B_MN = false>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmArgs p) {
@@ -134,7 +139,13 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint32_t b_dst = a_dst + S::A_BYTES;
           mbar_arrive_expect_tx(full, S::STAGE_BYTES);
           tma_load_2d(a_dst, &tmA, full, kb * G_BK, mb * G_BM);
-          tma_load_2d(b_dst, &tmB, full, kb * G_BK, nb * BN);
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(b_dst + c * (G_BK * 128), &tmB, full, nb * BN + c * 64, kb * G_BK);
+          } else {
+            tma_load_2d(b_dst, &tmB, full, kb * G_BK, nb * BN);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -142,7 +153,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(G_BM, BN);
+      constexpr uint32_t idesc = umma_idesc_bf16(G_BM, BN, 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -169,7 +180,13 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int k = 0; k < G_BK / 16; ++k) {
             // advancing 16 bf16 along K inside the 128-byte swizzle row = +32 bytes
-            umma_bf16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+            if (B_MN) {
+              // 16 k-rows = two 8-row groups of 1024 bytes; 64-column panels are G_BK*128 bytes apart
+              umma_bf16_ss(d_tmem, a_desc + 2 * k, umma_desc_mn_sw128(b_src + k * 2048, G_BK * 128, 1024),
+                           idesc, (kb | k) != 0);
+            } else {
+              umma_bf16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+            }
           }
           umma_commit(smem_u32(&bar_empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -241,6 +258,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
           }
           if (row_ok) {
+            if (p.mask) {
+              const __nv_bfloat16* mp = p.mask + row * p.ldm + col0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N && !(__bfloat162float(mp[j]) > 0.f)) v[j] = 0.f;
+            }
             if (p.residual) {
               const __nv_bfloat16* rp = p.residual + row * p.ldr + col0;
               if (full_chunk) {
@@ -341,11 +364,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool B_MN = false>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs& a,
                        cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
-  auto kern = gemm_bf16_tn_kernel<BN, STAGES, EPI>;
+  auto kern = gemm_bf16_tn_kernel<BN, STAGES, EPI, B_MN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -410,6 +433,36 @@ extern "C" int dz_gemm_bf16_tn(const void* A, long long lda, const void* W, long
   rc = make_tmap_bf16_2d(&tmB, W, N, K, ldw, 256, G_BK, true);
   if (rc) return rc;
   return launch_gemm<256, 4, EPI_STORE>(tmA, tmB, a, stream);
+}
+
+// out[M,N] = (A W) masked + residual with W [K, N] row-major: the data gradient dX = dY W of a
+// linear layer whose weight is stored [out_features, in_features], read in place (no transposed
+// copy).  mask [M, ldm] (optional): entries whose mask is <= 0 become 0 (the ReLU backward of the
+// layer below, fused); residual [M, ldr] (optional) is added afterwards (gradient accumulation).
+// Replaces the autograd matmul backward of large_models/ht_opt.py:178-197, :356-359 in the
+// first-order gamma search (large_models/trainer.py:714-741).
+extern "C" int dz_gemm_bf16_nn(const void* A, long long lda, const void* W, long long ldw, void* out,
+                               long long ldo, const void* residual, long long ldr, const void* mask,
+                               long long ldm, int M, int N, int K, int out_fp32, uint32_t* err,
+                               cudaStream_t stream) {
+  if (!A || !W || !out || M <= 0 || N <= 0 || K <= 0) return DZ_ERR_ARG;
+  if ((K & 7) || (N & 7) || (lda & 7) || (ldw & 7)) return DZ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return DZ_ERR_ALIGN;
+  int esz = out_fp32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || ((ldo * esz) & 15)) return DZ_ERR_ALIGN;
+  if (residual && ((reinterpret_cast<uintptr_t>(residual) & 15) || (ldr & 7))) return DZ_ERR_ALIGN;
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K;
+  a.out = out; a.ldo = ldo;
+  a.residual = reinterpret_cast<const __nv_bfloat16*>(residual); a.ldr = ldr;
+  a.mask = reinterpret_cast<const __nv_bfloat16*>(mask); a.ldm = ldm;
+  a.act = ACT_NONE; a.out_fp32 = out_fp32; a.out_scale = 1.0f; a.err = err;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, G_BM, G_BK, true);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tmB, W, K, N, ldw, G_BK, 64, true);      // box: 64 k-rows x 64 columns
+  if (rc) return rc;
+  return launch_gemm<256, 4, EPI_STORE, true>(tmA, tmB, a, stream);
 }
 
 // Fused logits + log-sum-exp partials: for every row r of A, over columns n of W:

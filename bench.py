@@ -41,7 +41,8 @@ def parse():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--mode", default="full", help="full | lora | prefix | lora+prefix")
     ap.add_argument("--zo-mode", default="inflight", choices=["inflight", "inplace"])
-    ap.add_argument("--enhanced", default="zo", choices=["none", "zo"])
+    ap.add_argument("--enhanced", default="zo", choices=["none", "zo", "fo"],
+                    help="DiZO gamma search: zeroth-order (the headline), first-order, or off (plain MeZO)")
     ap.add_argument("--overlap", action="store_true", help="sweep the next layer on a side stream")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "fsdp", "tp"],
                     help="dp: replicated parameters, per-rank batches (default); fsdp: row-sharded weights, "
@@ -157,7 +158,7 @@ def run_ours(a, world, rank, local):
     model.init_random_fast(seed=0)
     dp_group = False if par == "tp" else None
     engine = ZOEngine(model, eps=1e-3, mode=a.zo_mode, dp_group=dp_group)
-    projector = DiZOProjector(model, dp_group=dp_group) if a.enhanced == "zo" else None
+    projector = DiZOProjector(model, dp_group=dp_group) if a.enhanced != "none" else None
     data_rank = 0 if par == "tp" else rank            # tensor parallel: one global batch
     lr0, max_steps = 1e-6, 20000
     V = cfg.vocab_size
@@ -195,11 +196,13 @@ def run_ours(a, world, rank, local):
     if projector is not None:
         it = iter(range(10 ** 9))
         nb = lambda: resident[next(it) % n_res]
-        projector.search_zo(nb, seed=7)          # warm
+        search = (lambda sd: projector.search_zo(nb, seed=sd)) if a.enhanced == "zo" else \
+                 (lambda sd: projector.search_fo(nb))
+        search(7)                                # warm
         barrier(world)
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s0.record()
-        projector.search_zo(nb, seed=8)
+        search(8)
         s1.record()
         barrier(world)
         search_ms = max_over_ranks(s0.elapsed_time(s1), world)

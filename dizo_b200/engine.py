@@ -123,6 +123,8 @@ class DiZOProjector:
         # FO state persists across searches (large_models/trainer.py:401, :761)
         self.fo_gamma: torch.Tensor | None = None
         self.fo_opt = None
+        self.use_kernel_backward = True      # False: always differentiate through the autograd statement
+        self._gamma_grad = None
 
     def _reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.dp_group is not False and _dist_on(self.dp_group):
@@ -169,11 +171,16 @@ class DiZOProjector:
         if self.n:
             self.model.arena.sweep(alpha=self.gs.alpha)
 
-    def search_fo(self, next_batch: Callable[[], Batch], fo_loss: Callable) -> None:
+    def search_fo(self, next_batch: Callable[[], Batch], fo_loss: Callable | None = None) -> None:
         """``dizo_iters``: Adam on gamma through d loss / d gamma (gamma starts at 0 and, like
-        its Adam moments, persists across searches; L1 penalty ``l1 * sum |gamma|``)."""
+        its Adam moments, persists across searches; L1 penalty ``l1 * sum |gamma|``).
+
+        d loss / d alpha comes from the kernel backward (:class:`models.gamma_grad.GammaGrad`)
+        where the configuration is covered; otherwise from ``fo_loss(batch, alpha)``, an autograd
+        statement of the forward (:func:`models.opt_autograd.make_fo_loss`)."""
         if self.n == 0:
             return
+        from .models import gamma_grad
         self.measure()
         gs = self.gs
         self._begin(reinit=False)
@@ -181,12 +188,23 @@ class DiZOProjector:
             self.fo_gamma = torch.zeros(self.n, dtype=torch.float32, device=self.model.device,
                                         requires_grad=True)
             self.fo_opt = torch.optim.Adam([self.fo_gamma], lr=self.proj_lr)
+        native = fo_loss is None or (self.use_kernel_backward and gamma_grad.supported(self.model))
+        if native and self._gamma_grad is None:
+            self._gamma_grad = gamma_grad.GammaGrad(self.model)
         for _ in range(self.max_iters):
             batch = next_batch()
             self.fo_opt.zero_grad(set_to_none=True)
-            alpha = self.fo_gamma / (gs.ts.detach() + 1e-8)
-            loss = fo_loss(batch, alpha) + self.l1 * self.fo_gamma.abs().sum()
-            loss.backward()
+            if native:
+                with torch.no_grad():
+                    ts = gs.ts[:self.n] + 1e-8
+                    alpha = torch.zeros_like(gs.alpha)
+                    alpha[:self.n] = self.fo_gamma.detach() / ts
+                    _, g_alpha = self._gamma_grad.loss_and_grad(batch, alpha)
+                    self.fo_gamma.grad = g_alpha / ts + self.l1 * torch.sign(self.fo_gamma.detach())
+            else:
+                alpha = self.fo_gamma / (gs.ts.detach() + 1e-8)
+                loss = fo_loss(batch, alpha) + self.l1 * self.fo_gamma.abs().sum()
+                loss.backward()
             if _dist_on(self.dp_group):
                 dist.all_reduce(self.fo_gamma.grad, group=self.dp_group)
                 self.fo_gamma.grad.div_(dist.get_world_size(self.dp_group))

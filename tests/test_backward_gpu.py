@@ -143,3 +143,41 @@ def test_dot_scatter_diff():
     _sync_ok()
     assert torch.equal(dst[idx.long()], src) and dst[1].abs().sum().item() == 0
     assert torch.equal(df, (x.float() - y.float()).bfloat16())
+
+
+@pytest.mark.parametrize("kind", ["verbalizer", "lm"])
+def test_gamma_grad_kernel_backward_matches_autograd(kind):
+    """d loss / d alpha over a 12-layer bf16 model: kernel forward + backward against autograd
+    through the PyTorch statement of the same forward."""
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import DiZOProjector
+    from dizo_b200.models.gamma_grad import GammaGrad
+    from dizo_b200.models.opt import OPTModel, preset
+    from dizo_b200.models.opt_autograd import make_fo_loss
+
+    cfg = preset("opt-125m")
+    m = OPTModel(cfg, DEV, torch.bfloat16, mode="full").init_random_fast(seed=0)
+    proj = DiZOProjector(m)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    for n in m.arena.slot_names:
+        p = m.param(n)
+        p.add_((torch.randn(p.shape, device=DEV, generator=g) * 0.02).to(p.dtype))
+    b = synthetic_batch(0, 2, 160, cfg.vocab_size, seed=1, pad_left=17).to(DEV)
+    if kind == "lm":
+        B, L = b.input_ids.shape
+        rows = torch.cat([torch.arange(40, L - 1) + i * L for i in range(B)]).to(torch.int32).to(DEV)
+        b.rows = rows
+        b.targets = b.input_ids.reshape(-1)[(rows + 1).long()].contiguous()
+        b.cand_ids = None
+        b.classification = False
+        b.seq_start = torch.tensor([0, rows.numel()], dtype=torch.int32, device=DEV)
+    alpha = torch.rand(proj.n, device=DEV, generator=g) * 0.5 + 0.5
+    loss, grad = GammaGrad(m).loss_and_grad(b, alpha)
+    _sync_ok()
+    a = alpha.clone().requires_grad_(True)
+    ref_loss = make_fo_loss(m)(b, a)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 3e-2 * max(1.0, abs(ref_loss.item()))
+    cos = torch.nn.functional.cosine_similarity(grad, a.grad.float(), dim=0).item()
+    assert cos > 0.98, (cos, grad, a.grad)
+    assert _rel(grad, a.grad) < 0.2

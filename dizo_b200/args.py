@@ -135,7 +135,8 @@ class OurArguments:
     zo_mode: str = "inflight"               # inflight (theta never rewritten for a forward) | inplace
     zo_stochastic_rounding: bool = False    # unbiased bf16 update
     dp: int = 0                             # data-parallel ranks (0 = WORLD_SIZE)
-    tp: int = 1                             # tensor-parallel ranks
+    tp: int = 1                             # tensor-parallel ranks (1, or the number of ranks)
+    tp_max_tokens: int = 32768              # largest batch x padded length a tensor-parallel forward takes
     fsdp_shard: bool = False                # shard parameters over the data-parallel group
     eval_batch_size: int = 16               # candidates scored per forward in evaluation
     synthetic_task: bool = False            # seeded uniform ids + Bernoulli labels (no dataset)

@@ -100,17 +100,18 @@ class FSDPOPTModel(OPTModel):
                 del full
         return self
 
+    def gather_full(self, name: str, local: torch.Tensor) -> torch.Tensor:
+        """The unsharded tensor ``name`` from every rank's rows ``local`` (cold path, NCCL)."""
+        t = local.contiguous()
+        if not self._sharded(name):
+            return t.clone()
+        parts = [torch.empty_like(t) for _ in range(self.n)]
+        dist.all_gather(parts, t, group=self.group)
+        return torch.cat(parts, dim=0)
+
     def gather_state_dict(self) -> dict:
         """Full Hugging Face state dict on every rank (cold path: checkpoints, tests; NCCL)."""
-        sd = {}
-        for n in self.hf_order:
-            t = self.param(n).contiguous()
-            if not self._sharded(n):
-                sd[n] = t.clone()
-                continue
-            parts = [torch.empty_like(t) for _ in range(self.n)]
-            dist.all_gather(parts, t, group=self.group)
-            sd[n] = torch.cat(parts, dim=0)
+        sd = {n: self.gather_full(n, self.param(n)) for n in self.hf_order}
         if not self.untied:
             sd["lm_head.weight"] = sd[_P + "embed_tokens.weight"]
         return sd

@@ -111,18 +111,19 @@ class TPOPTModel(OPTModel):
                 del full
         return self
 
+    def gather_full(self, name: str, local: torch.Tensor) -> torch.Tensor:
+        """The unsharded tensor ``name`` from every rank's part ``local`` (cold path, NCCL)."""
+        k = self._kind(name)
+        t = local.contiguous()
+        if k == "rep":
+            return t.clone()
+        parts = [torch.empty_like(t) for _ in range(self.tp)]
+        dist.all_gather(parts, t, group=self.group)
+        return torch.cat(parts, dim=1 if k == "col" else 0)
+
     def gather_state_dict(self) -> dict:
         """Full (unsharded) Hugging Face state dict, assembled on every rank (cold path, NCCL)."""
-        sd = {}
-        for n in self.hf_order:
-            t = self.param(n).contiguous()
-            k = self._kind(n)
-            if k == "rep":
-                sd[n] = t.clone()
-                continue
-            parts = [torch.empty_like(t) for _ in range(self.tp)]
-            dist.all_gather(parts, t, group=self.group)
-            sd[n] = torch.cat(parts, dim=1 if k == "col" else 0)
+        sd = {n: self.gather_full(n, self.param(n)) for n in self.hf_order}
         if not self.untied:
             sd["lm_head.weight"] = sd[_P + "embed_tokens.weight"]
         return sd
@@ -135,6 +136,7 @@ class TPOPTModel(OPTModel):
         cfg, fc = self.config, self.comm
         nl, n, r = cfg.num_hidden_layers, self.tp, self.tp_rank
         d = cfg.hidden_size
+        batch = self._fit(batch)
         B, L = batch.input_ids.shape
         M = B * L
         assert M % (n * 128) == 0 and M <= self.max_tokens, "token rows must split into 128-row tiles per rank"
@@ -185,6 +187,31 @@ class TPOPTModel(OPTModel):
         self._rows_local = (r * rows, (r + 1) * rows)
         return h
 
+    def _fit(self, batch: Batch) -> Batch:
+        """Pad a batch so that its token rows split into 128-row tiles per rank: the length grows
+        on the left to a multiple of 128, and all-padding sequences are appended until the tile count
+        divides by the number of ranks.  Row indices of the caller are translated in ``final_rows``."""
+        B, L = batch.input_ids.shape
+        n = self.tp
+        Lp = -(-L // 128) * 128
+        Bp = B
+        while (Bp * (Lp // 128)) % n:
+            Bp += 1
+        self._row_map = None
+        if Lp == L and Bp == B:
+            return batch
+        dev = batch.input_ids.device
+        ids = torch.ones((Bp, Lp), dtype=batch.input_ids.dtype, device=dev)
+        pos = torch.ones((Bp, Lp), dtype=batch.positions.dtype, device=dev)
+        ids[:B, Lp - L:] = batch.input_ids
+        pos[:B, Lp - L:] = batch.positions
+        pad = torch.full((Bp,), Lp, dtype=torch.int32, device=dev)
+        old = batch.pad_left if batch.pad_left is not None else torch.zeros(B, dtype=torch.int32, device=dev)
+        pad[:B] = old + (Lp - L)
+        self._row_map = (L, Lp)
+        import dataclasses
+        return dataclasses.replace(batch, input_ids=ids, positions=pos, pad_left=pad)
+
     @torch.no_grad()
     def final_rows(self, h: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Final LayerNorm of the requested global rows, replicated on every rank: each rank fills
@@ -192,6 +219,9 @@ class TPOPTModel(OPTModel):
         cfg = self.config
         lo, hi = self._rows_local
         rows_l = rows.long()
+        if self._row_map is not None:                  # indices into the caller's unpadded batch
+            L0, Lp = self._row_map
+            rows_l = (rows_l // L0) * Lp + rows_l % L0 + (Lp - L0)
         own = (rows_l >= lo) & (rows_l < hi)
         local_idx = torch.where(own, rows_l - lo, torch.zeros_like(rows_l)).to(torch.int32)
         x = norm.gather_rows(h, local_idx)

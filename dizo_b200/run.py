@@ -102,8 +102,24 @@ class Framework:
                 mode = "lora"
             elif a.prefix_tuning:
                 mode = "prefix"
-            model = OPTModel(cfg, self.device, self._dtype(), mode=mode, lora_r=a.lora_r,
-                             lora_alpha=a.lora_alpha, num_prefix=a.num_prefix, untie_emb=a.untie_emb)
+            world = torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
+            self.dp_group = None                      # None: the default group, when there is one
+            if a.tp > 1 or a.fsdp_shard:
+                # sharded layouts (full-parameter ZO, fused collectives over NVLink peer memory)
+                assert mode == "full" and self.device.type == "cuda" and world > 1, \
+                    "--tp / --fsdp_shard need full-parameter mode on >= 2 GPUs"
+                if a.tp > 1:
+                    assert a.tp == world, "--tp must equal the number of ranks (one tensor-parallel group)"
+                    from .parallel.tp import TPOPTModel
+                    model = TPOPTModel(cfg, self.device, self._dtype(),
+                                       max_tokens=a.tp_max_tokens, untie_emb=a.untie_emb)
+                    self.dp_group = False             # every rank sees the same batch
+                else:
+                    from .parallel.fsdp import FSDPOPTModel
+                    model = FSDPOPTModel(cfg, self.device, self._dtype(), untie_emb=a.untie_emb)
+            else:
+                model = OPTModel(cfg, self.device, self._dtype(), mode=mode, lora_r=a.lora_r,
+                                 lora_alpha=a.lora_alpha, num_prefix=a.num_prefix, untie_emb=a.untie_emb)
             if state is not None:
                 model.init_random(a.seed)          # adapters; base weights are overwritten below
                 model.load_state_dict(state, strict=False)
@@ -183,7 +199,8 @@ class Framework:
         else:
             collator = DataCollatorForTokenClassification(self.tokenizer, pad_to_multiple_of=8)
         trainer = OurTrainer(model=self.model, args=a, train_dataset=train_dataset, eval_dataset=eval_samples,
-                             processing_class=self.tokenizer, data_collator=collator, task=self.task)
+                             processing_class=self.tokenizer, data_collator=collator, task=self.task,
+                             dp_group=getattr(self, "dp_group", None))
         if a.save_on_interrupt:
             trainer.add_callback(SIGUSR1Callback())
         last = None

@@ -32,7 +32,7 @@ from .engine import DiZOProjector, ZOEngine
 from .metrics import calculate_metric, f1
 from .models.opt import Batch, OPTModel, Transform
 from .utils import TrainerCallback, TrainerControl
-from .utils.checkpoint import load_checkpoint, save_checkpoint
+from .utils.checkpoint import full_state_dict, load_checkpoint, save_checkpoint
 
 logger = logging.getLogger(__name__)
 
@@ -121,6 +121,9 @@ class OurTrainer:
         self._metrics_f = None
         on = dist.is_available() and dist.is_initialized() and dp_group is not False
         self._rank = dist.get_rank(dp_group) if on else 0
+        # the one process that writes files (under tensor parallelism every rank has data rank 0)
+        self._writer = (dist.get_rank() == 0) if (dist.is_available() and dist.is_initialized()) else True
+        self._sharded = hasattr(model, "gather_state_dict")
         self._world = dist.get_world_size(dp_group) if on else 1
 
     # ------------------------------------------------------------------ small API
@@ -324,7 +327,7 @@ class OurTrainer:
     def _in_loop_eval(self) -> None:
         a = self.args
         path = "loss_acc/{}_{}_{}_enhanced_{}".format(a.task_name, a.trainer, "lora" if a.lora else "ft", a.enhanced)
-        if self._rank == 0:
+        if self._writer:
             os.makedirs(path, exist_ok=True)
             np.save(f"{path}/loss_list_seed_{a.seed}.npy", self.loss_list)
         if self.eval_dataset is None or len(self.eval_dataset) == 0 or self.task is None:
@@ -334,29 +337,30 @@ class OurTrainer:
         metrics["global_step"] = self.state.global_step
         logger.info(f"Eval results: {metrics}")
         self.accuracy.append(metrics[name])
-        if self._rank == 0:
+        if self._writer:
             np.save(f"{path}/accuracy_seed_{a.seed}.npy", self.accuracy)
         if metrics[name] >= self.objective:
             logger.info("Best dev result: {}".format(metrics[name]))
             self.objective = metrics[name]
             self.state.best_metric = float(metrics[name])
             # kept in host memory, and actually restorable (load_best_model_at_end)
-            self.best_model_ckpt = {k: v.detach().cpu() for k, v in self.model.state_dict().items()}
+            self.best_model_ckpt = {k: v.detach().cpu() for k, v in full_state_dict(self.model).items()}
 
     # ------------------------------------------------------------------ checkpoints
     def save_model(self, output_dir: Optional[str] = None) -> None:
         """Hugging Face layout: ``model.safetensors`` (or ``pytorch_model.bin``) + ``config.json``."""
         out = output_dir or self.args.output_dir
-        if self._rank == 0:
-            save_checkpoint(out, self.model, trainer=None)
+        if self._writer or self._sharded:
+            save_checkpoint(out, self.model, trainer=None, write=self._writer)
 
     def _save_checkpoint(self) -> str:
         out = os.path.join(self.args.output_dir, f"checkpoint-{self.state.global_step}")
-        if self._rank == 0:
-            save_checkpoint(out, self.model, trainer=self)
+        if self._writer or self._sharded:
+            save_checkpoint(out, self.model, trainer=self, write=self._writer)
+        if self._writer:
             self._rotate_checkpoints()
-        if self._world > 1:
-            dist.barrier(self.dp_group)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
         return out
 
     def _rotate_checkpoints(self) -> None:
@@ -385,7 +389,7 @@ class OurTrainer:
         if resume_from_checkpoint:
             load_checkpoint(resume_from_checkpoint, self.model, trainer=self)
             logger.info("Resumed from %s at step %d", resume_from_checkpoint, self.state.global_step)
-        if a.metrics_jsonl and self._rank == 0:
+        if a.metrics_jsonl and self._writer:
             self._metrics_f = open(a.metrics_jsonl, "a")
         logger.info("***** Running training *****")
         logger.info(f"  Num examples = {n}")

@@ -113,9 +113,29 @@ def load_weights(path: str) -> dict:
     raise CheckpointError(f"{path}: no model.safetensors / pytorch_model.bin")
 
 
-def save_checkpoint(out: str, model, trainer=None) -> None:
+def full_state_dict(model) -> dict:
+    """Unsharded Hugging Face state dict.  Sharded models (tensor parallel, FSDP) assemble it with
+    collectives: every rank of the model's group must call this."""
+    if hasattr(model, "gather_state_dict"):
+        return model.gather_state_dict()
+    return model.state_dict()
+
+
+def save_checkpoint(out: str, model, trainer=None, write: bool = True) -> None:
+    """Write a checkpoint directory.  With a sharded model every rank calls this (the gathers are
+    collective) and only the rank with ``write`` touches the file system; the files hold full
+    tensors, so a checkpoint can be resumed under a different parallel layout."""
+    sd = full_state_dict(model)
+    ar = model.arena
+    anchor = None
+    if trainer is not None and trainer.dizo_trainer is not None:
+        gather = getattr(model, "gather_full", None)
+        anchor = {n: (gather(n, ar.anchor_view(n)) if gather else ar.anchor_view(n)).detach().cpu().clone()
+                  for n in ar.slot_names}
+    if not write:
+        return
     os.makedirs(out, exist_ok=True)
-    save_weights(out, model.state_dict())
+    save_weights(out, sd)
     with open(os.path.join(out, "config.json"), "w") as f:
         json.dump(model.config.to_hf_dict(), f, indent=2)
     if trainer is not None:
@@ -128,8 +148,7 @@ def save_checkpoint(out: str, model, trainer=None) -> None:
             zo["dizo_i"] = trainer.dizo_trainer.i
             zo["pgm_count"] = trainer._pgm_count
             zo["dizo_seed_rng"] = trainer._dizo_seed_rng.get_state()
-            ar = model.arena
-            zo["anchor"] = {n: ar.anchor_view(n).detach().cpu().clone() for n in ar.slot_names}
+            zo["anchor"] = anchor
         torch.save(zo, os.path.join(out, "zo_state.pt"))
     _write_manifest(out)
 
@@ -161,7 +180,7 @@ def load_checkpoint(path: str, model, trainer=None, verify: bool = True) -> None
             trainer._dizo_seed_rng.set_state(zo["dizo_seed_rng"])
             ar = model.arena
             for n, t in zo.get("anchor", {}).items():
-                ar.anchor_view(n).copy_(t.to(ar.dtype))
+                ar.anchor_view(n).copy_(model.local_slice(n, t).to(ar.dtype))
 
 
 _CKPT_RE = re.compile(r"^checkpoint-(\d+)$")

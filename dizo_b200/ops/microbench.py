@@ -6,6 +6,8 @@ seconds, which is what a long training step sees under the power cap).
     python -m dizo_b200.ops.microbench attn --batch 8 --seq 1024 --heads 40 --hd 128
     python -m dizo_b200.ops.microbench sweep --mib 2048 [--flags z2,blend,norm,sr]
     python -m dizo_b200.ops.microbench layernorm --rows 8192 --d 5120
+    python -m dizo_b200.ops.microbench dgrad --m 8192 --n 5120 --k 20480      # dX = dY W, W [k, n]
+    python -m dizo_b200.ops.microbench attn_bwd --batch 8 --seq 1024 --heads 40 --hd 128
 
 Each run prints one JSON line with achieved TFLOP/s or GB/s and the fraction of the measured
 peak found in MEASURED_PEAKS.json at the repository root (if present).  ``--only ours`` skips the
@@ -68,7 +70,7 @@ def time_fn(fn, iters=20, warmup=3, seconds=0.0, flush=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn", "sweep", "layernorm"])
+    ap.add_argument("kernel", choices=["gemm", "dgrad", "attn", "attn_bwd", "sweep", "layernorm"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -102,6 +104,44 @@ def main():
             out.update(ours_ms=ms, ours_tflops=fl / ms / 1e9, ours_frac_of_measured=fl / ms / 1e9 / peak)
         if a.only != "ours":
             ms = time_fn(lambda: torch.matmul(x, w.t(), out=y), a.iters, seconds=a.seconds, flush=flush)
+            out.update(lib_ms=ms, lib_tflops=fl / ms / 1e9)
+    elif a.kernel == "dgrad":
+        from .backward import linear_dgrad
+        dy = torch.randn(a.m, a.k, device=dev, generator=g).bfloat16()
+        w = (torch.randn(a.k, a.n, device=dev, generator=g) * 0.02).bfloat16()
+        fl = 2.0 * a.m * a.n * a.k
+        peak = peaks["bf16_tflops_sustained" if a.seconds else "bf16_tflops"]
+        out.update(shape=[a.m, a.n, a.k])
+        if a.only != "lib":
+            ms = time_fn(lambda: linear_dgrad(dy, w), a.iters, seconds=a.seconds, flush=flush)
+            out.update(ours_ms=ms, ours_tflops=fl / ms / 1e9, ours_frac_of_measured=fl / ms / 1e9 / peak)
+        if a.only != "ours":
+            ms = time_fn(lambda: torch.matmul(dy, w), a.iters, seconds=a.seconds, flush=flush)
+            out.update(lib_ms=ms, lib_tflops=fl / ms / 1e9)
+    elif a.kernel == "attn_bwd":
+        from .attention import attention_backward
+        d = a.heads * a.hd
+        qkv = torch.randn(a.batch, a.seq, 3 * d, device=dev, generator=g).bfloat16()
+        do = torch.randn(a.batch, a.seq, d, device=dev, generator=g).bfloat16()
+        lse = torch.empty(a.batch, a.heads, a.seq, dtype=torch.float32, device=dev)
+        o = attention(qkv, a.heads, lse=lse)
+        dqkv = torch.empty_like(qkv)
+        # useful work: 5 GEMM-shaped products over the causal half (the two-pass kernel executes 7)
+        fl = 10.0 * a.batch * a.heads * a.seq * a.seq * a.hd / 2
+        out.update(shape=[a.batch, a.seq, a.heads, a.hd])
+        if a.only != "lib":
+            ms = time_fn(lambda: attention_backward(qkv, o, do, lse, a.heads, dqkv=dqkv), a.iters,
+                         seconds=a.seconds, flush=flush)
+            out.update(ours_ms=ms, ours_tflops=fl / ms / 1e9,
+                       ours_frac_of_measured=fl / ms / 1e9 / peaks["bf16_tflops"])
+        if a.only != "ours":
+            q, k, v = (t.view(a.batch, a.seq, a.heads, a.hd).transpose(1, 2).detach().requires_grad_(True)
+                       for t in qkv.split(d, dim=-1))
+            with torch.enable_grad():
+                so = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+            gso = do.view(a.batch, a.seq, a.heads, a.hd).transpose(1, 2)
+            ms = time_fn(lambda: torch.autograd.grad(so, (q, k, v), gso, retain_graph=True), a.iters,
+                         seconds=a.seconds, flush=flush)
             out.update(lib_ms=ms, lib_tflops=fl / ms / 1e9)
     elif a.kernel == "attn":
         d = a.heads * a.hd

@@ -44,7 +44,7 @@ def parse():
     ap.add_argument("--enhanced", default="zo", choices=["none", "zo", "fo"],
                     help="DiZO gamma search: zeroth-order (the headline), first-order, or off (plain MeZO)")
     ap.add_argument("--overlap", action="store_true", help="sweep the next layer on a side stream")
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "fsdp", "tp"],
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "fsdp", "tp", "pp"],
                     help="dp: replicated parameters, per-rank batches (default); fsdp: row-sharded weights, "
                          "fused gather+perturb+GEMM; tp: tensor parallel with fused AG->GEMM / GEMM->RS "
                          "(one global batch of --prompts x --seq)")
@@ -153,13 +153,16 @@ def run_ours(a, world, rank, local):
     elif par == "tp":
         from dizo_b200.parallel.tp import TPOPTModel
         model = TPOPTModel(cfg, dev, max_tokens=a.prompts * a.seq)
+    elif par == "pp":
+        from dizo_b200.parallel.pp import PPOPTModel
+        model = PPOPTModel(cfg, dev)
     else:
         model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=a.overlap)
     model.init_random_fast(seed=0)
-    dp_group = False if par == "tp" else None
+    dp_group = False if par in ("tp", "pp") else None
     engine = ZOEngine(model, eps=1e-3, mode=a.zo_mode, dp_group=dp_group)
     projector = DiZOProjector(model, dp_group=dp_group) if a.enhanced != "none" else None
-    data_rank = 0 if par == "tp" else rank            # tensor parallel: one global batch
+    data_rank = 0 if par in ("tp", "pp") else rank   # tensor / pipeline parallel: one global batch
     lr0, max_steps = 1e-6, 20000
     V = cfg.vocab_size
 
@@ -209,7 +212,7 @@ def run_ours(a, world, rank, local):
     clocks = sampler.stop() if rank == 0 else None
     _lib.check_device_errors()
     ms = step_ms + search_ms / 50.0
-    tokens = a.prompts * a.seq * (1 if par == "tp" else world)
+    tokens = a.prompts * a.seq * (1 if par in ("tp", "pp") else world)
 
     # ---- end to end through the public trainer call: pinned H2D of each step's inputs,
     #      the step, D2H read of its loss

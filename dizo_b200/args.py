@@ -137,6 +137,8 @@ class OurArguments:
     dp: int = 0                             # data-parallel ranks (0 = WORLD_SIZE)
     tp: int = 1                             # tensor-parallel ranks (1, or the number of ranks)
     tp_max_tokens: int = 32768              # largest batch x padded length a tensor-parallel forward takes
+    pp: int = 1                             # pipeline stages (1, or the number of ranks)
+    pp_micro_batches: int = 0               # micro-batches per forward (0 = one per stage)
     fsdp_shard: bool = False                # shard parameters over the data-parallel group
     eval_batch_size: int = 16               # candidates scored per forward in evaluation
     synthetic_task: bool = False            # seeded uniform ids + Bernoulli labels (no dataset)

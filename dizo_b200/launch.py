@@ -11,7 +11,7 @@ accumulation steps), builds the argument list for :mod:`dizo_b200.run` and runs 
 process for one GPU, through ``torch.distributed.run`` (one process per GPU, rendezvous on
 127.0.0.1) for ``NUM_GPU`` > 1.  Extra command-line arguments are passed through.
 
-Additions: ``PARALLEL`` in {dp, fsdp, tp} selects the multi-GPU layout of the ZO recipes (the
+Additions: ``PARALLEL`` in {dp, fsdp, tp, pp} selects the multi-GPU layout of the ZO recipes (the
 reference has none), and ``finetune_fsdp`` maps to the sharded layout of this framework.
 """
 from __future__ import annotations
@@ -71,8 +71,10 @@ def build_argv(recipe: str, env: Mapping[str, str]) -> List[str]:
             argv += ["--tp", str(n)]
         elif par == "fsdp" and n > 1:
             argv += ["--fsdp_shard"]
+        elif par == "pp" and n > 1:
+            argv += ["--pp", str(n)]
         elif par != "dp" and n > 1:
-            raise ValueError(f"PARALLEL must be dp, fsdp or tp, not {par!r}")
+            raise ValueError(f"PARALLEL must be dp, fsdp, tp or pp, not {par!r}")
     elif recipe in ("finetune", "finetune_fsdp"):
         fsdp = recipe == "finetune_fsdp"
         epoch, bs, lr, seed = e("EPOCH", 5), int(e("BS", 8)), e("LR", "1e-5"), e("SEED", 0)

@@ -239,7 +239,7 @@ class OPTModel:
         canon = [n for n, _, _ in base] + ["lm_head.weight"] + \
                 [n for n, _, _ in adapter_param_specs(config, 8, 5)]
         self.tensor_ids = {n: i for i, n in enumerate(canon)}
-        self.all_specs = base + extra + adapters
+        self.all_specs = [sp for sp in base + extra + adapters if self.owns(sp[0])]
         self.hf_order = [n for n, _, _ in self.all_specs]
         self.trainable_names = self._select_trainable()
         tset = set(self.trainable_names)
@@ -261,7 +261,12 @@ class OPTModel:
         self._merge_buf: dict = {}
         self.kv_capture: list | None = None      # set to [] to record per-layer qkv (generation)
 
-    # ------------------------------------------------------------------ sharding hook
+    # ------------------------------------------------------------------ sharding hooks
+    def owns(self, name: str) -> bool:
+        """Whether this rank holds parameter ``name`` at all (pipeline stages hold only their own
+        blocks; every other layout holds at least a part of every tensor)."""
+        return True
+
     def shard_of(self, name: str, shape: tuple) -> tuple[tuple, dict]:
         """(local shape, Piece keywords) of this rank's part of a parameter.  The base model
         holds every parameter whole; tensor- and fully-sharded-parallel subclasses override."""

@@ -65,6 +65,7 @@ struct CommGemmArgs {
                                  // (fused q|k|v: d); 0 = no repetition
   int wait_self;                 // own rows are also produced by this launch's push role
   int chunk_tiles;               // gather 1: row tiles per progress chunk of a source (0 = one chunk)
+  int join_tiles;                // tiles at the end of the order left to the push CTAs (0 = none)
   const uint32_t* ready_flags;   // local [world][CG_MAXC]: flag[s][c] >= ready_epoch once rank s has
                                  // pushed chunk c of its rows (unchunked pushes use c = 0 only)
   uint32_t ready_epoch;
@@ -326,17 +327,24 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
 
-  if ((int)blockIdx.x < p.n_push) {
+  // Push CTAs finish their copy long before the GEMM CTAs finish their tiles; with join_tiles > 0
+  // they then take the LAST join_tiles tiles of the tile order (the rows that arrive last anyway)
+  // instead of leaving their SMs idle.
+  const bool pusher = (int)blockIdx.x < p.n_push;
+  if (pusher) {
     cg_push_role(p, smem_raw);
-    return;
+    if (p.join_tiles <= 0) return;
+    __syncthreads();
   }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int num_tiles = p.num_m * p.num_n;
   const int num_kb = (p.K + CG_BK - 1) / CG_BK;
-  const int cta = blockIdx.x - p.n_push;
-  const int n_cta = gridDim.x - p.n_push;
+  const int reg_tiles = p.num_m * p.num_n - p.join_tiles;      // tiles of the CTAs that only multiply
+  const int cta = pusher ? reg_tiles + (int)blockIdx.x : (int)blockIdx.x - p.n_push;
+  const int n_cta = pusher ? p.n_push : (int)gridDim.x - p.n_push;
+  const int tile_end = pusher ? num_tiles : reg_tiles;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -367,7 +375,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       uint32_t seen = 0;      // bit s set: source s is known to have arrived
-      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+      for (int tile = cta; tile < tile_end && ok; tile += n_cta) {
         int mb, nb;
         cg_tile_coords(tile, p, mb, nb);
         if (p.gather) {
@@ -418,7 +426,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+      for (int tile = cta; tile < tile_end && ok; tile += n_cta) {
         if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1, &s_abort, p.err,
                        ERR_WAIT_TMEM_EMPTY)) {
           ok = false;
@@ -454,7 +462,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t out_stage = smem_base + CG_STAGES * CG_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = cta; tile < num_tiles; tile += n_cta) {
+    for (int tile = cta; tile < tile_end; tile += n_cta) {
       int mb, nb;
       cg_tile_coords(tile, p, mb, nb);
       if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &s_abort, p.err, ERR_WAIT_TMEM_FULL))
@@ -628,6 +636,7 @@ struct DzCommGemmDesc {
   int rank, world; void* counters; unsigned int push_target, gemm_target;
   int gemm_ctas;                 // 0 = all remaining SMs
   int chunk_rows;                // all-gather -> GEMM: rows per progress chunk of a source (0 = one chunk)
+  int join_tiles;                // tiles the push CTAs multiply after pushing (0 = they exit)
 };
 
 extern "C" int dz_comm_gemm_desc_bytes() { return (int)sizeof(DzCommGemmDesc); }
@@ -721,9 +730,12 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
     int tiles = a.num_m * a.num_n;
     int avail = sm_count() - a.n_push;
     if (avail < 1) return DZ_ERR_ARG;
+    int join = (a.n_push > 0 && d->join_tiles > 0) ? d->join_tiles : 0;
+    if (join >= tiles) return DZ_ERR_ARG;
+    a.join_tiles = join;
     gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : avail;
     if (gemm_ctas > avail) gemm_ctas = avail;
-    if (gemm_ctas > tiles) gemm_ctas = tiles;
+    if (gemm_ctas > tiles - join) gemm_ctas = tiles - join;
   }
   // every CTA must be resident at once (the roles wait on one another through flags)
   if (a.n_push + gemm_ctas > sm_count()) return DZ_ERR_TOO_LARGE;
@@ -734,8 +746,9 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   return cuda_rc(cudaGetLastError());
 }
 
-extern "C" int dz_comm_gemm_ctas(int M, int N, int n_push) {
-  int tiles = ((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
+// CTAs that only multiply, for a launch of this shape whose push CTAs take join_tiles tiles themselves
+extern "C" int dz_comm_gemm_ctas(int M, int N, int n_push, int join_tiles) {
+  int tiles = ((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN) - (join_tiles > 0 ? join_tiles : 0);
   int avail = sm_count() - n_push;
   return tiles < avail ? tiles : avail;
 }

@@ -57,10 +57,11 @@ class _Desc(ctypes.Structure):
         ("push_perturb", c_int), ("push_seed", ctypes.c_ulonglong), ("push_coef", c_float),
         ("push_tensor_id", c_int * 3), ("push_elem_base", c_ll * 3), ("gauss_table", c_void),
         ("rank", c_int), ("world", c_int), ("counters", c_void), ("push_target", c_uint),
-        ("gemm_target", c_uint), ("gemm_ctas", c_int), ("chunk_rows", c_int),
+        ("gemm_target", c_uint), ("gemm_ctas", c_int), ("chunk_rows", c_int), ("join_tiles", c_int),
     ]
 
 
+_SM_COUNT = 148       # B200
 MAX_CHUNKS = 16      # progress chunks per source (CG_MAXC of comm_gemm.cu)
 
 
@@ -89,6 +90,7 @@ class FusedComm:
         self.region = SymmRegion(total + 16 * 4096, self.group, device)
         self.device = self.region.device
         self.n_push = n_push
+        self.join = True          # push CTAs multiply tail tiles once their copy is out
         self.ag = [_Channel(self.region, ag_bytes) for _ in range(2)] if ag_bytes else []
         self.rs = [_Channel(self.region, rs_bytes) for _ in range(2)] if rs_bytes else []
         self.wst = [_Channel(self.region, w_bytes) for _ in range(2)] if w_bytes else []
@@ -119,12 +121,31 @@ class FusedComm:
         else:
             d.n_push = 0
         if M > 0:
-            ctas = L.dz_comm_gemm_ctas(M, N, d.n_push)
-            self._gemm_total += ctas
+            join = self._join_tiles(d, M, N) if (push and self.join) else 0
+            ctas = L.dz_comm_gemm_ctas(M, N, d.n_push, join)
+            d.join_tiles = join
+            self._gemm_total += ctas + (d.n_push if join else 0)
             d.gemm_target = self._gemm_total & 0xFFFFFFFF
             d.gemm_ctas = ctas
         rc = L.dz_comm_gemm(ctypes.byref(d), _lib.ptr(_lib.err_word(self.device)), _lib.stream_ptr())
         _lib.check(rc, "dz_comm_gemm")
+
+    def _join_tiles(self, d: _Desc, M: int, N: int) -> int:
+        """How many tiles at the end of the tile order the push CTAs take after their copy, so that
+        they and the CTAs that only multiply finish together.  Estimated from the bytes pushed (at the
+        rate a handful of CTAs reaches over NVLink) and the tensor-core time of one 128x256 tile."""
+        if d.push_perturb:
+            return 0                                   # the perturbing push keeps its CTAs busy
+        tiles = -(-M // 128) * -(-N // 256)
+        P = self.n_push
+        G = min(_SM_COUNT - P, tiles)
+        if tiles <= G + P:
+            return 0
+        t_tile = 2.0 * 128 * 256 * d.K / 8.0e12                               # seconds on one SM
+        out_bytes = d.push_nseg * d.push_rows * d.push_cols * 2 * max(1, self.world - 1)
+        tau = out_bytes / 350e9
+        j = (tiles / G - tau / t_tile) / (1.0 / G + 1.0 / P)
+        return int(max(0, min(0.8 * j, tiles - G)))
 
     def barrier(self) -> None:
         """All ranks have reached this point of their current streams (P2P flags, bounded wait)."""

@@ -104,7 +104,16 @@ class Framework:
                 mode = "prefix"
             world = torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
             self.dp_group = None                      # None: the default group, when there is one
-            if a.tp > 1 or a.fsdp_shard:
+            if a.pp > 1:
+                # consecutive blocks on consecutive ranks; every rank sees the same batch
+                assert a.pp == world, "--pp must equal the number of ranks (one pipeline)"
+                assert a.enhanced != "fo", "the first-order gamma search is not staged over a pipeline"
+                from .parallel.pp import PPOPTModel
+                model = PPOPTModel(cfg, self.device, self._dtype(), micro_batches=a.pp_micro_batches, mode=mode,
+                                   lora_r=a.lora_r, lora_alpha=a.lora_alpha, num_prefix=a.num_prefix,
+                                   untie_emb=a.untie_emb)
+                self.dp_group = False
+            elif a.tp > 1 or a.fsdp_shard:
                 # sharded layouts (full-parameter ZO, fused collectives over NVLink peer memory)
                 assert mode == "full" and self.device.type == "cuda" and world > 1, \
                     "--tp / --fsdp_shard need full-parameter mode on >= 2 GPUs"

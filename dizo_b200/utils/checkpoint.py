@@ -132,6 +132,8 @@ def save_checkpoint(out: str, model, trainer=None, write: bool = True) -> None:
         gather = getattr(model, "gather_full", None)
         anchor = {n: (gather(n, ar.anchor_view(n)) if gather else ar.anchor_view(n)).detach().cpu().clone()
                   for n in ar.slot_names}
+        if hasattr(model, "gather_dict"):              # pipeline stages hold disjoint sets of tensors
+            anchor = model.gather_dict(anchor)
     if not write:
         return
     os.makedirs(out, exist_ok=True)
@@ -180,7 +182,8 @@ def load_checkpoint(path: str, model, trainer=None, verify: bool = True) -> None
             trainer._dizo_seed_rng.set_state(zo["dizo_seed_rng"])
             ar = model.arena
             for n, t in zo.get("anchor", {}).items():
-                ar.anchor_view(n).copy_(model.local_slice(n, t).to(ar.dtype))
+                if n in ar.index:                      # a pipeline stage restores its own tensors only
+                    ar.anchor_view(n).copy_(model.local_slice(n, t).to(ar.dtype))
 
 
 _CKPT_RE = re.compile(r"^checkpoint-(\d+)$")

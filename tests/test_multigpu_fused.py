@@ -42,9 +42,9 @@ def test_fsdp_model_matches_unsharded():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("layout", [("--tp", "2"), ("--fsdp_shard",), ()])
+@pytest.mark.parametrize("layout", [("--tp", "2"), ("--fsdp_shard",), ("--pp", "2"), ()])
 def test_cli_training_on_two_gpus(tmp_path, layout):
-    """The command-line entry under tensor parallelism, FSDP sharding and plain data parallelism:
+    """The command-line entry under tensor parallelism, FSDP sharding, a pipeline and plain data parallelism:
     DiZO steps, in-loop evaluation, a checkpoint with full (unsharded) tensors, final metrics."""
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     out = tmp_path / "out"

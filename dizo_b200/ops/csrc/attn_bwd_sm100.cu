@@ -19,15 +19,16 @@
 // the epilogue (dQ, dK).  Masking is the forward's: key j visible to query i iff j <= i and
 // (j >= pad_left or j == i).
 //
-// Warps 0-3: one thread per stationary row (softmax arithmetic, epilogue); warp 4: TMEM
-// allocation, lane 0 issues tcgen05.mma; warp 5: lane 0 is the TMA producer.
+// Warps 0-7: softmax arithmetic and epilogue - a thread owns one stationary row and one 64-column
+// half of the streamed tile (warps w and w+4 share a TMEM lane quadrant and split the columns);
+// warp 8: TMEM allocation, lane 0 issues tcgen05.mma; warp 9: lane 0 is the TMA producer.
 #include "common.cuh"
 #include "host_util.h"
 
 namespace dz {
 
 constexpr int AB_T = 128;          // rows of a stationary or streamed tile
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;
 constexpr int AB_STAGES = 2;
 
 struct AttnBwdArgs {
@@ -63,7 +64,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   __shared__ __align__(8) uint64_t bar_x;
   __shared__ __align__(8) uint64_t bar_y_full[AB_STAGES], bar_y_empty[AB_STAGES];
   __shared__ __align__(8) uint64_t bar_s, bar_ds, bar_acc;
-  __shared__ float s_lse[4][AB_T], s_dsum[4][AB_T];     // per softmax warp: statistics of the streamed rows
+  __shared__ float4 s_stat[8][32];      // per softmax warp: {lse, D, lse, D} of its 64 streamed rows, two per entry
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
 
@@ -96,11 +97,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       mbar_init(smem_u32(&bar_y_empty[s]), 1);
     }
     mbar_init(smem_u32(&bar_s), 1);
-    mbar_init(smem_u32(&bar_ds), 4);
+    mbar_init(smem_u32(&bar_ds), 8);
     mbar_init(smem_u32(&bar_acc), 1);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(smem_u32(&s_tmem_base), 512);
     tmem_relinquish();
   }
@@ -112,7 +113,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128u;
   const uint32_t tm_acc1 = tmem_base + 256u, tm_acc2 = tmem_base + 384u;
 
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0 && n_it > 0) {
       // ---------------------------------------------- TMA producer
       // stationary: X1 = Q_i | K_j,  X2 = dO_i | V_j
@@ -147,7 +148,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     if (lane == 0 && n_it > 0) {
       // ---------------------------------------------- MMA issuer
       const uint32_t idesc_s = umma_idesc_bf16(AB_T, AB_T, 0, 0);
@@ -178,17 +179,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         // contraction over the 128 streamed rows: 16 rows = 8 packed TMEM columns of the A operand
-        // and two 8-row groups (1024 bytes each) of the MN-major B operand
+        // (rows 0-63 packed at columns [0,32), rows 64-127 at [64,96)) and two 8-row groups
+        // (1024 bytes each) of the MN-major B operand
         for (int kk = 0; kk < AB_T / 16; ++kk) {
           if (!DQ) {
             // dV_j += P^T dO_i
-            umma_bf16_ts(tm_acc1, tm_s + kk * 8, umma_desc_mn_sw128(y2 + kk * 2048, AB_T * 128, 1024),
-                         idesc_acc, (it | kk) != 0);
+            umma_bf16_ts(tm_acc1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8,
+                         umma_desc_mn_sw128(y2 + kk * 2048, AB_T * 128, 1024), idesc_acc, (it | kk) != 0);
           }
         }
         for (int kk = 0; kk < AB_T / 16; ++kk) {
           // dK_j += dS^T Q_i   |   dQ_i += dS K_j
-          umma_bf16_ts(DQ ? tm_acc1 : tm_acc2, tm_dp + kk * 8,
+          umma_bf16_ts(DQ ? tm_acc1 : tm_acc2, tm_dp + (kk >> 2) * 64 + (kk & 3) * 8,
                        umma_desc_mn_sw128(y1 + kk * 2048, AB_T * 128, 1024), idesc_acc, (it | kk) != 0);
         }
         umma_commit(smem_u32(&bar_y_empty[st]));
@@ -196,10 +198,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       if (ok) umma_commit(smem_u32(&bar_acc));
     }
   } else {
-    // ---------------------------------------------- softmax arithmetic, one thread per stationary row
-    const int r = warp * 32 + lane;
+    // ---------------------------------------------- softmax arithmetic: one stationary row, 64 columns
+    const int quad = warp & 3;                              // TMEM lane quadrant
+    const int half = warp >> 2;                             // which 64 streamed rows (columns of S)
+    const int r = quad * 32 + lane;
     const int xi = x0 + r;                                  // key index (DQ false) | query index (DQ true)
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const long long stat_base = ((long long)b * p.H + h) * p.L;
     float my_lse = 0.f, my_dsum = 0.f;
     if (DQ && xi < p.L) {
@@ -212,10 +216,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       if (!DQ) {
         // statistics of the streamed query rows, one private copy per warp (the __syncwarp that
         // ends every iteration orders these writes after the previous iteration's reads)
-        for (int c = lane; c < AB_T; c += 32) {
-          const int qi = y0 + c;
-          s_lse[warp][c] = qi < p.L ? p.lse[stat_base + qi] : 0.f;
-          s_dsum[warp][c] = qi < p.L ? p.dsum[stat_base + qi] : 0.f;
+        {
+          const int q0 = y0 + half * 64 + lane * 2;
+          float4 st;
+          st.x = q0 < p.L ? p.lse[stat_base + q0] : 0.f;
+          st.y = q0 < p.L ? p.dsum[stat_base + q0] : 0.f;
+          st.z = q0 + 1 < p.L ? p.lse[stat_base + q0 + 1] : 0.f;
+          st.w = q0 + 1 < p.L ? p.dsum[stat_base + q0 + 1] : 0.f;
+          s_stat[warp][lane] = st;
         }
         __syncwarp();
       }
@@ -223,10 +231,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);          // leave the loop as a whole warp
       if (!ok) break;
       tc_fence_after();
-      const float* lse_c = s_lse[warp];
-      const float* ds_c = s_dsum[warp];
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t sv[64], dv[64];
         tmem_ld_32x32(tm_s + lane_off + half * 64, sv);
         tmem_ld_32x32(tm_s + lane_off + half * 64 + 32, sv + 32);
@@ -236,14 +241,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
           float pr[2], dsv[2];
+          float4 st = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (!DQ) st = s_stat[warp][c >> 1];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int yi = y0 + half * 64 + c + u;
             const int kv = DQ ? yi : xi;
             const int qi = DQ ? xi : yi;
             const bool vis = (kv <= qi) && (kv >= pad || kv == qi) && (qi < p.L);
-            const float l = DQ ? my_lse : lse_c[half * 64 + c + u];
-            const float dd = DQ ? my_dsum : ds_c[half * 64 + c + u];
+            const float l = DQ ? my_lse : (u ? st.z : st.x);
+            const float dd = DQ ? my_dsum : (u ? st.w : st.y);
             const float pe = vis ? exp2f(fmaf(__uint_as_float(sv[c + u]), p.scale_log2, -l)) : 0.f;
             pr[u] = pe;
             dsv[u] = pe * (__uint_as_float(dv[c + u]) - dd);
@@ -251,13 +258,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           sv[c >> 1] = pack_bf16x2(pr[0], pr[1]);
           dv[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
         }
-        // packed results go back over columns that have already been read
+        // packed results go back over the first 32 of the 64 columns this warp has just read (never
+        // over columns that the other warp of the quadrant reads)
         if (!DQ) {
-          tmem_st_32x16(tm_s + lane_off + half * 32, sv);
-          tmem_st_32x16(tm_s + lane_off + half * 32 + 16, sv + 16);
+          tmem_st_32x16(tm_s + lane_off + half * 64, sv);
+          tmem_st_32x16(tm_s + lane_off + half * 64 + 16, sv + 16);
         }
-        tmem_st_32x16(tm_dp + lane_off + half * 32, dv);
-        tmem_st_32x16(tm_dp + lane_off + half * 32 + 16, dv + 16);
+        tmem_st_32x16(tm_dp + lane_off + half * 64, dv);
+        tmem_st_32x16(tm_dp + lane_off + half * 64 + 16, dv + 16);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -276,7 +284,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
           const uint32_t tm = which == 0 ? tm_acc1 : tm_acc2;
           const float f = (DQ || which == 1) ? p.scale : 1.0f;
           const int col0 = (DQ ? p.q_col0 : (which == 0 ? p.v_col0 : p.k_col0)) + h * hd;
-          for (int c0 = 0; c0 < hd; c0 += 16) {
+          for (int c0 = half * 16; c0 < hd; c0 += 32) {       // the two warps of a quadrant alternate
             uint32_t o[16];
             tmem_ld_32x16(tm + lane_off + c0, o);
             tmem_ld_wait();
@@ -301,7 +309,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     if (s_abort) {
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);

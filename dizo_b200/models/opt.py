@@ -416,17 +416,49 @@ class OPTModel:
         shape = (rows,) + tuple(t0.shape[1:])
         return torch.as_strided(t0, shape, t0.stride())
 
+    def _blend_range(self, group: int, transform: Transform | None) -> tuple[int, int] | None:
+        """Piece range a transform has to stage for ``group``, or None for the whole group.
+
+        A DiZO blend without perturbation (the gamma-search forwards) changes only the constrained
+        tensors.  Under full fine-tuning those are the k/v projection weights, which open every
+        block's piece list together with the q weight (one fused QKV operand): staging just these
+        three instead of the whole block cuts the sweep traffic of a search forward by 4x.  The
+        globals hold no constrained tensor then, so nothing of them is staged."""
+        if (transform is None or transform.alpha is None or transform.coef != 0.0
+                or transform.coef_dev is not None or self.mode != "full"):
+            return None
+        lo, hi = self.arena.group_range(group)
+        if group < 0:
+            return (lo, lo)
+        names = [p.name for p in self.arena.pieces[lo:lo + 3]]
+        want = ["self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight"]
+        if len(names) == 3 and all(n.endswith(w) for n, w in zip(names, want)) and \
+                all(p.slot < 0 for p in self.arena.pieces[lo + 3:hi]):
+            return (lo, lo + 3)
+        return None
+
     def _resolver(self, group: int, transform: Transform | None, staged: torch.Tensor | None,
                   shift: int) -> Callable[[str], torch.Tensor]:
+        only = None
+        if staged is not None:
+            r = self._blend_range(group, transform)
+            if r is not None:
+                only = {p.name for p in self.arena.pieces[r[0]:r[1]]}
+
         def get(name: str) -> torch.Tensor:
             ar = self._where[name]
-            if ar is self.arena and staged is not None:
+            if ar is self.arena and staged is not None and (only is None or name in only):
                 return ar.view(name, base=staged, shift=shift)
             return ar.view(name)
         return get
 
     def _sweep_group(self, group: int, transform: Transform, dst: torch.Tensor) -> int:
         lo, hi = self.arena.group_range(group)
+        r = self._blend_range(group, transform)
+        if r is not None:
+            lo, hi = r
+            if lo == hi:
+                return 0
         self.arena.sweep(t_begin=lo, t_end=hi, dst=dst, seed1=transform.seed, c1=transform.coef,
                          c1_dev=transform.coef_dev, alpha=transform.alpha)
         return self.arena.span(lo, hi)[0]

@@ -261,17 +261,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int ch = 0; ch < A_BKV / 32; ++ch) tmem_ld_32x32(tm_s[t] + lane_off + ch * 32, sv + ch * 32);
       tmem_ld_wait();
-      float bmax = -INFINITY;
+      // four independent chains: a single running maximum would serialise 128 dependent operations
+      float bm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < A_BKV; ++c) {
           if (!visible(c)) sv[c] = 0xff800000u;  // -inf
-          bmax = fmaxf(bmax, __uint_as_float(sv[c]));
+          bm[c & 3] = fmaxf(bm[c & 3], __uint_as_float(sv[c]));
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < A_BKV; ++c) bmax = fmaxf(bmax, __uint_as_float(sv[c]));
+        for (int c = 0; c < A_BKV; ++c) bm[c & 3] = fmaxf(bm[c & 3], __uint_as_float(sv[c]));
       }
+      float bmax = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
       bmax *= p.scale_log2;       // scale > 0: max commutes with the scaling
       // lazily raised maximum
       float m_new = m_used;
@@ -301,14 +303,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // ---- probabilities -> bf16 pairs (packed in place) -> TMEM, over the columns S occupied
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
-      float psum = 0.f;
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < A_BKV; c += 2) {
         float e0 = exp2f(fmaf(__uint_as_float(sv[c]), p.scale_log2, -mref));
         float e1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, -mref));
-        psum += e0 + e1;
+        ps[(c >> 1) & 3] += e0 + e1;
         sv[c >> 1] = pack_bf16x2(e0, e1);
       }
+      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
 #pragma unroll
       for (int ch = 0; ch < A_BKV / 32; ++ch) tmem_st_32x16(tm_s[t] + lane_off + ch * 16, sv + ch * 16);
       l_sum += psum;

@@ -140,26 +140,28 @@ __device__ __forceinline__ bool cg_wait_flag(const uint32_t* p, uint32_t epoch, 
 // Tiles are visited source by source, own rows first.
 __device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, int& mb, int& nb) {
   if (p.gather == 1) {
-    // own rows first; then chunk by chunk, and inside a chunk source by source in the order
-    // rank+1, rank+2, ...: every source pushes its chunk c to all ranks before chunk c+1, so
-    // this is the order in which the rows arrive
+    // own rows first; then chunk by chunk (every source pushes its chunk c to all ranks before chunk
+    // c+1, so this is the order in which the rows arrive).  Inside the own block and inside a chunk
+    // the walk is column-major - all row tiles of the group for one 256-column block of W, then the
+    // next block - so the CTAs in flight share a few W tiles and the group's A rows instead of
+    // streaming the whole of W (which exceeds L2 at small world sizes) once per row tile.
     const int mbs = p.rows_per_src / CG_BM;          // row tiles per source
     const int per_src = mbs * p.num_n;
     if (tile < per_src) {
-      mb = p.rank * mbs + tile / p.num_n;
-      nb = tile % p.num_n;
+      mb = p.rank * mbs + tile % mbs;
+      nb = tile / mbs;
     } else {
       const int ct = p.chunk_tiles > 0 ? p.chunk_tiles : mbs;
-      const int per_cs = ct * p.num_n;               // tiles of one (chunk, source)
-      const int per_c = per_cs * (p.world - 1);
+      const int rows_c = ct * (p.world - 1);         // row tiles of one chunk over all sources
+      const int per_c = rows_c * p.num_n;
       int t = tile - per_src;
-      int c = t / per_c;
+      const int c = t / per_c;
       t -= c * per_c;
-      int s = t / per_cs + 1;
-      t -= (s - 1) * per_cs;
-      int src = (p.rank + s) % p.world;
-      mb = src * mbs + c * ct + t / p.num_n;
-      nb = t % p.num_n;
+      nb = t / rows_c;
+      const int rr = t - nb * rows_c;
+      const int s = rr / ct + 1;
+      const int src = (p.rank + s) % p.world;
+      mb = src * mbs + c * ct + (rr - (s - 1) * ct);
     }
   } else {
     int gm = p.num_m < 16 ? p.num_m : 16;

@@ -33,13 +33,13 @@ namespace dz {
 constexpr int CG_BM = 128;
 constexpr int CG_BN = 256;
 constexpr int CG_BK = 64;
-constexpr int CG_STAGES_PUSH = 3;   // ring depth when a tile is staged for the reduce-scatter epilogue
+constexpr int CG_STAGES_PUSH = 4;   // ring depth with the reduce-scatter epilogue (plus 32 KB of row staging)
 constexpr int CG_STAGES_PLAIN = 4;
 constexpr int CG_THREADS = 192;
 constexpr int CG_A_BYTES = CG_BM * CG_BK * 2;
 constexpr int CG_B_BYTES = CG_BN * CG_BK * 2;
 constexpr int CG_STAGE_BYTES = CG_A_BYTES + CG_B_BYTES;
-constexpr int CG_OUT_STAGE_BYTES = CG_BM * CG_BN * 2;           // bf16 tile staged for coalesced remote stores
+constexpr int CG_OUT_STAGE_BYTES = 4 * 32 * 256;                // per epilogue warp: 32 rows x 128 bf16 columns
 constexpr int CG_SMEM_PUSH = CG_STAGES_PUSH * CG_STAGE_BYTES + CG_OUT_STAGE_BYTES + 1024;
 constexpr int CG_SMEM_PLAIN = CG_STAGES_PLAIN * CG_STAGE_BYTES + 1024;   // both >= the 128 KB Gaussian table
 constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
@@ -494,7 +494,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = nb * CG_BN + c * 32;
-        if (col0 >= p.N) continue;
+        if (col0 < p.N) {
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -527,12 +527,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < 32; ++j)
               if (full_chunk || col0 + j < p.N) orow_f32[col0 + j] = v[j];
           } else if (p.push_out) {
-            // stage the tile in shared memory (16-byte units XOR-swizzled by the row so that
-            // neither this row-per-thread fill nor the row-per-warp drain conflicts on banks)
+            // stage this warp's 32 rows x 128 columns (one half of the tile's width) in its own
+            // shared-memory block, 16-byte units XOR-swizzled by the row against bank conflicts
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const uint32_t unit = (uint32_t)(c * 4 + q) ^ (uint32_t)(row_in_tile & 31);
-              const uint32_t addr = out_stage + row_in_tile * (CG_BN * 2) + unit * 16;
+              const uint32_t unit = (uint32_t)((c & 3) * 4 + q) ^ (uint32_t)(lane & 15);
+              const uint32_t addr = out_stage + quad * 8192 + lane * 256 + unit * 16;
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
                            "r"(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1])), "r"(pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3])),
                            "r"(pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5])), "r"(pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]))
@@ -555,33 +555,39 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (col0 + j < p.N) orow_bf[col0 + j] = __float2bfloat16(v[j]);
           }
         }
+        }
+        if (p.push_out && (c & 3) == 3) {
+          // drain one half of the width: the warp sends its 32 rows, two per store instruction
+          // (256 contiguous bytes each) to the rank that owns them, so the NVLink writes are
+          // full-width instead of 16-byte fragments.  Only this warp touches the block.
+          __syncwarp();
+          const int half = c >> 2;
+          const long long row0 = (long long)mb * CG_BM + quad * 32;
+          const int owner = (int)(row0 / p.rows_per_owner);
+          __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
+                                 (long long)p.rank * p.out_slot_stride +
+                                 (row0 - (long long)owner * p.rows_per_owner) * p.ldo +
+                                 (long long)nb * CG_BN + half * 128;
+          const int unit = lane & 15;
+          const int colu = nb * CG_BN + half * 128 + unit * 8;
+#pragma unroll 4
+          for (int rr = lane >> 4; rr < 32; rr += 2) {
+            if (row0 + rr < p.M && colu < p.N) {
+              const uint32_t addr = out_stage + quad * 8192 + rr * 256 + (((uint32_t)unit ^ (uint32_t)(rr & 15)) * 16);
+              uint4 o;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(addr) : "memory");
+              *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + unit * 8) = o;
+            }
+          }
+          __syncwarp();
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
-      if (p.push_out) {
-        // drain: every warp sends whole rows (512 contiguous bytes per store instruction) to the
-        // rank that owns them, so the NVLink writes are full-width instead of 16-byte fragments
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const long long row0 = (long long)mb * CG_BM;
-        const int owner = (int)(row0 / p.rows_per_owner);
-        __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
-                               (long long)p.rank * p.out_slot_stride +
-                               (row0 - (long long)owner * p.rows_per_owner) * p.ldo + (long long)nb * CG_BN;
-        const int colu = nb * CG_BN + lane * 8;
-        for (int rr = quad; rr < CG_BM; rr += 4) {
-          if (row0 + rr < p.M && colu < p.N) {
-            const uint32_t addr = out_stage + rr * (CG_BN * 2) + (((uint32_t)lane ^ (uint32_t)(rr & 31)) * 16);
-            uint4 o;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(addr) : "memory");
-            *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + lane * 8) = o;
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
     }
     if (p.push_out) __threadfence_system();     // this CTA's remote tile stores are ordered
   }
@@ -719,11 +725,10 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   if (!a.counters) return DZ_ERR_ARG;
   static bool configured = false;
   if (!configured) {
+    // the ring depth is the same with and without the reduce-scatter epilogue: one instantiation
+    static_assert(CG_STAGES_PUSH == CG_STAGES_PLAIN, "one kernel instantiation expected");
     cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<CG_STAGES_PUSH>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, CG_SMEM_PUSH);
-    if (e != cudaSuccess) return cuda_rc(e);
-    e = cudaFuncSetAttribute(comm_gemm_kernel<CG_STAGES_PLAIN>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, CG_SMEM_PLAIN);
     if (e != cudaSuccess) return cuda_rc(e);
     configured = true;
   }

@@ -113,18 +113,29 @@ def main():
     seg = [dict(w_shard=shard, dst_row0=rank * Fl, tensor_id=3, elem_base=rank * Fl * d)]
     state = {"slot": None}
 
-    def fused_fsdp():
-        # steady state of the pipeline: this launch multiplies the weight pushed by the previous one
-        if state["slot"] is None:
-            state["slot"], _ = fc.fsdp_launch(push=dict(segments=seg, seed=9, coef=1e-3))
-        prev = state["slot"]
-        state["slot"], _ = fc.fsdp_launch(push=dict(segments=seg, seed=9, coef=1e-3),
-                                          gemm=dict(slot=prev, N=F, x=xs, rows_per_src=Fl, out=yf))
-
     from ..ops.zo import ParamArena, Piece
     ar = ParamArena([Piece("w", (Fl, d), tensor_id=3, elem_base=rank * Fl * d)], dev)
     ar.view("w").copy_(shard)
     stage = torch.empty_like(ar.data)
+    # the model's policy (FSDPOPTModel.push_perturb_limit): a small shard is perturbed by the push CTAs on
+    # its way out; a large one is perturbed by the whole-GPU sweep first and pushed as a plain copy
+    staged_push = Fl * d > 24 * 1024 * 1024
+    seg_staged = [dict(w_shard=stage[:Fl * d].view(Fl, d), dst_row0=rank * Fl, tensor_id=3,
+                       elem_base=rank * Fl * d)]
+
+    def push_spec():
+        if staged_push:
+            ar.sweep(dst=stage, seed1=9, c1=1e-3)
+            return dict(segments=seg_staged, seed=9, coef=0.0)
+        return dict(segments=seg, seed=9, coef=1e-3)
+
+    def fused_fsdp():
+        # steady state of the pipeline: this launch multiplies the weight pushed by the previous one
+        if state["slot"] is None:
+            state["slot"], _ = fc.fsdp_launch(push=push_spec())
+        prev = state["slot"]
+        state["slot"], _ = fc.fsdp_launch(push=push_spec(),
+                                          gemm=dict(slot=prev, N=F, x=xs, rows_per_src=Fl, out=yf))
 
     def base_fsdp():
         ar.sweep(dst=stage, seed1=9, c1=1e-3)                     # perturb the shard

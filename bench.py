@@ -318,8 +318,8 @@ def run_reference(a):
     ref = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(ref) or not os.listdir(ref):
-        why = ("reference is not installable: it ships no setup.py/pyproject (pip install of "
-               "/root/reference fails) and its trainer imports symbols removed from transformers 5.x")
+        why = ("reference is not installable: it ships no setup.py/pyproject (pip install of the "
+               "source tree fails) and its trainer imports symbols removed from transformers 5.x")
     else:
         sys.path.insert(0, ref)
         try:

@@ -249,11 +249,41 @@ class OurTrainer:
                 self.dizo_trainer.dizo_zo_iters(self.model, norms_ready=sq is not None)
             else:
                 self.dizo_trainer.dizo_iters(self.model)
-            if a.verbose:
-                gs = self.dizo_trainer.projector.gs
-                logger.info("DiZO projection %d: alpha mean %.4f min %.4f max %.4f (%.2fs)",
-                            self.dizo_trainer.i, gs.alpha.mean().item(), gs.alpha.min().item(),
-                            gs.alpha.max().item(), time.time() - t0)
+            if a.verbose or self._metrics_f:
+                # gamma / ||theta - theta_0|| per constrained tensor: how far the projection pulled
+                pr = self.dizo_trainer.projector
+                gs = pr.gs
+                al = gs.alpha[:max(pr.n, 1)].float()
+                rec = {"projection": self.dizo_trainer.i, "step": self.state.global_step + 1,
+                       "alpha_mean": round(al.mean().item(), 5), "alpha_min": round(al.min().item(), 5),
+                       "alpha_max": round(al.max().item(), 5),
+                       "ts_mean": round(gs.ts[:max(pr.n, 1)].float().mean().item(), 6),
+                       "search_s": round(time.time() - t0, 3)}
+                if a.verbose:
+                    logger.info("DiZO projection %s", rec)
+                if self._metrics_f:
+                    self._metrics_f.write(json.dumps(rec) + "\n")
+
+    def _log_phases(self, ev) -> None:
+        """Device time of the two phases of a profiled step (max over the ranks): the two forwards
+        with their in-flight perturbation, and the update sweep (+ gamma search when one was due);
+        the update's parameter traffic as GB/s when it was a plain update."""
+        ev[2].synchronize()
+        t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], dtype=torch.float64,
+                         device=self.model.device)
+        if dist.is_available() and dist.is_initialized():
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        fwd_ms, upd_ms = (float(x) for x in t.tolist())
+        a = self.args
+        searched = bool(a.enhanced) and a.enhanced != "None" and self.dizo_trainer is not None and \
+            (self.state.global_step + 1) % a.dizo_interval == 0
+        rec = {"step": self.state.global_step + 1, "forwards_ms": round(fwd_ms, 3), "update_ms": round(upd_ms, 3)}
+        if not searched and upd_ms > 0:
+            nbytes = 2 * self.model.arena.trainable_numel() * self.model.arena.data.element_size()
+            rec["update_gbs"] = round(nbytes / upd_ms / 1e6, 1)
+        logger.info("profile %s", rec)
+        if self._metrics_f:
+            self._metrics_f.write(json.dumps(rec) + "\n")
 
     def training_step(self, inputs) -> float:
         """One full optimisation step from host inputs: H2D copy, ``zo_step``, ``zo_update``,
@@ -407,16 +437,26 @@ class OurTrainer:
             if self.state.global_step >= self.state.max_steps:
                 break
             profiling = prof is not None and prof[0] <= self.state.global_step < prof[1]
-            if profiling and self.model.device.type == "cuda":
+            on_gpu = self.model.device.type == "cuda"
+            ev = None
+            if profiling and on_gpu:
                 torch.cuda.nvtx.range_push(f"zo_step_{self.state.global_step}")
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                ev[0].record()
             if a.trainer == "zo":
                 loss_t = self.zo_step(self.model, inputs)
+                if ev:
+                    ev[1].record()
                 self.zo_update(a, self.model)
             else:
                 from .models.opt_autograd import fo_training_step
                 loss_t = fo_training_step(self, inputs)
-            if profiling and self.model.device.type == "cuda":
+                if ev:
+                    ev[1].record()
+            if ev:
+                ev[2].record()
                 torch.cuda.nvtx.range_pop()
+                self._log_phases(ev)
             loss = float(loss_t.item())                      # the step's one device->host read
             if a.logging_nan_inf_filter and (math.isnan(loss) or math.isinf(loss)):
                 loss = tr_loss / max(1, self.state.global_step - start_step)

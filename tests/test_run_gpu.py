@@ -40,6 +40,16 @@ def test_cli_training_runs_on_gpu(tmp_path, monkeypatch, extra):
     assert 0.0 <= m["accuracy"] <= 1.0 and "dev_accuracy" in m
 
 
+def test_profiled_steps_report_phase_times(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    mj = tmp_path / "metrics.jsonl"
+    assert main(_common(tmp_path, "--enhanced", "zo", "--profile_steps", "1:4", "--metrics_jsonl", str(mj))) == 0
+    recs = [json.loads(l) for l in open(mj)]
+    prof = [r for r in recs if "forwards_ms" in r]
+    assert len(prof) == 3 and all(r["forwards_ms"] > 0 and r["update_ms"] > 0 for r in prof)
+    assert any("update_gbs" in r for r in prof) and any("projection" in r for r in recs)
+
+
 def test_lm_style_training_and_resume_on_gpu(tmp_path, monkeypatch):
     monkeypatch.chdir(tmp_path)
     args = _common(tmp_path)

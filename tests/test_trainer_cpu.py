@@ -209,8 +209,13 @@ def test_run_main_end_to_end(tmp_path, monkeypatch):
                "--num_dev", "8", "--num_eval", "8", "--train_set_seed", "0", "--max_steps", "4",
                "--learning_rate", "1e-3", "--per_device_train_batch_size", "4", "--train_as_classification",
                "--enhanced", "zo", "--dizo_interval", "2", "--dizo_max_iters", "1", "--output_dir",
-               str(tmp_path / "out"), "--save_steps", "0", "--zo_eval_steps", "2", "--max_length", "64"])
+               str(tmp_path / "out"), "--save_steps", "0", "--zo_eval_steps", "2", "--max_length", "64",
+               "--metrics_jsonl", str(tmp_path / "metrics.jsonl"), "--zo_log_steps", "2"])
     assert rc == 0
+    recs = [json.loads(l) for l in open(tmp_path / "metrics.jsonl")]
+    proj = [r for r in recs if "projection" in r]
+    assert len(proj) == 2 and all(r["alpha_min"] <= r["alpha_mean"] <= r["alpha_max"] for r in proj)
+    assert any("tokens_per_s" in r for r in recs)
     files = os.listdir(tmp_path / "result")
     assert any(f.endswith("trainset0.json") for f in files)
     m = json.load(open(tmp_path / "result" / files[0]))

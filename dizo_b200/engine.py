@@ -99,6 +99,71 @@ class ZOEngine:
         return self.loss1
 
 
+def batch_signature(batch: Batch) -> tuple:
+    """Shapes of every tensor of a batch (what a captured step is specialised to)."""
+    return tuple((k, tuple(v.shape)) if isinstance(v, torch.Tensor) else (k, v)
+                 for k, v in sorted(batch.__dict__.items()))
+
+
+class GraphedZOStep:
+    """One whole ZO-SGD step (two forwards with in-flight perturbation, the projected-gradient
+    arithmetic, the update sweep) captured in a CUDA graph and replayed with one launch.
+
+    For models whose step is bound by kernel-launch overhead rather than by the kernels (hundreds
+    of launches of a few microseconds each on the small OPT sizes).  What changes from step to step
+    lives in device memory and is refreshed before each replay: the batch (copied into the captured
+    input tensors), the perturbation seed (the sweeps read it through ``seed1_dev``) and the
+    learning rate.  One instance serves one batch signature; single-process (the data-parallel
+    all-reduce is not captured), ``inflight`` mode, round-to-nearest updates."""
+
+    def __init__(self, engine: ZOEngine, example: Batch, warmup: int = 2):
+        assert engine.mode == "inflight" and not engine.stochastic_rounding
+        assert engine.dp_group is False or not _dist_on(engine.dp_group), "single-process only"
+        dev = engine.model.device
+        assert dev.type == "cuda"
+        self.engine = engine
+        self.signature = batch_signature(example)
+        self.batch = Batch(**{k: (v.to(dev).clone() if isinstance(v, torch.Tensor) else v)
+                              for k, v in example.__dict__.items()})
+        self.seed = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.lr = torch.zeros(1, dtype=torch.float32, device=dev)       # 0 while warming up: theta unchanged
+        self._lrg = torch.zeros(1, dtype=torch.float32, device=dev)
+        cur = torch.cuda.current_stream(dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._body()
+        cur.wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._body()
+        self.replays = 0
+
+    def _body(self) -> torch.Tensor:
+        e, eps = self.engine, self.engine.eps
+        l1 = e.forward(self.batch, Transform(coef=eps, seed_dev=self.seed))
+        l2 = e.forward(self.batch, Transform(coef=-eps, seed_dev=self.seed))
+        e.loss1.copy_(l1.reshape(1))
+        e.loss2.copy_(l2.reshape(1))
+        scalar_diff(e.loss1, e.loss2, 1.0 / (2.0 * eps), e.projected_grad)
+        torch.mul(e.projected_grad, self.lr, out=self._lrg)
+        e.model.arena.sweep(seed1_dev=self.seed, c1=-1.0, c1_dev=self._lrg)
+        return e.loss1
+
+    def __call__(self, batch: Batch, lr: float, seed: int) -> torch.Tensor:
+        assert batch_signature(batch) == self.signature, "batch shape differs from the captured one"
+        for k, v in batch.__dict__.items():
+            if isinstance(v, torch.Tensor):
+                getattr(self.batch, k).copy_(v, non_blocking=True)
+        self.seed.fill_(int(seed))
+        self.lr.fill_(float(lr))
+        self.graph.replay()
+        self.replays += 1
+        return self.loss
+
+
 class DiZOProjector:
     """gamma search + projection for the constrained tensors of ``model.arena``."""
 

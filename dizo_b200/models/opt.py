@@ -170,6 +170,7 @@ class Transform:
     coef: float = 0.0
     coef_dev: torch.Tensor | None = None
     alpha: torch.Tensor | None = None     # DiZO blend ratios per slot (fp32, on the device)
+    seed_dev: torch.Tensor | None = None  # 1-element int64 on the device: overrides ``seed`` (graph replays)
 
 
 @dataclass
@@ -460,7 +461,7 @@ class OPTModel:
             if lo == hi:
                 return 0
         self.arena.sweep(t_begin=lo, t_end=hi, dst=dst, seed1=transform.seed, c1=transform.coef,
-                         c1_dev=transform.coef_dev, alpha=transform.alpha)
+                         c1_dev=transform.coef_dev, seed1_dev=transform.seed_dev, alpha=transform.alpha)
         return self.arena.span(lo, hi)[0]
 
     def _layer_weights(self, i: int, get: Callable[[str], torch.Tensor]) -> SimpleNamespace:

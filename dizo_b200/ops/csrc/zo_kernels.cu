@@ -65,6 +65,7 @@ struct ZoSweepArgs {
   int t_begin, t_end;           // tensors of the range
   long long chunk_begin, chunk_end;
   unsigned long long seed1, seed2;
+  const unsigned long long* seed1_dev;   // if set: seed1 is read from the device (graph replays)
   float c1, c2;                 // host coefficients
   const float* c1_ptr;          // if set: c1 = c1 * *c1_ptr
   const float* c2_ptr;
@@ -171,7 +172,9 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
 // flight (64 KB per SM), which is what it takes to cover HBM latency at full bandwidth.
 template <bool Z2, bool BLEND, bool NORM, bool SR>
 __global__ void __launch_bounds__(ZO_THREADS, 1)
-zo_sweep_kernel(const ZoSweepArgs a) {
+zo_sweep_kernel(const ZoSweepArgs a_in) {
+  ZoSweepArgs a = a_in;
+  if (a.seed1_dev) a.seed1 = *a.seed1_dev;     // a captured launch takes the step's seed from memory
   extern __shared__ __align__(16) uint8_t zo_smem[];
   __half* tab = reinterpret_cast<__half*>(zo_smem);
   {
@@ -327,13 +330,16 @@ extern "C" int dz_zo_tensor_struct_bytes() { return (int)sizeof(ZoTensor); }
 // One sweep over arena chunks [chunk_begin, chunk_end) (tensors [t_begin, t_end) of the
 // table).  flags: bit0 second z term, bit1 blend with anchor, bit2 emit norm partials,
 // bit3 stochastic rounding.
-extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, const void* anchor,
-                           const void* table, int t_begin, int t_end, long long chunk_begin,
-                           long long chunk_end, unsigned long long seed1, float c1,
-                           const float* c1_ptr, unsigned long long seed2, float c2,
-                           const float* c2_ptr, const float* alpha, float* chunk_sq,
-                           unsigned long long sr_seed, int flags, const void* gauss_table,
-                           cudaStream_t stream) {
+// seed1_dev (optional): device word holding seed1, read by the kernel instead of the argument, so
+// that a launch captured in a CUDA graph perturbs with a new seed at every replay.
+extern "C" int dz_zo_sweep_seeded(const void* src, void* dst, long long dst_shift, const void* anchor,
+                                  const void* table, int t_begin, int t_end, long long chunk_begin,
+                                  long long chunk_end, unsigned long long seed1,
+                                  const unsigned long long* seed1_dev, float c1,
+                                  const float* c1_ptr, unsigned long long seed2, float c2,
+                                  const float* c2_ptr, const float* alpha, float* chunk_sq,
+                                  unsigned long long sr_seed, int flags, const void* gauss_table,
+                                  cudaStream_t stream) {
   if (!src || !dst || !table || !gauss_table || t_end <= t_begin) return DZ_ERR_ARG;
   if (reinterpret_cast<uintptr_t>(gauss_table) & 15) return DZ_ERR_ALIGN;
   const bool z2 = flags & 1, blend = flags & 2, norm = flags & 4, sr = flags & 8;
@@ -344,7 +350,7 @@ extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, cons
   a.src = (const __nv_bfloat16*)src; a.dst = (__nv_bfloat16*)dst; a.dst_shift = dst_shift;
   a.anchor = (const __nv_bfloat16*)anchor; a.table = (const ZoTensor*)table;
   a.t_begin = t_begin; a.t_end = t_end; a.chunk_begin = chunk_begin; a.chunk_end = chunk_end;
-  a.seed1 = seed1; a.seed2 = seed2; a.c1 = c1; a.c2 = c2; a.c1_ptr = c1_ptr; a.c2_ptr = c2_ptr;
+  a.seed1 = seed1; a.seed1_dev = seed1_dev; a.seed2 = seed2; a.c1 = c1; a.c2 = c2; a.c1_ptr = c1_ptr; a.c2_ptr = c2_ptr;
   a.alpha = alpha; a.chunk_sq = chunk_sq; a.sr_seed = sr_seed;
   a.gauss_table = (const __half*)gauss_table;
   int key = (z2 ? 1 : 0) | (blend ? 2 : 0) | (norm ? 4 : 0) | (sr ? 8 : 0);
@@ -361,6 +367,18 @@ extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, cons
 #undef DZ_CASE
   }
   return DZ_ERR_ARG;
+}
+
+extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, const void* anchor,
+                           const void* table, int t_begin, int t_end, long long chunk_begin,
+                           long long chunk_end, unsigned long long seed1, float c1,
+                           const float* c1_ptr, unsigned long long seed2, float c2,
+                           const float* c2_ptr, const float* alpha, float* chunk_sq,
+                           unsigned long long sr_seed, int flags, const void* gauss_table,
+                           cudaStream_t stream) {
+  return dz_zo_sweep_seeded(src, dst, dst_shift, anchor, table, t_begin, t_end, chunk_begin, chunk_end, seed1,
+                            nullptr, c1, c1_ptr, seed2, c2, c2_ptr, alpha, chunk_sq, sr_seed, flags,
+                            gauss_table, stream);
 }
 
 extern "C" int dz_zo_reduce_chunks(const void* table, int num_tensors, const float* chunk_sq,

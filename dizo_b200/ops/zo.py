@@ -186,14 +186,15 @@ class ParamArena:
     # ------------------------------------------------------------------ the sweep
     def sweep(self, *, t_begin: int = 0, t_end: int | None = None, dst: torch.Tensor | None = None,
               seed1: int = 0, c1: float = 0.0, c1_dev: torch.Tensor | None = None,
-              seed2: int = 0, c2: float = 0.0, c2_dev: torch.Tensor | None = None,
+              seed1_dev: torch.Tensor | None = None, seed2: int = 0, c2: float = 0.0, c2_dev: torch.Tensor | None = None,
               alpha: torch.Tensor | None = None, sq_out: torch.Tensor | None = None,
               stochastic_round_seed: int | None = None) -> None:
         """dst[range] = round(blend(theta) + c1*z(seed1) + c2*z(seed2)); optional norms.
 
         ``dst=None`` writes the arena in place; otherwise ``dst`` is a staging buffer whose
         element 0 corresponds to the first element of the range.  ``c?_dev`` (1-element fp32
-        tensors) multiply the host coefficients on the device.  ``alpha`` ([n_slots] fp32)
+        tensors) multiply the host coefficients on the device; ``seed1_dev`` (1-element int64 tensor)
+        replaces ``seed1`` by a value read on the device (CUDA-graph replays).  ``alpha`` ([n_slots] fp32)
         switches on the blend ``theta_0 + alpha*(theta - theta_0)`` for slotted pieces;
         ``sq_out`` ([n_slots] fp32) receives ``||stored - theta_0||^2`` per slotted piece of
         the range."""
@@ -211,6 +212,8 @@ class ParamArena:
         if (blend or norm) and self.anchor is None:
             raise ValueError("blend/norm need set_dizo() first")
         if self.device.type != "cuda":
+            if seed1_dev is not None:
+                seed1 = int(seed1_dev.item()) & (2 ** 64 - 1)
             self._sweep_cpu(t_begin, t_end, out, shift, seed1, c1, c1_dev, seed2, c2, c2_dev,
                             use_z2, alpha, sq_out, stochastic_round_seed)
             return
@@ -221,15 +224,17 @@ class ParamArena:
         if norm and self._chunk_sq is None:
             self._chunk_sq = torch.zeros(max(self._n_sq_chunks, 1), dtype=torch.float32,
                                          device=self.device)
-        rc = L.dz_zo_sweep(
+        if seed1_dev is not None:
+            assert seed1_dev.dtype == torch.int64 and seed1_dev.is_cuda and seed1_dev.numel() == 1
+        rc = L.dz_zo_sweep_seeded(
             _lib.ptr(self.data), _lib.ptr(out), ctypes.c_longlong(shift), _lib.ptr(self.anchor),
             _lib.ptr(self.table()), t_begin, t_end, ctypes.c_longlong(begin // CHUNK),
-            ctypes.c_longlong(end // CHUNK), ctypes.c_uint64(seed1 & (2 ** 64 - 1)),
+            ctypes.c_longlong(end // CHUNK), ctypes.c_uint64(seed1 & (2 ** 64 - 1)), _lib.ptr(seed1_dev),
             ctypes.c_float(c1), _lib.ptr(c1_dev), ctypes.c_uint64(seed2 & (2 ** 64 - 1)),
             ctypes.c_float(c2 if use_z2 else 0.0), _lib.ptr(c2_dev), _lib.ptr(alpha),
             _lib.ptr(self._chunk_sq), ctypes.c_uint64((stochastic_round_seed or 0) & (2 ** 64 - 1)),
             flags, _lib.ptr(gauss_table_dev(self.device)), _lib.stream_ptr())
-        _lib.check(rc, "dz_zo_sweep")
+        _lib.check(rc, "dz_zo_sweep_seeded")
         if norm:
             rc = L.dz_zo_reduce_chunks(
                 ctypes.c_void_p(self.table().data_ptr() + t_begin * self.table_stride()),

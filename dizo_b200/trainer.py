@@ -119,6 +119,7 @@ class OurTrainer:
         self._pgm_count = 0          # batches the gamma search has consumed (saved for resume)
         self._phase_ms: Dict[str, float] = {}
         self._metrics_f = None
+        self._graphs: dict = {}
         on = dist.is_available() and dist.is_initialized() and dp_group is not False
         self._rank = dist.get_rank(dp_group) if on else 0
         # the one process that writes files (under tensor parallelism every rank has data rank 0)
@@ -263,6 +264,33 @@ class OurTrainer:
                     logger.info("DiZO projection %s", rec)
                 if self._metrics_f:
                     self._metrics_f.write(json.dumps(rec) + "\n")
+
+    # ------------------------------------------------------------------ CUDA-graph replay
+    def _graph_ok(self) -> bool:
+        """``--zo_cuda_graph``: replay the step as one CUDA graph when nothing but the plain step is
+        due (no projection), on one process, for differentiable objectives."""
+        a = self.args
+        if not getattr(a, "zo_cuda_graph", False) or self.model.device.type != "cuda" or a.non_diff:
+            return False
+        if self._world > 1 or self.engine.mode != "inflight" or self.engine.stochastic_rounding:
+            return False
+        if type(self.model).hidden_states is not OPTModel.hidden_states:
+            return False
+        due = bool(a.enhanced) and a.enhanced != "None" and self.dizo_trainer is not None and \
+            (self.state.global_step + 1) % a.dizo_interval == 0
+        return not due
+
+    def _graphed_zo_step(self, inputs) -> torch.Tensor:
+        from .engine import GraphedZOStep, batch_signature
+        self.zo_random_seed = int(np.random.randint(1_000_000_000))      # same draw as zo_step
+        batch = self._to_batch(inputs)
+        key = batch_signature(batch)
+        g = self._graphs.get(key)
+        if g is None:
+            if len(self._graphs) >= 8:                                   # ragged shapes: keep the cache small
+                self._graphs.pop(next(iter(self._graphs)))
+            g = self._graphs[key] = GraphedZOStep(self.engine, batch)
+        return g(batch, self._get_learning_rate(), self.zo_random_seed)
 
     def _log_phases(self, ev) -> None:
         """Device time of the two phases of a profiled step (max over the ranks): the two forwards
@@ -443,7 +471,11 @@ class OurTrainer:
                 torch.cuda.nvtx.range_push(f"zo_step_{self.state.global_step}")
                 ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
                 ev[0].record()
-            if a.trainer == "zo":
+            if a.trainer == "zo" and self._graph_ok():
+                loss_t = self._graphed_zo_step(inputs)
+                if ev:
+                    ev[1].record()
+            elif a.trainer == "zo":
                 loss_t = self.zo_step(self.model, inputs)
                 if ev:
                     ev[1].record()

@@ -8,6 +8,9 @@ seconds, which is what a long training step sees under the power cap).
     python -m dizo_b200.ops.microbench layernorm --rows 8192 --d 5120
     python -m dizo_b200.ops.microbench dgrad --m 8192 --n 5120 --k 20480      # dX = dY W, W [k, n]
     python -m dizo_b200.ops.microbench attn_bwd --batch 8 --seq 1024 --heads 40 --hd 128
+    python -m dizo_b200.ops.microbench lnbwd --rows 8192 --d 5120
+    python -m dizo_b200.ops.microbench lmhead --rows 4096 --d 5120 --n 50272   # log-sum-exp fused LM head
+    python -m dizo_b200.ops.microbench decode --batch 8 --seq 1024 --heads 40 --hd 128
 
 Each run prints one JSON line with achieved TFLOP/s or GB/s and the fraction of the measured
 peak found in MEASURED_PEAKS.json at the repository root (if present).  ``--only ours`` skips the
@@ -70,7 +73,7 @@ def time_fn(fn, iters=20, warmup=3, seconds=0.0, flush=None):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "dgrad", "attn", "attn_bwd", "sweep", "layernorm"])
+    ap.add_argument("kernel", choices=["gemm", "dgrad", "attn", "attn_bwd", "sweep", "layernorm", "lnbwd", "lmhead", "decode"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -143,6 +146,42 @@ def main():
             ms = time_fn(lambda: torch.autograd.grad(so, (q, k, v), gso, retain_graph=True), a.iters,
                          seconds=a.seconds, flush=flush)
             out.update(lib_ms=ms, lib_tflops=fl / ms / 1e9)
+    elif a.kernel == "lnbwd":
+        from .backward import layernorm_backward
+        x = torch.randn(a.rows, a.d, device=dev, generator=g).bfloat16()
+        dy = torch.randn(a.rows, a.d, device=dev, generator=g).bfloat16()
+        w = torch.randn(a.d, device=dev, generator=g).bfloat16()
+        nbytes = 6.0 * a.rows * a.d                      # read x and dy, write dx
+        ms = time_fn(lambda: layernorm_backward(dy, x, w), a.iters, seconds=a.seconds, flush=flush)
+        out.update(shape=[a.rows, a.d], ours_ms=ms, ours_gbs=nbytes / ms / 1e6,
+                   ours_frac_of_measured=nbytes / ms / 1e6 / peaks["hbm_gbs"])
+    elif a.kernel == "lmhead":
+        from .loss import token_logprobs
+        x = torch.randn(a.rows, a.d, device=dev, generator=g).bfloat16()
+        table = (torch.randn(a.n, a.d, device=dev, generator=g) * 0.02).bfloat16()
+        tg = torch.randint(0, a.n, (a.rows,), device=dev, generator=g, dtype=torch.int32)
+        fl = 2.0 * a.rows * a.n * a.d
+        out.update(shape=[a.rows, a.n, a.d])
+        if a.only != "lib":
+            ms = time_fn(lambda: token_logprobs(x, table, tg), a.iters, seconds=a.seconds, flush=flush)
+            out.update(ours_ms=ms, ours_tflops=fl / ms / 1e9, ours_frac_of_measured=fl / ms / 1e9 / peaks["bf16_tflops"],
+                       logits_bytes_avoided=2.0 * a.rows * a.n)
+        if a.only != "ours":
+            def ref():
+                lg = torch.matmul(x, table.t()).float()
+                return torch.log_softmax(lg, dim=-1).gather(1, tg.long().view(-1, 1))
+            ms = time_fn(ref, a.iters, seconds=a.seconds, flush=flush)
+            out.update(lib_ms=ms, lib_tflops=fl / ms / 1e9)
+    elif a.kernel == "decode":
+        from .decode import decode_attention
+        d = a.heads * a.hd
+        q = torch.randn(a.batch, d, device=dev, generator=g).bfloat16()
+        kc = torch.randn(a.batch, a.seq, d, device=dev, generator=g).bfloat16()
+        vc = torch.randn(a.batch, a.seq, d, device=dev, generator=g).bfloat16()
+        nbytes = 4.0 * a.batch * a.seq * d               # the K and V cache rows read once
+        ms = time_fn(lambda: decode_attention(q, kc, vc, a.seq, a.heads), a.iters, seconds=a.seconds, flush=flush)
+        out.update(shape=[a.batch, a.seq, a.heads, a.hd], ours_ms=ms, ours_gbs=nbytes / ms / 1e6,
+                   ours_frac_of_measured=nbytes / ms / 1e6 / peaks["hbm_gbs"])
     elif a.kernel == "attn":
         d = a.heads * a.hd
         qkv = torch.randn(a.batch, a.seq, 3 * d, device=dev, generator=g).bfloat16()

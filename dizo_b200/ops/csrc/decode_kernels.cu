@@ -16,7 +16,9 @@
 
 namespace dz {
 
-constexpr int DA_THREADS = 128;
+constexpr int DA_THREADS = 256;
+constexpr int DA_WARPS = DA_THREADS / 32;
+constexpr int DA_UNROLL = 4;      // independent cache rows in flight per thread
 
 __global__ void __launch_bounds__(DA_THREADS)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
@@ -26,37 +28,52 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
                    long long ldp, int n_prefix, const int* __restrict__ pad_left, int kv_len, int hd,
                    float scale, __nv_bfloat16* __restrict__ out, long long ldo) {
   extern __shared__ float s_score[];          // [n_prefix + kv_len]
-  __shared__ float s_red[DA_THREADS / 32];
+  __shared__ float s_red[DA_WARPS];
   __shared__ float s_q[128];
+  __shared__ float s_part[DA_WARPS][128];     // per-warp partial outputs
   const int b = blockIdx.y, h = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pad = pad_left ? pad_left[b] : 0;
   const int total = n_prefix + kv_len;
   if (tid < hd) s_q[tid] = __bfloat162float(q[(long long)b * ldq + h * hd + tid]) * scale;
   __syncthreads();
-  // scores: one key per half-warp pass (16 lanes x 8 elements cover hd <= 128)
+  const __nv_bfloat16* kbase = kc + (long long)b * ld_seq + h * hd;
+  const __nv_bfloat16* vbase = vc + (long long)b * ld_seq + h * hd;
+  // ---- scores: a half-warp per key (16 lanes x 8 elements cover hd <= 128), DA_UNROLL keys of
+  // each half-warp in flight.  The trip count is the same for every lane of a warp (the shuffles
+  // need all 32 lanes).
   const int sub = lane >> 4, l16 = lane & 15;
+  const bool col_ok = l16 * 8 < hd;
   float lmax = -INFINITY;
-  // the trip count is the same for every lane of a warp (the shuffles below need all 32 lanes)
-  for (int jb = warp * 2; jb < total; jb += (DA_THREADS / 32) * 2) {
-    const int j = jb + sub;
-    const bool in_range = j < total;
-    float acc = 0.f;
-    if (in_range && l16 * 8 < hd) {
-      const __nv_bfloat16* krow = j < n_prefix ? pk + (long long)j * ldp + h * hd
-                                               : kc + (long long)b * ld_seq + (long long)(j - n_prefix) * ld_row + h * hd;
-      uint4 kv = *reinterpret_cast<const uint4*>(krow + l16 * 8);
-      const float* qq = s_q + l16 * 8;
-      acc = qq[0] * bf16_lo(kv.x) + qq[1] * bf16_hi(kv.x) + qq[2] * bf16_lo(kv.y) + qq[3] * bf16_hi(kv.y) +
-            qq[4] * bf16_lo(kv.z) + qq[5] * bf16_hi(kv.z) + qq[6] * bf16_lo(kv.w) + qq[7] * bf16_hi(kv.w);
-    }
+  for (int jb = warp * 2; jb < total; jb += DA_WARPS * 2 * DA_UNROLL) {
+    uint4 kv[DA_UNROLL];
 #pragma unroll
-    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (in_range) {
-      const bool vis = j < n_prefix || (j - n_prefix) >= pad;
-      if (!vis) acc = -INFINITY;
-      if (l16 == 0) s_score[j] = acc;
-      lmax = fmaxf(lmax, acc);
+    for (int u = 0; u < DA_UNROLL; ++u) {
+      const int j = jb + u * DA_WARPS * 2 + sub;
+      kv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (j < total && col_ok) {
+        const __nv_bfloat16* krow = j < n_prefix ? pk + (long long)j * ldp + h * hd
+                                                 : kbase + (long long)(j - n_prefix) * ld_row;
+        kv[u] = *reinterpret_cast<const uint4*>(krow + l16 * 8);
+      }
+    }
+    const float* qq = s_q + l16 * 8;
+#pragma unroll
+    for (int u = 0; u < DA_UNROLL; ++u) {
+      const int j = jb + u * DA_WARPS * 2 + sub;
+      float acc = 0.f;
+      if (col_ok)
+        acc = qq[0] * bf16_lo(kv[u].x) + qq[1] * bf16_hi(kv[u].x) + qq[2] * bf16_lo(kv[u].y) +
+              qq[3] * bf16_hi(kv[u].y) + qq[4] * bf16_lo(kv[u].z) + qq[5] * bf16_hi(kv[u].z) +
+              qq[6] * bf16_lo(kv[u].w) + qq[7] * bf16_hi(kv[u].w);
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (j < total) {
+        const bool vis = j < n_prefix || (j - n_prefix) >= pad;
+        if (!vis) acc = -INFINITY;
+        if (l16 == 0) s_score[j] = acc;
+        lmax = fmaxf(lmax, acc);
+      }
     }
   }
 #pragma unroll
@@ -64,7 +81,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
   if (lane == 0) s_red[warp] = lmax;
   __syncthreads();
   float m = s_red[0];
-  for (int w = 1; w < DA_THREADS / 32; ++w) m = fmaxf(m, s_red[w]);
+  for (int w = 1; w < DA_WARPS; ++w) m = fmaxf(m, s_red[w]);
   __syncthreads();
   float lsum = 0.f;
   for (int j = tid; j < total; j += DA_THREADS) {
@@ -77,16 +94,45 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,
   if (lane == 0) s_red[warp] = lsum;
   __syncthreads();
   float denom = 0.f;
-  for (int w = 0; w < DA_THREADS / 32; ++w) denom += s_red[w];
-  // output: thread c accumulates column c over all keys (coalesced across the block)
-  if (tid < hd) {
-    float acc = 0.f;
-    for (int j = 0; j < total; ++j) {
-      const __nv_bfloat16* vrow = j < n_prefix ? pv + (long long)j * ldp + h * hd
-                                               : vc + (long long)b * ld_seq + (long long)(j - n_prefix) * ld_row + h * hd;
-      acc = fmaf(s_score[j], __bfloat162float(vrow[tid]), acc);
+  for (int w = 0; w < DA_WARPS; ++w) denom += s_red[w];
+  // ---- output: warp w takes keys w, w + 8, ...; lane l the columns [4l, 4l + 4); DA_UNROLL rows
+  // in flight; the warps' partial sums meet in shared memory.
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool vcol_ok = lane * 4 < hd;
+  for (int jb = warp; jb < total; jb += DA_WARPS * DA_UNROLL) {
+    uint2 vv[DA_UNROLL];
+    float pj[DA_UNROLL];
+#pragma unroll
+    for (int u = 0; u < DA_UNROLL; ++u) {
+      const int j = jb + u * DA_WARPS;
+      vv[u] = make_uint2(0u, 0u);
+      pj[u] = 0.f;
+      if (j < total) {
+        pj[u] = s_score[j];
+        if (vcol_ok) {
+          const __nv_bfloat16* vrow = j < n_prefix ? pv + (long long)j * ldp + h * hd
+                                                   : vbase + (long long)(j - n_prefix) * ld_row;
+          vv[u] = *reinterpret_cast<const uint2*>(vrow + lane * 4);
+        }
+      }
     }
-    out[(long long)b * ldo + h * hd + tid] = __float2bfloat16(acc / denom);
+#pragma unroll
+    for (int u = 0; u < DA_UNROLL; ++u) {
+      acc[0] = fmaf(pj[u], bf16_lo(vv[u].x), acc[0]);
+      acc[1] = fmaf(pj[u], bf16_hi(vv[u].x), acc[1]);
+      acc[2] = fmaf(pj[u], bf16_lo(vv[u].y), acc[2]);
+      acc[3] = fmaf(pj[u], bf16_hi(vv[u].y), acc[3]);
+    }
+  }
+  if (vcol_ok) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s_part[warp][lane * 4 + c] = acc[c];
+  }
+  __syncthreads();
+  if (tid < hd) {
+    float o = 0.f;
+    for (int w = 0; w < DA_WARPS; ++w) o += s_part[w][tid];
+    out[(long long)b * ldo + h * hd + tid] = __float2bfloat16(o / denom);
   }
 }
 

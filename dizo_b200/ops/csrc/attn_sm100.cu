@@ -24,6 +24,7 @@
 // tile while the other does its exps.
 #include "common.cuh"
 #include "host_util.h"
+#include "attn_args.h"
 
 namespace dz {
 
@@ -32,18 +33,6 @@ constexpr int A_BKV = 128;   // keys per block
 constexpr int A_THREADS = 320;
 constexpr int A_KV_STAGES = 2;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;  // log2 units
-
-struct AttnArgs {
-  int B, L, H, hd;
-  int n_prefix;
-  long long ld_out;          // row stride of the context output (elements)
-  __nv_bfloat16* out;        // [B*L, ld_out], head h at columns [h*hd, (h+1)*hd)
-  const int* pad_left;       // [B] or null
-  float* lse;                // [B, H, L] or null: log2-domain log-sum-exp of every query row
-  float scale_log2;          // softmax scale * log2(e)
-  int q_col0, k_col0, v_col0;  // first column of the Q / K / V sections inside the QKV rows
-  uint32_t* err;
-};
 
 template <int HDP>
 struct AttnSmem {
@@ -382,9 +371,18 @@ static int launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const CU
   return cuda_rc(cudaGetLastError());
 }
 
+// sixteen-softmax-warp variant (attn16_sm100.cu)
+int launch_attn16_hd(int hdp, const CUtensorMap& tmQ, const CUtensorMap& tmKV, const CUtensorMap& tmPK,
+                     const CUtensorMap& tmPV, const AttnArgs& a, cudaStream_t stream);
+static int g_attn_variant = 0;
+
 }  // namespace dz
 
 using namespace dz;
+
+// 0: one thread per query row (8 softmax warps); 1: two threads per row (16 softmax warps)
+extern "C" void dz_attn_set_variant(int v) { g_attn_variant = v; }
+extern "C" int dz_attn_get_variant() { return g_attn_variant; }
 
 // qkv: [B*L, ld_qkv] bf16 with Q at columns [q_col0, q_col0 + H*hd), K at k_col0, V at v_col0.
 // out: [B*L, ld_out] bf16.  prefix_k / prefix_v: [n_prefix, ld_prefix] bf16 or null.
@@ -424,6 +422,7 @@ extern "C" int dz_attn_fwd_lse(const void* qkv, long long ld_qkv, int q_col0, in
   a.out = (__nv_bfloat16*)out; a.pad_left = pad_left; a.lse = lse;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.q_col0 = q_col0; a.k_col0 = k_col0; a.v_col0 = v_col0; a.err = err;
+  if (g_attn_variant == 1) return launch_attn16_hd(hdp, tmQ, tmKV, tmPK, tmPV, a, stream);
   if (hdp == 64) return launch_attn<64>(tmQ, tmKV, tmPK, tmPV, a, stream);
   return launch_attn<128>(tmQ, tmKV, tmPK, tmPV, a, stream);
 }

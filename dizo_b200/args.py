@@ -143,6 +143,7 @@ class OurArguments:
     eval_batch_size: int = 16               # candidates scored per forward in evaluation
     synthetic_task: bool = False            # seeded uniform ids + Bernoulli labels (no dataset)
     synthetic_seq_len: int = 64
+    heartbeat_timeout: float = 0.0          # > 0: ranks report every step through the store; a silent peer raises PeerLost
     zo_cuda_graph: bool = False             # replay each ZO step as one CUDA graph (launch-bound small models)
     profile_steps: Optional[str] = None     # "a:b": NVTX range + per-phase device timers
     metrics_jsonl: Optional[str] = None

@@ -4,7 +4,10 @@ Each rank writes ``(step, wall time)`` under its own key after every step and, b
 launches the next one, reads its peers' keys; a peer whose heartbeat is older than
 ``stale_after`` seconds (or that is more than ``max_lag`` steps behind) raises
 :class:`PeerLost` on the host, before any kernel or collective that would wait for that peer is
-launched.  The reference has no failure detection at all (its only signal handling is the
+launched.  ``sync(step)`` is the strict form the trainer uses: report, then wait on the host until
+every peer has reported the same step (a store poll, about a millisecond per step), so a rank
+that left between two steps is noticed before the step's first collective instead of inside it.
+The reference has no failure detection at all (its only signal handling is the
 SIGUSR1 callback, large_models/utils.py:291-315).
 """
 from __future__ import annotations
@@ -48,3 +51,17 @@ class Heartbeat:
                 raise PeerLost(f"rank {r} has not reported for {now - t:.1f}s (last step {s})")
             if self.max_lag is not None and step - s > self.max_lag:
                 raise PeerLost(f"rank {r} is {step - s} steps behind")
+
+    def sync(self, step: int, poll: float = 0.001) -> None:
+        """Report ``step`` and wait (on the host) until every peer has reported it too."""
+        self.beat(step)
+        t0 = time.time()
+        while True:
+            behind = {r: s for r, (s, _) in self.peers().items() if s < step}
+            if not behind:
+                return
+            if time.time() - t0 > self.stale_after:
+                r, s = next(iter(behind.items()))
+                raise PeerLost(f"rank {r} did not reach step {step} within {self.stale_after:.1f}s "
+                               f"(last reported step {s})")
+            time.sleep(poll)

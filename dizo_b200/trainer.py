@@ -120,6 +120,15 @@ class OurTrainer:
         self._phase_ms: Dict[str, float] = {}
         self._metrics_f = None
         self._graphs: dict = {}
+        # host-side failure detection: every rank reports its step through the rendezvous store and
+        # looks at its peers before it launches the next step (nothing on the device waits for a
+        # peer that is known to be gone)
+        self._heartbeat = None
+        hb_t = float(getattr(args, "heartbeat_timeout", 0.0) or 0.0)
+        if hb_t > 0 and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            from .parallel.health import Heartbeat
+            self._heartbeat = Heartbeat(dist.distributed_c10d._get_default_store(), dist.get_rank(),
+                                        dist.get_world_size(), stale_after=hb_t)
         on = dist.is_available() and dist.is_initialized() and dp_group is not False
         self._rank = dist.get_rank(dp_group) if on else 0
         # the one process that writes files (under tensor parallelism every rank has data rank 0)
@@ -464,6 +473,8 @@ class OurTrainer:
         for epoch, step_in_epoch, spe, inputs in stream:
             if self.state.global_step >= self.state.max_steps:
                 break
+            if self._heartbeat is not None:
+                self._heartbeat.sync(self.state.global_step)       # raises PeerLost on the host
             profiling = prof is not None and prof[0] <= self.state.global_step < prof[1]
             on_gpu = self.model.device.type == "cuda"
             ev = None

@@ -144,3 +144,51 @@ def test_dead_peer_is_reported_by_heartbeat():
     outs = _run_ranks(DEAD_PEER_SCRIPT, 2, timeout=120)
     rc0, out0 = outs[0]
     assert rc0 == 9 and "PEER_LOST" in out0, out0[-2000:]
+
+
+TRAINER_PEER_SCRIPT = textwrap.dedent('''
+    import datetime, os, sys, time, torch, torch.distributed as dist
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=60))
+    from dizo_b200.args import OurArguments
+    from dizo_b200.models.opt import OPTModel, preset
+    from dizo_b200.parallel.health import PeerLost
+    from dizo_b200.tasks import SyntheticDataset
+    from dizo_b200.trainer import OurTrainer
+    from dizo_b200.utils import (DataCollatorWithPaddingAndNesting, StubTokenizer, TrainerCallback,
+                                 encode_prompt)
+    rank = dist.get_rank()
+    tmp = os.environ["HB_TMP"]
+    a = OurArguments(trainer="zo", learning_rate=1e-3, max_steps=200, per_device_train_batch_size=2,
+                     train_as_classification=True, zo_eval_steps=100000, output_dir=os.path.join(tmp, f"o{rank}"),
+                     save_steps=0, task_name="Synthetic", model_name="opt-tiny", max_length=64,
+                     heartbeat_timeout=2.0)
+    task = SyntheticDataset(n_train=64, n_valid=8)
+    tok = StubTokenizer(["terrible", "great", "It", "was", "fine", "dull", "film"])
+    model = OPTModel(preset("opt-tiny"), "cpu", torch.float32).init_random(0)
+    feats = []
+    for smp in task.samples["train"]:
+        enc, ol = encode_prompt(task, task.get_template(), [], smp, tok, max_length=64)
+        gold = smp.candidates.index(smp.correct_candidate)
+        feats.append([{"input_ids": enc[i], "labels": gold, "option_len": ol[i], "num_options": 2} for i in range(2)])
+
+    class Leave(TrainerCallback):
+        def on_step_end(self, args, state, control, **kw):
+            if rank == 1 and state.global_step == 3:
+                os._exit(0)                 # between steps, nothing in flight
+            time.sleep(0.05)
+    tr = OurTrainer(model, a, train_dataset=feats, processing_class=tok,
+                    data_collator=DataCollatorWithPaddingAndNesting(tok, pad_to_multiple_of=8), task=task,
+                    callbacks=[Leave()])
+    try:
+        tr.train()
+        print("NOT_DETECTED")
+    except PeerLost as e:
+        print("PEER_LOST at step", tr.state.global_step, e)
+        os._exit(9)
+''')
+
+
+def test_trainer_stops_on_the_host_when_a_peer_leaves(tmp_path):
+    outs = _run_ranks(TRAINER_PEER_SCRIPT, 2, timeout=200, extra_env={"HB_TMP": str(tmp_path)})
+    rc0, out0 = outs[0]
+    assert "PEER_LOST" in out0 and rc0 == 9, out0[-3000:]

@@ -77,4 +77,13 @@ def test_cli_training_over_a_pipeline(tmp_path):
     from dizo_b200.utils.checkpoint import load_weights
     sd = load_weights(str(ck))
     assert "model.decoder.layers.0.fc1.weight" in sd and "model.decoder.final_layer_norm.weight" in sd
+    # the checkpoint holds full tensors: it loads into a single-process model (another layout) as it is
+    import torch
+    from dizo_b200.models.opt import OPTModel, preset
+    from dizo_b200.utils.checkpoint import load_checkpoint
+    solo = OPTModel(preset("opt-tiny"), "cpu", torch.float32)
+    missing = solo.load_state_dict(sd, strict=True)
+    assert not missing
+    load_checkpoint(str(ck), solo)
+    assert torch.equal(solo.param("model.decoder.layers.1.fc2.weight"), sd["model.decoder.layers.1.fc2.weight"])
     assert any(f.endswith(".json") for f in os.listdir(tmp_path / "result"))

@@ -88,7 +88,7 @@ class Framework:
             if cfg_path and os.path.exists(cfg_path):
                 with open(cfg_path) as f:
                     cfg = OPTConfig.from_hf(json.load(f))
-                state = load_weights(path)
+                state = load_weights(path, lazy=True)       # one tensor at a time: every rank keeps its slice
             else:
                 key = os.path.basename(path.rstrip("/")).lower().replace("opt1p3b", "opt-1.3b")
                 cfg = preset(key)

@@ -84,7 +84,72 @@ def save_weights(out: str, state_dict: dict) -> str:
     return p
 
 
-def load_weights(path: str) -> dict:
+class LazyWeights:
+    """Read-only mapping name -> tensor over a Hugging Face checkpoint directory that materialises one
+    tensor (safetensors) or one shard (``.bin``) at a time, so loading OPT-66B on eight ranks does not
+    hold eight full state dicts in host memory: every rank pulls a tensor, keeps its slice, drops it."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self._where: dict[str, str] = {}
+        self._safe = True
+        self._bin_cache: tuple[str, dict] | None = None
+        st, sti = os.path.join(path, "model.safetensors"), os.path.join(path, "model.safetensors.index.json")
+        pb, pbi = os.path.join(path, "pytorch_model.bin"), os.path.join(path, "pytorch_model.bin.index.json")
+        if os.path.exists(st):
+            from safetensors import safe_open
+            with safe_open(st, "pt") as f:
+                self._where = {k: "model.safetensors" for k in f.keys()}
+        elif os.path.exists(sti):
+            with open(sti) as f:
+                self._where = dict(json.load(f)["weight_map"])
+        elif os.path.exists(pbi):
+            self._safe = False
+            with open(pbi) as f:
+                self._where = dict(json.load(f)["weight_map"])
+        elif os.path.exists(pb):
+            self._safe = False
+            self._bin_cache = ("pytorch_model.bin", torch.load(pb, map_location="cpu", weights_only=True))
+            self._where = {k: "pytorch_model.bin" for k in self._bin_cache[1]}
+        else:
+            raise CheckpointError(f"{path}: no model.safetensors / pytorch_model.bin")
+
+    def __contains__(self, name) -> bool:
+        return name in self._where
+
+    def keys(self):
+        return self._where.keys()
+
+    def __iter__(self):
+        return iter(self._where)
+
+    def __len__(self) -> int:
+        return len(self._where)
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        shard = self._where[name]
+        if self._safe:
+            from safetensors import safe_open
+            with safe_open(os.path.join(self.path, shard), "pt") as f:
+                return f.get_tensor(name)
+        if self._bin_cache is None or self._bin_cache[0] != shard:
+            self._bin_cache = (shard, torch.load(os.path.join(self.path, shard), map_location="cpu",
+                                                 weights_only=True))
+        return self._bin_cache[1][name]
+
+    def get(self, name: str, default=None):
+        return self[name] if name in self._where else default
+
+    def items(self):
+        for k in self._where:
+            yield k, self[k]
+
+
+def load_weights(path: str, lazy: bool = False):
+    """The checkpoint's state dict; ``lazy`` returns a :class:`LazyWeights` view instead of reading
+    every tensor up front."""
+    if lazy:
+        return LazyWeights(path)
     st = os.path.join(path, "model.safetensors")
     if os.path.exists(st):
         from safetensors.torch import load_file
@@ -158,7 +223,7 @@ def save_checkpoint(out: str, model, trainer=None, write: bool = True) -> None:
 def load_checkpoint(path: str, model, trainer=None, verify: bool = True) -> None:
     if verify:
         verify_checkpoint(path)
-    model.load_state_dict(load_weights(path), strict=False)
+    model.load_state_dict(load_weights(path, lazy=True), strict=False)
     if trainer is None:
         return
     from ..trainer import TrainerState

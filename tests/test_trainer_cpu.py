@@ -226,3 +226,31 @@ def test_run_main_end_to_end(tmp_path, monkeypatch):
                "--max_length", "128"])
     assert rc == 0
     assert result_file_tag(OurArguments(task_name="X", model_name="a/b", num_train=3, tag="t")) == "X-b-ntrain3-t"
+
+
+def test_lazy_weights_over_sharded_checkpoints(tmp_path):
+    from safetensors.torch import save_file
+    from dizo_b200.utils.checkpoint import LazyWeights, load_weights
+    cfg = preset("opt-tiny")
+    m = OPTModel(cfg, "cpu", torch.float32).init_random(1)
+    sd = {k: v for k, v in m.state_dict().items() if k != "lm_head.weight"}
+    names = sorted(sd)
+    half = len(names) // 2
+    for kind in ("safetensors", "bin"):
+        d = tmp_path / kind
+        os.makedirs(d)
+        parts = {f"part-1.{kind}": names[:half], f"part-2.{kind}": names[half:]}
+        for fn, ks in parts.items():
+            if kind == "safetensors":
+                save_file({k: sd[k].contiguous() for k in ks}, str(d / fn))
+            else:
+                torch.save({k: sd[k] for k in ks}, d / fn)
+        idx = "model.safetensors.index.json" if kind == "safetensors" else "pytorch_model.bin.index.json"
+        json.dump({"weight_map": {k: fn for fn, ks in parts.items() for k in ks}}, open(d / idx, "w"))
+        lazy = load_weights(str(d), lazy=True)
+        assert isinstance(lazy, LazyWeights) and set(lazy.keys()) == set(names) and len(lazy) == len(names)
+        m2 = OPTModel(cfg, "cpu", torch.float32)
+        assert m2.load_state_dict(lazy, strict=True) == []
+        assert torch.equal(m2.arena.data, m.arena.data) and torch.equal(m2.frozen.data, m.frozen.data)
+        full = load_weights(str(d))
+        assert set(full) == set(names) and torch.equal(full[names[0]], lazy[names[0]])

@@ -67,6 +67,82 @@ def verify_checkpoint(path: str) -> None:
             raise CheckpointError(f"{path}: {name} is corrupted (checksum mismatch)")
 
 
+def iter_full_tensors(model):
+    """(name, full tensor) pairs in Hugging Face order.  For sharded models each tensor is gathered
+    on its own (a collective: every rank of the model's group iterates), so nothing larger than one
+    full tensor exists on a device at a time."""
+    if hasattr(model, "gather_full"):                      # tensor parallel / FSDP
+        tied = None
+        for n in model.hf_order:
+            t = model.gather_full(n, model.param(n))
+            if n == "model.decoder.embed_tokens.weight":
+                tied = t
+            yield n, t
+        if not model.untied and tied is not None:
+            yield "lm_head.weight", tied
+    elif hasattr(model, "gather_state_dict"):              # pipeline stages
+        yield from model.gather_state_dict().items()
+    else:
+        yield from model.state_dict().items()
+
+
+def save_weights_sharded(out: str, items, write: bool = True, max_shard_bytes: int = 8 << 30) -> list[str]:
+    """Stream (name, tensor) pairs into safetensors files of at most ``max_shard_bytes``: one
+    ``model.safetensors`` when everything fits, otherwise ``model-0000i-of-0000n.safetensors`` plus
+    ``model.safetensors.index.json`` (the Hugging Face sharded layout).  Tensors are moved to the
+    host one at a time; with ``write`` False the pairs are only consumed (the gathers behind them
+    are collective)."""
+    from safetensors.torch import save_file
+    if write:
+        os.makedirs(out, exist_ok=True)
+    shards: list[tuple[str, list[str]]] = []
+    cur: dict = {}
+    cur_bytes = 0
+    total = 0
+    embed_ptr = None
+
+    def flush():
+        nonlocal cur, cur_bytes
+        if cur:
+            tmp = f"model-part{len(shards) + 1:05d}.safetensors"
+            save_file(cur, os.path.join(out, tmp), metadata={"format": "pt"})
+            shards.append((tmp, list(cur)))
+            cur, cur_bytes = {}, 0
+
+    for name, t in items:
+        if not write:
+            continue
+        if name == "lm_head.weight" and embed_ptr is not None and t.data_ptr() == embed_ptr:
+            continue                                        # tied: stored once, as Hugging Face does
+        if name == "model.decoder.embed_tokens.weight":
+            embed_ptr = t.data_ptr()
+        c = t.detach().to("cpu").contiguous()
+        if c.data_ptr() == t.data_ptr():
+            c = c.clone()
+        nb = c.numel() * c.element_size()
+        if cur and cur_bytes + nb > max_shard_bytes:
+            flush()
+        cur[name] = c
+        cur_bytes += nb
+        total += nb
+    if not write:
+        return []
+    flush()
+    if len(shards) == 1:
+        os.replace(os.path.join(out, shards[0][0]), os.path.join(out, "model.safetensors"))
+        return ["model.safetensors"]
+    weight_map, names = {}, []
+    for i, (tmp, keys) in enumerate(shards):
+        final = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        os.replace(os.path.join(out, tmp), os.path.join(out, final))
+        names.append(final)
+        for k in keys:
+            weight_map[k] = final
+    with open(os.path.join(out, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=2)
+    return names
+
+
 def save_weights(out: str, state_dict: dict) -> str:
     os.makedirs(out, exist_ok=True)
     sd = {k: v.detach().cpu().contiguous() for k, v in state_dict.items()}
@@ -186,11 +262,11 @@ def full_state_dict(model) -> dict:
     return model.state_dict()
 
 
-def save_checkpoint(out: str, model, trainer=None, write: bool = True) -> None:
+def save_checkpoint(out: str, model, trainer=None, write: bool = True, max_shard_bytes: int = 8 << 30) -> None:
     """Write a checkpoint directory.  With a sharded model every rank calls this (the gathers are
     collective) and only the rank with ``write`` touches the file system; the files hold full
-    tensors, so a checkpoint can be resumed under a different parallel layout."""
-    sd = full_state_dict(model)
+    tensors (streamed one at a time into safetensors shards), so a checkpoint can be resumed under
+    a different parallel layout."""
     ar = model.arena
     anchor = None
     if trainer is not None and trainer.dizo_trainer is not None:
@@ -199,10 +275,9 @@ def save_checkpoint(out: str, model, trainer=None, write: bool = True) -> None:
                   for n in ar.slot_names}
         if hasattr(model, "gather_dict"):              # pipeline stages hold disjoint sets of tensors
             anchor = model.gather_dict(anchor)
+    save_weights_sharded(out, iter_full_tensors(model), write=write, max_shard_bytes=max_shard_bytes)
     if not write:
         return
-    os.makedirs(out, exist_ok=True)
-    save_weights(out, sd)
     with open(os.path.join(out, "config.json"), "w") as f:
         json.dump(model.config.to_hf_dict(), f, indent=2)
     if trainer is not None:

@@ -133,6 +133,24 @@ def test_hf_can_load_saved_checkpoint(tmp_path):
     assert (ref - mine).abs().max().item() < 1e-4
 
 
+def test_sharded_checkpoint_layout_loads_in_hf_and_lazily(tmp_path):
+    from transformers import OPTForCausalLM
+    tr, _, _ = _trainer(tmp_path)
+    out = str(tmp_path / "sharded")
+    save_checkpoint(out, tr.model, trainer=None, max_shard_bytes=200_000)
+    files = sorted(os.listdir(out))
+    shards = [f for f in files if f.startswith("model-") and f.endswith(".safetensors")]
+    assert len(shards) >= 3 and "model.safetensors.index.json" in files and "model.safetensors" not in files
+    assert shards[0] == f"model-00001-of-{len(shards):05d}.safetensors"
+    verify_checkpoint(out)
+    hf = OPTForCausalLM.from_pretrained(out).eval()
+    ids = torch.randint(4, 500, (2, 12))
+    assert (hf(input_ids=ids).logits - tr.model.logits(make_batch(ids)).view(2, 12, -1)).abs().max().item() < 1e-4
+    m2 = OPTModel(preset("opt-tiny"), "cpu", torch.float32)
+    load_checkpoint(out, m2)
+    assert torch.equal(m2.arena.data, tr.model.arena.data)
+
+
 def test_sigusr1_callback_saves_and_stops(tmp_path):
     tr, _, _ = _trainer(tmp_path, max_steps=50)
     cb = SIGUSR1Callback(exit_on_end=False)

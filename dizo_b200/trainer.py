@@ -32,7 +32,7 @@ from .engine import DiZOProjector, ZOEngine
 from .metrics import calculate_metric, f1
 from .models.opt import Batch, OPTModel, Transform
 from .utils import TrainerCallback, TrainerControl
-from .utils.checkpoint import full_state_dict, load_checkpoint, save_checkpoint
+from .utils.checkpoint import load_checkpoint, save_checkpoint
 
 logger = logging.getLogger(__name__)
 
@@ -411,7 +411,12 @@ class OurTrainer:
             self.objective = metrics[name]
             self.state.best_metric = float(metrics[name])
             # kept in host memory, and actually restorable (load_best_model_at_end)
-            self.best_model_ckpt = {k: v.detach().cpu() for k, v in full_state_dict(self.model).items()}
+            if self._sharded:
+                # every rank keeps its own shards (a full copy per rank would not fit the host for the
+                # model sizes that are sharded in the first place)
+                self.best_model_ckpt = {n: self.model.param(n).detach().cpu().clone() for n in self.model.hf_order}
+            else:
+                self.best_model_ckpt = {k: v.detach().cpu() for k, v in self.model.state_dict().items()}
 
     # ------------------------------------------------------------------ checkpoints
     def save_model(self, output_dir: Optional[str] = None) -> None:
@@ -533,7 +538,11 @@ class OurTrainer:
         if a.load_best_model_at_end and self.best_model_ckpt is not None:
             if self._world > 1:
                 dist.barrier(self.dp_group)
-            self.model.load_state_dict(self.best_model_ckpt)
+            if self._sharded:
+                for n, t in self.best_model_ckpt.items():
+                    self.model.param(n).copy_(t)
+            else:
+                self.model.load_state_dict(self.best_model_ckpt)
         runtime = time.time() - t_start
         done = max(1, self.state.global_step - start_step)
         metrics = {"train_runtime": round(runtime, 4),

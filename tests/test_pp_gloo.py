@@ -61,7 +61,8 @@ CLI_SCRIPT = textwrap.dedent('''
                "--num_train", "16", "--num_dev", "4", "--num_eval", "8", "--train_set_seed", "0", "--max_steps", "4",
                "--learning_rate", "1e-4", "--per_device_train_batch_size", "4", "--train_as_classification",
                "--output_dir", os.path.join(tmp, "out"), "--save_steps", "2", "--zo_eval_steps", "2",
-               "--max_length", "32", "--dizo_interval", "2", "--dizo_max_iters", "2", "--pp", "2"])
+               "--max_length", "32", "--dizo_interval", "2", "--dizo_max_iters", "2", "--pp", "2",
+               "--load_best_model_at_end"])
     assert rc == 0
     print("CLI_OK", dist.get_rank())
 ''')

@@ -126,6 +126,9 @@ def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[
     which is kept, as Hugging Face does).  ``transform`` is accepted for API symmetry and must
     be None: perturb in place around the call when decoding under a perturbation."""
     assert transform is None, "decode under a perturbation by perturbing in place around generate()"
+    if type(model).hidden_states is not OPTModel.hidden_states:
+        raise NotImplementedError("autoregressive decoding runs on replicated parameters; the tensor-parallel, "
+                                  "FSDP and pipeline layouts cover training and candidate scoring only")
     dev = model.device
     ids = torch.as_tensor(input_ids).long()
     B0, L0 = ids.shape

@@ -239,6 +239,28 @@ def run_ours(a, world, rank, local):
                "h2d_bytes_per_step": hb[0].nbytes(), "d2h_bytes_per_step": 4, "last_loss": last}
 
     nparam = model.arena.trainable_numel()
+    # ---- perturb bandwidth: one pass of the in-flight perturbation over every parameter group
+    #      (theta + eps z into the per-layer staging buffer, z regenerated), as each forward does;
+    #      bytes = parameters read + staged copy written.  The update sweep is the same kernel in place.
+    sweep_gbs = None
+    if par == "dp" and model.arena.trainable_numel() > 0:
+        from dizo_b200.models.opt import Transform
+        groups = model.arena.groups()
+        biggest = max(model.arena.group_numel(g) for g in groups)
+
+        def one_pass(seed):
+            tr = Transform(seed=seed, coef=1e-3)
+            for k, g in enumerate(groups):
+                model._sweep_group(g, tr, model._staging_for(("bench", k % 2), biggest))
+        one_pass(1)
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record()
+        for i in range(3):
+            one_pass(2 + i)
+        w1.record()
+        torch.cuda.synchronize()
+        sweep_ms = max_over_ranks(w0.elapsed_time(w1) / 3, world)
+        sweep_gbs = 2 * model.arena.trainable_numel() * model.arena.data.element_size() / sweep_ms / 1e6
     out = {
         "metric": "zo_train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
@@ -251,7 +273,7 @@ def run_ours(a, world, rank, local):
                    "zo_step_ms": step_ms, "gamma_search_ms": search_ms, "gamma_search_period": 50,
                    "l2_policy": "per-step working set (parameters) far exceeds L2; no flush needed",
                    "trainable_params": nparam},
-        "sweep_gbs_note": "see profiles/ for perturb+update GB/s",
+        "perturb_update_gbs": sweep_gbs,
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
     }
     return out

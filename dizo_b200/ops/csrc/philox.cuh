@@ -33,15 +33,11 @@ __host__ __device__ __forceinline__ Philox4 philox4x32(uint32_t c0, uint32_t c1,
                                                        uint32_t c3, uint32_t k0, uint32_t k1) {
 #pragma unroll
   for (int r = 0; r < ROUNDS; ++r) {
-#ifdef __CUDA_ARCH__
-    uint32_t hi0 = __umulhi(PHILOX_M0, c0);
-    uint32_t hi1 = __umulhi(PHILOX_M1, c2);
-#else
-    uint32_t hi0 = (uint32_t)(((uint64_t)PHILOX_M0 * c0) >> 32);
-    uint32_t hi1 = (uint32_t)(((uint64_t)PHILOX_M1 * c2) >> 32);
-#endif
-    uint32_t lo0 = PHILOX_M0 * c0;
-    uint32_t lo1 = PHILOX_M1 * c2;
+    // one widening 32x32->64 multiply per product, both halves used
+    const uint64_t p0 = static_cast<uint64_t>(PHILOX_M0) * c0;
+    const uint64_t p1 = static_cast<uint64_t>(PHILOX_M1) * c2;
+    const uint32_t hi0 = static_cast<uint32_t>(p0 >> 32), lo0 = static_cast<uint32_t>(p0);
+    const uint32_t hi1 = static_cast<uint32_t>(p1 >> 32), lo1 = static_cast<uint32_t>(p1);
     uint32_t n0 = hi1 ^ c1 ^ k0;
     uint32_t n2 = hi0 ^ c3 ^ k1;
     c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;

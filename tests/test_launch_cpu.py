@@ -31,3 +31,27 @@ def test_first_order_and_icl_recipes():
     assert a.num_train == 32 and a.num_eval == 1000 and a.trainer == "none" and a.verbose
     with pytest.raises(ValueError):
         build_argv("dizo", {})
+
+
+def test_tensor_parallel_batch_fitting():
+    """Token rows are padded to 128-row tiles per rank; caller row indices are translated."""
+    import types
+    import torch
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.parallel.tp import TPOPTModel
+    dummy = types.SimpleNamespace(tp=8)
+    b = synthetic_batch(0, 3, 40, 1000, pad_left=5)
+    fitted = TPOPTModel._fit(dummy, b)
+    Bp, Lp = fitted.input_ids.shape
+    assert Lp == 128 and (Bp * (Lp // 128)) % 8 == 0 and Bp >= 3
+    assert torch.equal(fitted.input_ids[:3, Lp - 40:], b.input_ids)
+    assert (fitted.input_ids[:3, :Lp - 40] == 1).all() and (fitted.input_ids[3:] == 1).all()
+    assert fitted.pad_left[:3].tolist() == [5 + Lp - 40] * 3 and fitted.pad_left[3:].tolist() == [Lp] * (Bp - 3)
+    L0, Lp2 = dummy._row_map
+    rows = b.rows.long()
+    mapped = (rows // L0) * Lp2 + rows % L0 + (Lp2 - L0)
+    assert torch.equal(fitted.input_ids.reshape(-1)[mapped], b.input_ids.reshape(-1)[rows])
+    # already fitting batches pass through untouched
+    dummy2 = types.SimpleNamespace(tp=2)
+    b2 = synthetic_batch(0, 2, 128, 1000)
+    assert TPOPTModel._fit(dummy2, b2) is b2 and dummy2._row_map is None

@@ -148,20 +148,30 @@ def make_fo_loss(model: OPTModel) -> Callable[[Batch, torch.Tensor], torch.Tenso
 
 
 def fo_training_step(trainer, inputs) -> torch.Tensor:
-    """One AdamW step of ordinary fine-tuning over the trainable arena (``--trainer regular``)."""
+    """One AdamW step of ordinary fine-tuning over the trainable arena (``--trainer regular``, the
+    reference's comparison arm, large_models/finetune.sh).  ``inputs`` is one batch or a list of
+    micro-batches whose gradients are accumulated (mean) before the step; under data parallelism
+    the arena gradient is averaged over the ranks."""
+    import torch.distributed as dist
     model, a = trainer.model, trainer.args
-    batch = trainer._to_batch(inputs)
+    micro = inputs if isinstance(inputs, list) else [inputs]
     data = model.arena.data
     if getattr(trainer, "_fo_opt", None) is None:
         data.requires_grad_(True)
         trainer._fo_opt = torch.optim.AdamW([data], lr=a.learning_rate, weight_decay=a.weight_decay)
     for g in trainer._fo_opt.param_groups:
         g["lr"] = trainer._get_learning_rate()
+    total = None
     with torch.enable_grad():
-        loss = functional_loss(model, batch)
-        loss.backward()
+        for one in micro:
+            loss = functional_loss(model, trainer._to_batch(one)) / len(micro)
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+    if trainer._world > 1:
+        dist.all_reduce(data.grad, group=trainer.dp_group if trainer.dp_group is not None else None)
+        data.grad.div_(trainer._world)
     if a.max_grad_norm and a.max_grad_norm > 0:
         torch.nn.utils.clip_grad_norm_([data], a.max_grad_norm)
     trainer._fo_opt.step()
     trainer._fo_opt.zero_grad(set_to_none=True)
-    return loss.detach().reshape(1)
+    return total.reshape(1)

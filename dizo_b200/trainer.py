@@ -452,7 +452,8 @@ class OurTrainer:
         assert a.trainer in ("zo", "regular"), "train() needs --trainer zo|regular"
         n = len(self.train_dataset)
         gb = a.per_device_train_batch_size * self._world
-        steps_per_epoch = max(1, n // gb)
+        accum = max(1, a.gradient_accumulation_steps) if a.trainer == "regular" else 1
+        steps_per_epoch = max(1, n // (gb * accum))
         self.state.max_steps = a.max_steps if a.max_steps > 0 else int(math.ceil(a.num_train_epochs * steps_per_epoch))
         if a.linear_probing:
             from .models.probe import linear_probe
@@ -474,8 +475,18 @@ class OurTrainer:
         tr_loss = 0.0
         start_step = self.state.global_step
         prof = _parse_range(a.profile_steps)
-        stream = self._batches(salt=0, skip_steps=self.state.global_step)
+        stream = self._batches(salt=0, skip_steps=self.state.global_step * accum)
         for epoch, step_in_epoch, spe, inputs in stream:
+            if accum > 1:
+                # one optimiser step = `accum` micro-batches (large_models/finetune.sh splits the batch
+                # this way for the tasks that do not fit)
+                micro = [inputs]
+                for _ in range(accum - 1):
+                    epoch, step_in_epoch, spe, nxt = next(stream)
+                    micro.append(nxt)
+                inputs = micro
+                spe = max(1, spe // accum)
+                step_in_epoch = step_in_epoch // accum
             if self.state.global_step >= self.state.max_steps:
                 break
             if self._heartbeat is not None:
@@ -509,8 +520,9 @@ class OurTrainer:
             if a.logging_nan_inf_filter and (math.isnan(loss) or math.isinf(loss)):
                 loss = tr_loss / max(1, self.state.global_step - start_step)
             tr_loss += loss
-            tokens += int(torch.as_tensor(inputs["input_ids"]).numel()) if not isinstance(inputs, Batch) \
-                else int(inputs.input_ids.numel())
+            for one in (inputs if isinstance(inputs, list) else [inputs]):
+                tokens += int(torch.as_tensor(one["input_ids"]).numel()) if not isinstance(one, Batch) \
+                    else int(one.input_ids.numel())
             self.state.global_step += 1
             self.state.epoch = epoch + (step_in_epoch + 1) / spe
             self._fire("on_step_end")
@@ -527,6 +539,13 @@ class OurTrainer:
             self.loss_list.append(loss)
             if a.trainer == "zo" and self.state.global_step % a.zo_eval_steps == 0 and not a.no_eval:
                 self._in_loop_eval()
+            if a.trainer == "regular" and not a.no_eval and (
+                    (a.evaluation_strategy == "epoch" and step_in_epoch + 1 == spe) or
+                    (a.evaluation_strategy == "steps" and a.eval_steps and self.state.global_step % a.eval_steps == 0)):
+                self._in_loop_eval()
+            if a.trainer == "regular" and a.save_strategy == "epoch" and step_in_epoch + 1 == spe \
+                    and a.save_total_limit != 0:
+                self._save_checkpoint()
             if a.save_strategy == "steps" and a.save_steps > 0 and self.state.global_step % a.save_steps == 0 \
                     and a.save_total_limit != 0:
                 self._save_checkpoint()

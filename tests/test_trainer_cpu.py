@@ -272,3 +272,29 @@ def test_lazy_weights_over_sharded_checkpoints(tmp_path):
         assert torch.equal(m2.arena.data, m.arena.data) and torch.equal(m2.frozen.data, m.frozen.data)
         full = load_weights(str(d))
         assert set(full) == set(names) and torch.equal(full[names[0]], lazy[names[0]])
+
+
+def test_first_order_trainer_accumulation_equals_large_batch(tmp_path):
+    """--trainer regular: two micro-batches of 2 accumulate to the step of one batch of 4; the loss
+    falls; evaluation runs at the end of every epoch."""
+    tr_a, _, _ = _trainer(tmp_path / "a", trainer="regular", learning_rate=1e-3, max_steps=6,
+                          per_device_train_batch_size=4, lr_scheduler_type="constant", max_grad_norm=0.0)
+    tr_b, _, _ = _trainer(tmp_path / "b", trainer="regular", learning_rate=1e-3, max_steps=6,
+                          per_device_train_batch_size=2, gradient_accumulation_steps=2,
+                          lr_scheduler_type="constant", max_grad_norm=0.0)
+    ma, mb = tr_a.train(), tr_b.train()
+    assert abs(ma["train_loss"] - mb["train_loss"]) < 1e-4
+    # AdamW normalises the step, so elements whose gradient is at rounding level may move differently;
+    # the trajectories as a whole coincide
+    ref = OPTModel(preset("opt-tiny"), "cpu", torch.float32).init_random(0).arena.data
+    da, db = tr_a.model.arena.data.detach() - ref, tr_b.model.arena.data.detach() - ref
+    assert da.norm() > 0 and ((da - db).norm() / da.norm()).item() < 0.05
+    tr_d, _, _ = _trainer(tmp_path / "d", trainer="regular", learning_rate=1e-3, max_steps=12,
+                          per_device_train_batch_size=4, lr_scheduler_type="constant")
+    tr_d.train_dataset = tr_d.train_dataset[:4]             # the same four examples every step
+    tr_d.train()
+    assert tr_d.loss_list[-1] < tr_d.loss_list[0] - 0.05
+    tr_c, _, _ = _trainer(tmp_path / "c", trainer="regular", learning_rate=1e-3, max_steps=0, num_train_epochs=2,
+                          per_device_train_batch_size=16, evaluation_strategy="epoch", zo_eval_steps=10 ** 6)
+    tr_c.train()
+    assert tr_c.state.global_step == 8 and len(tr_c.accuracy) == 2      # 64 examples / 16 = 4 steps per epoch

@@ -40,6 +40,17 @@ def test_cli_training_runs_on_gpu(tmp_path, monkeypatch, extra):
     assert 0.0 <= m["accuracy"] <= 1.0 and "dev_accuracy" in m
 
 
+def test_first_order_trainer_runs_on_gpu(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    args = _common(tmp_path, "--gradient_accumulation_steps", "2", "--evaluation_strategy", "steps", "--eval_steps", "3")
+    args[args.index("--trainer") + 1] = "regular"
+    assert main(args) == 0
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    res = [f for f in os.listdir(tmp_path / "result") if f.endswith(".json")]
+    assert 0.0 <= json.load(open(tmp_path / "result" / res[0]))["accuracy"] <= 1.0
+
+
 def test_profiled_steps_report_phase_times(tmp_path, monkeypatch):
     monkeypatch.chdir(tmp_path)
     mj = tmp_path / "metrics.jsonl"

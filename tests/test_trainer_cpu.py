@@ -298,3 +298,43 @@ def test_first_order_trainer_accumulation_equals_large_batch(tmp_path):
                           per_device_train_batch_size=16, evaluation_strategy="epoch", zo_eval_steps=10 ** 6)
     tr_c.train()
     assert tr_c.state.global_step == 8 and len(tr_c.accuracy) == 2      # 64 examples / 16 = 4 steps per epoch
+
+
+def test_linear_probing_end_to_end(tmp_path, monkeypatch):
+    """--linear_probing: features from the forward, logistic regression on the host, coefficients
+    written into the LM-head rows of the class tokens (large_models/trainer.py:855-957)."""
+    monkeypatch.chdir(tmp_path)
+    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--trainer", "zo", "--linear_probing",
+               "--lp_early_stopping", "--num_train", "40", "--num_dev", "8", "--num_eval", "16",
+               "--train_set_seed", "0", "--per_device_train_batch_size", "8", "--train_as_classification", "False",
+               "--output_dir", str(tmp_path / "out"), "--max_length", "64", "--max_steps", "1"])
+    assert rc == 0
+    files = [f for f in os.listdir(tmp_path / "result") if f.endswith(".json")]
+    assert 0.0 <= json.load(open(tmp_path / "result" / files[0]))["accuracy"] <= 1.0
+
+
+def test_non_differentiable_objective_end_to_end(tmp_path, monkeypatch):
+    """--non_diff on a generation task: the ZO loss is minus the F1 of decoded answers
+    (large_models/trainer.py:1544-1568); data from $DIZO_DATA_DIR jsonl files."""
+    d = tmp_path / "data" / "squad"
+    os.makedirs(d)
+    rng = random.Random(0)
+    words = ["fine", "dull", "film", "cast", "plot", "warm", "cold", "score"]
+    for split, n in (("train", 24), ("validation", 8)):
+        with open(d / f"{split}.jsonl", "w") as f:
+            for i in range(n):
+                ctx = " ".join(rng.choice(words) for _ in range(8))
+                ans = ctx.split()[rng.randrange(8)]
+                f.write(json.dumps({"id": str(i), "title": "t", "context": ctx, "question": "which word ?",
+                                    "answers": {"text": [ans], "answer_start": [0]}}) + "\n")
+    monkeypatch.setenv("DIZO_DATA_DIR", str(tmp_path / "data"))
+    monkeypatch.chdir(tmp_path)
+    rc = main(["--task_name", "SQuAD", "--model_name", "opt-tiny", "--trainer", "zo", "--non_diff",
+               "--num_train", "16", "--num_dev", "4", "--num_eval", "4", "--train_set_seed", "0", "--max_steps", "2",
+               "--learning_rate", "1e-4", "--per_device_train_batch_size", "4", "--train_as_classification", "False",
+               "--output_dir", str(tmp_path / "out"), "--max_length", "96", "--max_new_tokens", "3",
+               "--zo_eval_steps", "1000", "--save_steps", "0"])
+    assert rc == 0
+    files = [f for f in os.listdir(tmp_path / "result") if f.endswith(".json")]
+    m = json.load(open(tmp_path / "result" / files[0]))
+    assert "f1" in m and 0.0 <= m["f1"] <= 1.0

@@ -1,7 +1,7 @@
 // Counter-based Gaussian stream shared by every kernel that needs the perturbation z.
 //
 // z for element e of tensor t under seed s is a pure function of (s, t, e):
-//   words = Philox4x32-10(counter = (e >> 3, t, stream, 0), key = (s_lo, s_hi))
+//   words = Philox4x32-7(counter = (e >> 3, t, stream, 0), key = (s_lo, s_hi))
 //   word  = words[(e & 7) >> 1];  u = word & 0xffff for even e, word >> 16 for odd e
 //   z     = T[u],  T[i] = fp16( Phi^-1((i + 0.5) / 65536) )     (65536-entry inverse-CDF table)
 // so one Philox call yields the 8 normals of one 16-byte group of bf16 parameters, z is
@@ -49,12 +49,16 @@ __host__ __device__ __forceinline__ Philox4 philox4x32(uint32_t c0, uint32_t c1,
 
 #ifdef __CUDACC__
 constexpr int GAUSS_TABLE_SIZE = 65536;
+// Rounds of the z stream: Philox4x32 is Crush-resistant from 7 rounds (Salmon et al., SC'11; 10 is the
+// library default) and the sweep spends a third of its time in them.  Must equal Z_PHILOX_ROUNDS of
+// ops/philox.py (the host oracle).  Other streams (gamma draws, stochastic rounding, sampling) keep 10.
+constexpr int Z_PHILOX_ROUNDS = 7;
 
 // The 8 normals of group `grp` (= element index >> 3) of tensor `tid`; `tab` may point to
 // shared or global memory.
 __device__ __forceinline__ void gauss8(const __half* tab, uint64_t seed, uint32_t tid, uint32_t grp,
                                        uint32_t stream, float z[8]) {
-  Philox4 p = philox4x32<10>(grp, tid, stream, 0u, static_cast<uint32_t>(seed),
+  Philox4 p = philox4x32<Z_PHILOX_ROUNDS>(grp, tid, stream, 0u, static_cast<uint32_t>(seed),
                              static_cast<uint32_t>(seed >> 32));
   z[0] = __half2float(tab[p.x & 0xffffu]); z[1] = __half2float(tab[p.x >> 16]);
   z[2] = __half2float(tab[p.y & 0xffffu]); z[3] = __half2float(tab[p.y >> 16]);

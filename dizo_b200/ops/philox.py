@@ -3,7 +3,7 @@
 ``z(seed, tensor_id, e)`` is a pure function of the seed, the tensor's stream id and the
 element index ``e`` inside the *full* tensor:
 
-    words = Philox4x32-10(counter=(e >> 3, tensor_id, stream, 0), key=(seed_lo, seed_hi))
+    words = Philox4x32-7(counter=(e >> 3, tensor_id, stream, 0), key=(seed_lo, seed_hi))
     w     = words[(e & 7) >> 1];  u = w & 0xffff for even e, w >> 16 for odd e
     z     = T[u],   T[i] = float16(Phi^-1((i + 0.5) / 65536))
 
@@ -72,6 +72,13 @@ def gauss_words(words: np.ndarray) -> np.ndarray:
     return out
 
 
+# Rounds of the perturbation stream z.  Philox4x32 is specified with 10 rounds by default and is
+# "Crush-resistant" from 7 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11); the
+# sweep spends a third of its time in the rounds, so z uses 7 (4.7 -> 5.1 TB/s).  The scalar draws of the
+# gamma search and the stochastic-rounding stream keep 10.  Must equal Z_PHILOX_ROUNDS in csrc/philox.cuh.
+Z_PHILOX_ROUNDS = 7
+
+
 def gaussian(seed: int, tensor_id: int, numel: int, elem_base: int = 0, stream: int = 0) -> np.ndarray:
     """z for elements [elem_base, elem_base + numel) of tensor ``tensor_id`` (fp32)."""
     assert elem_base % 8 == 0
@@ -79,7 +86,7 @@ def gaussian(seed: int, tensor_id: int, numel: int, elem_base: int = 0, stream: 
     ngroups = (numel + 7) >> 3
     grp = (np.arange(g0, g0 + ngroups, dtype=np.uint64) & _MASK).astype(np.uint32)
     c = philox4x32(grp, np.uint32(tensor_id), np.uint32(stream), np.uint32(0),
-                   seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+                   seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF, rounds=Z_PHILOX_ROUNDS)
     words = np.stack(c, axis=-1)
     return gauss_words(words).reshape(-1)[:numel]
 

@@ -33,3 +33,34 @@ def test_gaussian_is_layout_invariant():
     # different tensors / seeds decorrelate
     other = philox.gaussian(7, 12, 4096 * 3)
     assert abs(np.corrcoef(full, other)[0, 1]) < 0.05
+
+
+def test_z_stream_statistics_with_reduced_rounds():
+    """The perturbation stream runs Philox4x32 with Z_PHILOX_ROUNDS rounds: uniform 16-bit indices,
+    unit-variance normals, no correlation between neighbouring counters, tensors or seeds."""
+    import numpy as np
+    from dizo_b200.ops import philox as P
+    assert P.Z_PHILOX_ROUNDS == 7
+    n = 1 << 22
+    z = P.gaussian(123, 5, n)
+    assert abs(z.mean()) < 5 / np.sqrt(n) and abs(z.var() - 1.0) < 0.01
+    assert abs(np.mean(z ** 3)) < 0.01 and abs(np.mean(z ** 4) - 3.0) < 0.05
+    # neighbouring elements / neighbouring 8-element groups (consecutive counters)
+    for lag in (1, 2, 7, 8, 9, 64, 4096):
+        c = float(np.mean(z[:-lag] * z[lag:]))
+        assert abs(c) < 5 / np.sqrt(n), (lag, c)
+    # other tensor id, other seed, nearby seed
+    for other in (P.gaussian(123, 6, n), P.gaussian(124, 5, n), P.gaussian(123 + (1 << 32), 5, n)):
+        assert abs(float(np.mean(z * other))) < 5 / np.sqrt(n)
+    # uniformity of the raw 16-bit indices over 4096 coarse bins
+    grp = np.arange(n >> 3, dtype=np.uint32)
+    words = np.stack(P.philox4x32(grp, np.uint32(5), np.uint32(0), np.uint32(0), 123, 0, rounds=P.Z_PHILOX_ROUNDS), -1)
+    idx = np.concatenate([(words & np.uint32(0xFFFF)).ravel(), (words >> np.uint32(16)).ravel()])
+    counts = np.bincount(idx >> 4, minlength=4096).astype(np.float64)
+    expect = idx.size / 4096
+    chi2 = float(((counts - expect) ** 2 / expect).sum())
+    assert abs(chi2 - 4095) < 6 * np.sqrt(2 * 4095), chi2
+    # every bit position of the 32-bit words is balanced
+    for bit in range(32):
+        frac = float(((words >> np.uint32(bit)) & np.uint32(1)).mean())
+        assert abs(frac - 0.5) < 5 * 0.5 / np.sqrt(words.size), (bit, frac)

@@ -335,22 +335,125 @@ def run_baseline(a, world, rank, local):
 
 
 # ------------------------------------------------------------------------------- reference
+REFERENCE_MULTI_GPU_REASON = (
+    "the reference's zeroth-order path is single-GPU only: large_models/run.py:32 pins "
+    "CUDA_VISIBLE_DEVICES=0 and zo_step / zo_update (large_models/trainer.py:1570-1617) contain no "
+    "collective, so there is no N-GPU reference job to time")
+
+
 def run_reference(a):
-    """The unmodified reference from baseline/_ref, or the reason it cannot run here."""
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(ref) or not os.listdir(ref):
-        why = ("reference is not installable: it ships no setup.py/pyproject (pip install of the "
-               "source tree fails) and its trainer imports symbols removed from transformers 5.x")
-    else:
-        sys.path.insert(0, ref)
-        try:
-            import trainer as _ref_trainer  # noqa: F401  (the reference's flat module layout)
-        except Exception as e:  # pragma: no cover - depends on the box
-            why = f"reference import fails under the installed libraries: {type(e).__name__}: {e}"[:300]
-    if why is None:
-        why = "reference imported but its ZO path pins CUDA_VISIBLE_DEVICES=0 and needs HF hub data"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """Time the unmodified reference (``baseline/_ref``) on the same metric and configuration.
+
+    The reference's own ``OurTrainer.zo_step`` / ``zo_update`` and ``dizo_trainer.dizo_zo_iters`` run on a
+    random-init Hugging Face OPT model of the named shape in bf16 (its ``--load_bfloat16`` dtype), fed
+    the synthetic batches in the layout of its nesting collator: one sequence per candidate, two
+    candidates per prompt, as its classification path does (large_models/run.py:415-419).  Nothing of
+    this repository's package is imported on this path."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+
+    def unavailable(why):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if world > 1 or a.gpus > 1:
+        return unavailable(REFERENCE_MULTI_GPU_REASON)
+    if a.parallelism != "dp" or a.mode != "full":
+        return unavailable("the reference arm times full-parameter ZO on one GPU only")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device in this process; the reference's DiZO module allocates on 'cuda' "
+                           "(large_models/trainer.py:389)")
+    from baseline import ref_harness as H
+    try:
+        ref, shimmed = H.import_reference()
+    except H.ReferenceUnavailable as e:
+        return unavailable(str(e))
+    if a.model not in H.OPT_SHAPES:
+        return unavailable(f"no shape table entry for {a.model}")
+    import numpy as np
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    enhanced = None if a.enhanced == "none" else a.enhanced
+    if enhanced == "fo":
+        return unavailable("the reference arm times the zeroth-order gamma search (the headline configuration)")
+    V, cands = 50272, a.baseline_candidates
+    model = H.build_hf_opt(a.model, dev, torch.bfloat16)
+    lr0, max_steps = 1e-6, 20000
+    n_res = a.warmup + a.steps
+    resident = [{k: v.to(dev) for k, v in H.reference_batch(s, a.prompts, a.seq, V, candidates=cands).items()}
+                for s in range(n_res)]
+    search_batches = [{k: v.to(dev) for k, v in H.reference_batch(5000 + s, a.prompts, a.seq, V,
+                                                                 candidates=cands).items()} for s in range(10)]
+    tr = H.make_reference_trainer(ref, model, dev, lr=lr0, max_steps=max_steps, zo_eps=1e-3,
+                                  enhanced=enhanced, search_batches=search_batches)
+    np.random.seed(0)
+    torch.cuda.synchronize()
+    for s in range(a.warmup):
+        H.reference_step(tr, resident[s])
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(a.warmup, n_res):
+        H.reference_step(tr, resident[s])
+    e1.record()
+    torch.cuda.synchronize()
+    step_ms = e0.elapsed_time(e1) / a.steps
+
+    search_ms = 0.0
+    if enhanced == "zo":
+        tr.dizo_trainer.dizo_zo_iters(tr.model, base_model=tr.base_model)      # warm, as the other arms do
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        tr.dizo_trainer.dizo_zo_iters(tr.model, base_model=tr.base_model)
+        s1.record()
+        torch.cuda.synchronize()
+        search_ms = s0.elapsed_time(s1)
+    clocks = sampler.stop()
+    ms = step_ms + search_ms / 50.0
+    tokens = a.prompts * a.seq
+
+    e2e = None
+    if not a.skip_e2e:
+        hb = [H.reference_batch(10_000 + s, a.prompts, a.seq, V, candidates=cands, pin=True)
+              for s in range(a.steps + 2)]
+        for s in range(2):
+            float(H.reference_step(tr, hb[s]))
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        last = 0.0
+        for s in range(2, 2 + a.steps):
+            # zo_forward moves the pinned host batch to the device itself (_prepare_inputs, once per
+            # forward); the loss and the projected gradient are read back on the host
+            last = float(H.reference_step(tr, hb[s]))
+        t1.record()
+        torch.cuda.synchronize()
+        e2e_ms = t0.elapsed_time(t1) / a.steps + search_ms / 50.0
+        e2e = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": 2 * H.batch_nbytes(hb[0]),
+               # bf16 loss + bf16 projected gradient, and per forward the loss wrapper's host reads of
+               # option_len (8 B) and of the num_options comparison (1 B) for every sequence
+               "d2h_bytes_per_step": 2 + 2 + 2 * 9 * a.prompts * cands,
+               "last_loss": last}
+    print(json.dumps({
+        "metric": "zo_train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded uniform ids, Bernoulli labels); random-init weights",
+        "impl": "reference",
+        "config": {"model": a.model, "global_batch": a.prompts, "seq_len": a.seq, "parallelism": "dp1",
+                   "trainable": "full", "forwards_per_step": 2, "enhanced": a.enhanced,
+                   "candidates_per_prompt": cands, "sequences_per_forward": a.prompts * cands,
+                   "zo_step_ms": step_ms, "gamma_search_ms": search_ms, "gamma_search_period": 50,
+                   "l2_policy": "per-step working set (parameters) far exceeds L2; no flush needed",
+                   "reference_entry_points": "OurTrainer.zo_step, zo_update, dizo_trainer.dizo_zo_iters",
+                   "library_names_stubbed": shimmed},
+        "gpu_launches": None, "clocks": clocks, "e2e": e2e}))
     return 0
 
 

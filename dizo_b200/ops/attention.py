@@ -16,24 +16,6 @@ import torch
 from . import _lib
 
 
-def set_variant(v: int) -> None:
-    """0: one thread per query row (eight softmax warps); 1: two threads per row (sixteen softmax
-    warps, ``csrc/attn16_sm100.cu``).  ``DIZO_ATTN_VARIANT`` sets the default."""
-    _lib.lib().dz_attn_set_variant(int(v))
-
-
-_variant_from_env = False
-
-
-def _apply_env_variant() -> None:
-    global _variant_from_env
-    if not _variant_from_env:
-        _variant_from_env = True
-        v = os.environ.get("DIZO_ATTN_VARIANT")
-        if v is not None:
-            set_variant(int(v))
-
-
 def attention_reference(qkv: torch.Tensor, n_heads: int, pad_left: torch.Tensor | None = None,
                         prefix_k: torch.Tensor | None = None, prefix_v: torch.Tensor | None = None,
                         scale: float | None = None) -> torch.Tensor:
@@ -80,7 +62,6 @@ def attention(qkv: torch.Tensor, n_heads: int, pad_left: torch.Tensor | None = N
     if not qkv.is_cuda:
         assert lse is None, "the CPU statement differentiates through autograd instead"
         return attention_reference(qkv, n_heads, pad_left, prefix_k, prefix_v, scale)
-    _apply_env_variant()
     assert qkv.dtype == torch.bfloat16 and qkv.dim() == 3 and qkv.stride(-1) == 1
     B, L, d3 = qkv.shape
     d = d3 // 3

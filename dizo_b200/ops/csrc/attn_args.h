@@ -1,4 +1,4 @@
-// Launch description shared by the attention forward kernels (attn_sm100.cu, attn16_sm100.cu).
+// Launch description shared by the attention forward kernels (attn_sm100.cu).
 #pragma once
 #include <cuda_bf16.h>
 #include <cstdint>

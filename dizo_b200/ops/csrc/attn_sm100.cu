@@ -371,18 +371,9 @@ static int launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const CU
   return cuda_rc(cudaGetLastError());
 }
 
-// sixteen-softmax-warp variant (attn16_sm100.cu)
-int launch_attn16_hd(int hdp, const CUtensorMap& tmQ, const CUtensorMap& tmKV, const CUtensorMap& tmPK,
-                     const CUtensorMap& tmPV, const AttnArgs& a, cudaStream_t stream);
-static int g_attn_variant = 0;
-
 }  // namespace dz
 
 using namespace dz;
-
-// 0: one thread per query row (8 softmax warps); 1: two threads per row (16 softmax warps)
-extern "C" void dz_attn_set_variant(int v) { g_attn_variant = v; }
-extern "C" int dz_attn_get_variant() { return g_attn_variant; }
 
 // qkv: [B*L, ld_qkv] bf16 with Q at columns [q_col0, q_col0 + H*hd), K at k_col0, V at v_col0.
 // out: [B*L, ld_out] bf16.  prefix_k / prefix_v: [n_prefix, ld_prefix] bf16 or null.
@@ -422,7 +413,6 @@ extern "C" int dz_attn_fwd_lse(const void* qkv, long long ld_qkv, int q_col0, in
   a.out = (__nv_bfloat16*)out; a.pad_left = pad_left; a.lse = lse;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.q_col0 = q_col0; a.k_col0 = k_col0; a.v_col0 = v_col0; a.err = err;
-  if (g_attn_variant == 1) return launch_attn16_hd(hdp, tmQ, tmKV, tmPK, tmPV, a, stream);
   if (hdp == 64) return launch_attn<64>(tmQ, tmKV, tmPK, tmPV, a, stream);
   return launch_attn<128>(tmQ, tmKV, tmPK, tmPV, a, stream);
 }

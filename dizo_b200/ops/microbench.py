@@ -89,13 +89,9 @@ def main():
     ap.add_argument("--seconds", type=float, default=0.0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="both", choices=["both", "ours", "lib"])
-    ap.add_argument("--attn-variant", type=int, default=None, help="attention forward kernel: 0 or 1")
     a = ap.parse_args()
     peaks = _peaks()
     dev = "cuda"
-    if a.attn_variant is not None:
-        from .attention import set_variant
-        set_variant(a.attn_variant)
     g = torch.Generator(device=dev).manual_seed(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.seconds == 0 else None
     out = {"kernel": a.kernel, "mode": "sustained" if a.seconds else "burst"}

@@ -23,3 +23,11 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _run_in_scratch_directory(tmp_path, monkeypatch):
+    """The trainer writes its ``loss_acc/`` curves and result files relative to the working directory,
+    as the reference does (large_models/trainer.py:1331-1345); run every test from a scratch directory
+    so that a test run leaves the source tree clean."""
+    monkeypatch.chdir(tmp_path)

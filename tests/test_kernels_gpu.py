@@ -58,45 +58,6 @@ def test_attention_left_pad_and_prefix(hd):
         assert torch.isfinite(out.float()).all()
 
 
-@pytest.fixture
-def sixteen_warp_attention():
-    from dizo_b200.ops.attention import set_variant
-    set_variant(1)
-    yield
-    set_variant(0)
-
-
-@pytest.mark.parametrize("B,L,H,hd", [(2, 256, 4, 64), (1, 128, 2, 128), (2, 200, 3, 80), (1, 64, 2, 64),
-                                      (3, 384, 2, 128), (1, 1000, 2, 80), (1, 520, 1, 128)])
-def test_attention_sixteen_warp_variant(sixteen_warp_attention, B, L, H, hd):
-    g = torch.Generator(device=DEV).manual_seed(B * 1000 + L + hd)
-    d = H * hd
-    qkv = (torch.randn(B, L, 3 * d, device=DEV, generator=g) * 2).bfloat16()
-    pad = torch.tensor([0, L // 3, L - 5][:B], dtype=torch.int32, device=DEV)
-    pk = torch.randn(5, d, device=DEV, generator=g).bfloat16()
-    pv = torch.randn(5, d, device=DEV, generator=g).bfloat16()
-    lse = torch.empty(B, H, L, dtype=torch.float32, device=DEV)
-    out = attention(qkv, H, lse=lse)
-    _sync_ok()
-    ref = attention_reference(qkv.float(), H)
-    assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
-    q, k, _ = qkv.float().split(d, dim=-1)
-    s = torch.einsum("bhqd,bhkd->bhqk", q.view(B, L, H, hd).transpose(1, 2), k.view(B, L, H, hd).transpose(1, 2))
-    idx = torch.arange(L, device=DEV)
-    s = (s * hd ** -0.5).masked_fill(~(idx[None, :] <= idx[:, None]), float("-inf"))
-    assert (lse - torch.logsumexp(s, dim=-1) * 1.4426950408889634).abs().max().item() < 3e-2
-    out2 = attention(qkv, H, pad_left=pad, prefix_k=pk, prefix_v=pv)
-    _sync_ok()
-    ref2 = attention_reference(qkv.float(), H, pad_left=pad, prefix_k=pk.float(), prefix_v=pv.float())
-    for b in range(B):
-        p0 = int(pad[b])
-        assert (out2[b, p0:].float() - ref2[b, p0:]).abs().max().item() < 6e-2, b
-    assert torch.isfinite(out2.float()).all()
-    again = attention(qkv, H, pad_left=pad, prefix_k=pk, prefix_v=pv)
-    _sync_ok()
-    assert torch.equal(out2, again)
-
-
 def test_attention_large_scores_rescale():
     # big logits force the lazily-raised running maximum to be corrected
     B, L, H, hd = 1, 512, 2, 64

@@ -133,7 +133,7 @@ class OurArguments:
     zo_log_steps: int = 50                  # (:1321)
     zo_eval_steps: int = 100                # in-loop dev evaluation period (:1327)
     zo_mode: str = "inflight"               # inflight (theta never rewritten for a forward) | inplace
-    zo_stochastic_rounding: bool = False    # unbiased bf16 update
+    zo_stochastic_rounding: Optional[bool] = None   # unbiased bf16 update; default: on for bf16 parameters
     dp: int = 0                             # data-parallel ranks (0 = WORLD_SIZE)
     tp: int = 1                             # tensor-parallel ranks (1, or the number of ranks)
     tp_max_tokens: int = 32768              # largest batch x padded length a tensor-parallel forward takes

@@ -30,7 +30,7 @@ import torch
 import torch.distributed as dist
 
 from .models.opt import Batch, OPTModel, Transform
-from .ops.zo import GammaState, scalar_diff
+from .ops.zo import GammaState, fd_eps, scalar_diff, sr_seed_for
 
 logger = logging.getLogger(__name__)
 
@@ -41,13 +41,21 @@ def _dist_on(group=None) -> bool:
 
 class ZOEngine:
     def __init__(self, model: OPTModel, eps: float = 1e-3, mode: str = "inflight",
-                 dp_group=None, stochastic_rounding: bool = False):
+                 dp_group=None, stochastic_rounding: bool | None = None):
+        """``stochastic_rounding=None`` (default) switches it on for bf16 parameters: at the reference's
+        hyper-parameters (lr 1e-6..1e-7, eps 1e-3) an update lr*g*z is about 5e-7, far below half a bf16
+        ulp of a typical weight (3e-5 at |w| = 0.01), so round-to-nearest would drop almost every update
+        (the reference's fp16 has 8x finer steps).  Stochastic rounding keeps the update unbiased."""
         assert mode in ("inflight", "inplace")
         self.model = model
         self.eps = eps
+        # bf16 arenas perturb with bf16(eps); the finite difference divides by what was applied
+        self.eps_fd = fd_eps(eps, model.arena.dtype)
         self.mode = mode
         self.dp_group = dp_group          # None: the default group; False: no data parallelism
-        self.stochastic_rounding = stochastic_rounding
+        if stochastic_rounding is None:
+            stochastic_rounding = model.arena.dtype == torch.bfloat16
+        self.stochastic_rounding = bool(stochastic_rounding)
         dev = model.device
         f = dict(dtype=torch.float32, device=dev)
         self.loss1 = torch.zeros(1, **f)
@@ -73,7 +81,7 @@ class ZOEngine:
     def update(self, seed: int, lr: float, sq_out: torch.Tensor | None = None) -> None:
         """theta -= lr * g * z(seed) (``zo_update``); optionally also emit the DiZO norms of
         the updated tensors from the same pass."""
-        sr = (seed * 0x9E3779B97F4A7C15 + 1) & (2 ** 64 - 1) if self.stochastic_rounding else None
+        sr = sr_seed_for(seed) if self.stochastic_rounding else None
         self.model.arena.sweep(seed1=seed, c1=-lr, c1_dev=self.projected_grad, sq_out=sq_out,
                                stochastic_round_seed=sr)
 
@@ -93,7 +101,7 @@ class ZOEngine:
             self.perturb(seed, 1.0)
         self.loss1.copy_(l1.reshape(1))
         self.loss2.copy_(l2.reshape(1))
-        scalar_diff(self.loss1, self.loss2, 1.0 / (2.0 * eps), self.projected_grad)
+        scalar_diff(self.loss1, self.loss2, 1.0 / (2.0 * self.eps_fd), self.projected_grad)
         self.reduce_scalar(self.projected_grad)
         self.update(seed, lr, sq_out)
         return self.loss1
@@ -114,10 +122,11 @@ class GraphedZOStep:
     lives in device memory and is refreshed before each replay: the batch (copied into the captured
     input tensors), the perturbation seed (the sweeps read it through ``seed1_dev``) and the
     learning rate.  One instance serves one batch signature; single-process (the data-parallel
-    all-reduce is not captured), ``inflight`` mode, round-to-nearest updates."""
+    all-reduce is not captured), ``inflight`` mode.  With stochastic rounding the rounding stream's seed
+    is derived from the step's seed on the device."""
 
     def __init__(self, engine: ZOEngine, example: Batch, warmup: int = 2):
-        assert engine.mode == "inflight" and not engine.stochastic_rounding
+        assert engine.mode == "inflight"
         assert engine.dp_group is False or not _dist_on(engine.dp_group), "single-process only"
         dev = engine.model.device
         assert dev.type == "cuda"
@@ -147,9 +156,10 @@ class GraphedZOStep:
         l2 = e.forward(self.batch, Transform(coef=-eps, seed_dev=self.seed))
         e.loss1.copy_(l1.reshape(1))
         e.loss2.copy_(l2.reshape(1))
-        scalar_diff(e.loss1, e.loss2, 1.0 / (2.0 * eps), e.projected_grad)
+        scalar_diff(e.loss1, e.loss2, 1.0 / (2.0 * e.eps_fd), e.projected_grad)
         torch.mul(e.projected_grad, self.lr, out=self._lrg)
-        e.model.arena.sweep(seed1_dev=self.seed, c1=-1.0, c1_dev=self._lrg)
+        e.model.arena.sweep(seed1_dev=self.seed, c1=-1.0, c1_dev=self._lrg,
+                            stochastic_round_seed=1 if e.stochastic_rounding else None)
         return e.loss1
 
     def __call__(self, batch: Batch, lr: float, seed: int) -> torch.Tensor:
@@ -270,9 +280,7 @@ class DiZOProjector:
                 alpha = self.fo_gamma / (gs.ts.detach() + 1e-8)
                 loss = fo_loss(batch, alpha) + self.l1 * self.fo_gamma.abs().sum()
                 loss.backward()
-            if _dist_on(self.dp_group):
-                dist.all_reduce(self.fo_gamma.grad, group=self.dp_group)
-                self.fo_gamma.grad.div_(dist.get_world_size(self.dp_group))
+            self._reduce(self.fo_gamma.grad)
             self.fo_opt.step()
         with torch.no_grad():
             gs.gamma.copy_(self.fo_gamma.detach())

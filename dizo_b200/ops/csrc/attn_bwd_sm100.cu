@@ -349,12 +349,8 @@ static int launch_attn_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, co
                            cudaStream_t stream) {
   using S = AttnBwdSmem<HDP>;
   auto kern = attn_bwd_kernel<HDP, DQ>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, kern, S::TOTAL)) return rc_cfg;
   dim3 grid((a.L + AB_T - 1) / AB_T, a.H, a.B);
   kern<<<grid, AB_THREADS, S::TOTAL, stream>>>(tmQKV, tmDO, a);
   return cuda_rc(cudaGetLastError());

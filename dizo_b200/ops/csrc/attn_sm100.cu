@@ -359,12 +359,8 @@ static int launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const CU
                        const CUtensorMap& tmPV, const AttnArgs& a, cudaStream_t stream) {
   using S = AttnSmem<HDP>;
   auto kern = attn_fwd_kernel<HDP>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, kern, S::TOTAL)) return rc_cfg;
   int pairs = (a.L + 2 * A_BQ - 1) / (2 * A_BQ);
   dim3 grid(pairs, a.H, a.B);
   kern<<<grid, A_THREADS, S::TOTAL, stream>>>(tmQ, tmKV, tmPK, tmPV, a);

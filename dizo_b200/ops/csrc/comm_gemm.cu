@@ -100,7 +100,7 @@ struct CommGemmArgs {
   float push_coef;
   int push_tensor_id[3];
   long long push_elem_base[3];   // index of push_src[s][0,0] inside the full tensor
-  const __half* gauss_table;
+  const uint16_t* gauss_table;
   // ---- bookkeeping
   int rank, world;
   unsigned int* counters;        // local [2 + CG_MAXC]: pushers done, gemm CTAs done, pushers done per
@@ -179,12 +179,12 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
   __shared__ int s_go;
   __shared__ int s_first_idle;     // first chunk counter this launch leaves untouched
   // stage the inverse-CDF table when the pushed rows are perturbed
-  const __half* tab = nullptr;
+  const uint16_t* tab = nullptr;
   if (p.push_perturb) {
     const uint4* src = reinterpret_cast<const uint4*>(p.gauss_table);
     uint4* dst = reinterpret_cast<uint4*>(smem_raw);
     for (int i = threadIdx.x; i < GAUSS_TABLE_SIZE * 2 / 16; i += CG_THREADS) dst[i] = __ldg(src + i);
-    tab = reinterpret_cast<const __half*>(smem_raw);
+    tab = reinterpret_cast<const uint16_t*>(smem_raw);
   }
   if (threadIdx.x == 0) { s_go = 1; s_first_idle = 0; }
   __syncthreads();
@@ -273,6 +273,7 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
         }
       }
       if (p.push_perturb) {
+        const uint32_t push_coef_pair = bf16x2_splat(p.push_coef);
 #pragma unroll
         for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
           if (!live[u]) continue;
@@ -280,15 +281,10 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
           const int seg = (int)(vv / seg_total);
           const long long v = vv - seg * seg_total;
           const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
-          float x[8] = {bf16_lo(raw[u].x), bf16_hi(raw[u].x), bf16_lo(raw[u].y), bf16_hi(raw[u].y),
-                        bf16_lo(raw[u].z), bf16_hi(raw[u].z), bf16_lo(raw[u].w), bf16_hi(raw[u].w)};
-          float z[8];
           const long long e = p.push_elem_base[seg] + r * p.push_cols + c;
-          gauss8(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3), 0u, z);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = fmaf(p.push_coef, z[j], x[j]);
-          raw[u].x = pack_bf16x2(x[0], x[1]); raw[u].y = pack_bf16x2(x[2], x[3]);
-          raw[u].z = pack_bf16x2(x[4], x[5]); raw[u].w = pack_bf16x2(x[6], x[7]);
+          // the same packed bf16 fma as the staging sweep, so a pushed shard equals a swept one bit for bit
+          raw[u] = perturb8_packed(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3),
+                                   push_coef_pair, raw[u]);
         }
       }
       // nearest consumer first: rank d reads the rows of d+1, d+2, ... in that order
@@ -719,19 +715,12 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.push_flag_ptrs = (uint32_t* const*)d->push_flag_ptrs; a.push_epoch = d->push_epoch;
   a.push_wait_acks = (const uint32_t*)d->push_wait_acks; a.push_wait_epoch = d->push_wait_epoch;
   a.push_perturb = d->push_perturb; a.push_seed = d->push_seed; a.push_coef = d->push_coef;
-  a.gauss_table = (const __half*)d->gauss_table;
+  a.gauss_table = (const uint16_t*)d->gauss_table;
   a.rank = d->rank; a.world = d->world; a.counters = (unsigned int*)d->counters;
   a.push_target = d->push_target; a.gemm_target = d->gemm_target; a.err = err;
   if (!a.counters) return DZ_ERR_ARG;
-  static bool configured = false;
-  if (!configured) {
-    // the ring depth is the same with and without the reduce-scatter epilogue: one instantiation
-    static_assert(CG_STAGES_PUSH == CG_STAGES_PLAIN, "one kernel instantiation expected");
-    cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<CG_STAGES_PUSH>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, CG_SMEM_PUSH);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, comm_gemm_kernel<CG_STAGES_PUSH>, CG_SMEM_PUSH)) return rc_cfg;
   int gemm_ctas = 0;
   if (has_gemm) {
     int tiles = a.num_m * a.num_n;

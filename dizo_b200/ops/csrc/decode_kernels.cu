@@ -292,13 +292,8 @@ extern "C" int dz_decode_attn(const void* q, long long ldq, const void* kc, cons
     return DZ_ERR_ARG;
   size_t smem = sizeof(float) * (size_t)(n_prefix + kv_len);
   if (smem > 160 * 1024) return DZ_ERR_TOO_LARGE;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         160 * 1024);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, decode_attn_kernel, 160 * 1024)) return rc_cfg;
   dim3 grid(H, B);
   decode_attn_kernel<<<grid, DA_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, ld_seq, ld_row,

@@ -420,13 +420,8 @@ extern "C" int dz_gemm2_bf16_tn(const void* A, long long lda, const void* W, lon
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tmB, W, N, K, ldw, G2_BN / 2, G2_BK, true);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_tn_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, gemm2_bf16_tn_kernel, G2_SMEM)) return rc_cfg;
   int tiles = a.num_m * a.num_n;
   static int max_clusters = 0;
   if (!max_clusters) {

@@ -369,12 +369,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs&
                        cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
   auto kern = gemm_bf16_tn_kernel<BN, STAGES, EPI, B_MN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, kern, S::TOTAL)) return rc_cfg;
   a.num_m = (a.M + G_BM - 1) / G_BM;
   a.num_n = (a.N + BN - 1) / BN;
   a.group_m = a.num_m < 16 ? a.num_m : 16;

@@ -75,15 +75,39 @@ inline int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t d0, ui
   return r == CUDA_SUCCESS ? DZ_OK : DZ_ERR_TMAP;
 }
 
+// Launch attributes and device properties are per device, and one process may drive several GPUs:
+// both are cached per device index, not per process.
+constexpr int DZ_MAX_DEVICES = 64;
+
 inline int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+  static int n[DZ_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool cached = dev >= 0 && dev < DZ_MAX_DEVICES;
+  if (cached && n[dev]) return n[dev];
+  int v = 0;
+  cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+  if (v <= 0) v = 148;
+  if (cached) n[dev] = v;
+  return v;
+}
+
+struct PerDeviceFlag {
+  bool set[DZ_MAX_DEVICES] = {};
+};
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device).
+template <class Kern>
+inline int ensure_dyn_smem(PerDeviceFlag& f, Kern kern, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  const bool cached = dev >= 0 && dev < DZ_MAX_DEVICES;
+  if (cached && f.set[dev]) return DZ_OK;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (cached) f.set[dev] = true;
+  return DZ_OK;
 }
 
 }  // namespace dz

@@ -13,6 +13,9 @@
 //     v   = anchor + alpha[slot] * (v - anchor)     if BLEND and the tensor has a slot
 //     v  += c1 * z(seed1) + c2 * z(seed2)           z regenerated from Philox in registers
 //     dst = bf16(v)                                 round-to-nearest or stochastic
+// (fp32 arithmetic), except for the plain perturbation dst = theta + c1 z(seed1) - the sweep
+// every forward pass runs - which stays in packed bf16: dst = fma.rn.bf16x2(bf16(c1), z, theta),
+// exact product and sum with one rounding, and none of the unpack / convert / pack instructions.
 //     chunk_sq[chunk] = sum (v - anchor)^2          if NORM and the tensor has a slot
 // dst may be the arena itself (in-place perturb / restore / update / projection) or a
 // staging buffer (perturbed or projected weights for one forward, theta untouched).
@@ -31,7 +34,7 @@ namespace dz {
 constexpr int ZO_CHUNK = 256;    // elements; tensor starts are aligned to this (one warp pass)
 constexpr int ZO_THREADS = 768;  // one persistent CTA (24 warps) per SM
 constexpr int ZO_UNROLL = 4;     // 16-byte loads in flight per lane
-constexpr int ZO_SMEM = 65536 * 2; // the fp16 inverse-CDF table
+constexpr int ZO_SMEM = 65536 * 2; // the bf16 inverse-CDF table
 
 struct ZoTensor {
   long long offset;         // first element in the arena
@@ -72,7 +75,7 @@ struct ZoSweepArgs {
   const float* alpha;           // [slots] blend ratios
   float* chunk_sq;              // norm partials: [sq_base + chunk inside the piece]
   unsigned long long sr_seed;   // stochastic rounding stream
-  const __half* gauss_table;    // [65536] fp16 inverse normal CDF (global memory)
+  const uint16_t* gauss_table;  // [65536] bf16 bits of the inverse normal CDF (global memory)
 };
 
 __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, long long pos) {
@@ -88,9 +91,31 @@ __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, 
 template <bool Z2, bool BLEND, bool NORM, bool SR>
 __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t, float alpha,
                                          long long cpos, int lane, const uint4 raw,
-                                         const __half* tab, float c1, float c2) {
+                                         const uint16_t* tab, float c1, float c2, uint32_t c1_pair) {
   const long long e0 = cpos - t.offset + lane * 8;  // element inside this piece
   float sq = 0.f;
+  constexpr bool PACKED = !Z2 && !BLEND && !NORM && !SR;
+  if (PACKED) {
+    if (e0 < t.numel) {
+      uint4 o = raw;
+      if (c1 != 0.f) o = perturb8_packed(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
+      if (e0 + 8 > t.numel) {
+        // ragged tail of a tensor: keep the padding elements as they were
+        uint32_t ov[4] = {o.x, o.y, o.z, o.w};
+        const uint32_t rawv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (e0 + j >= t.numel) {
+            const uint32_t m = (j & 1) ? 0xffff0000u : 0xffffu;
+            ov[j >> 1] = (ov[j >> 1] & ~m) | (rawv[j >> 1] & m);
+          }
+        }
+        o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+      }
+      *reinterpret_cast<uint4*>(a.dst + (cpos + lane * 8 - a.dst_shift)) = o;
+    }
+    return;
+  }
   if (e0 < t.numel) {
     const long long pos = cpos + lane * 8;
     float v[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
@@ -174,9 +199,12 @@ template <bool Z2, bool BLEND, bool NORM, bool SR>
 __global__ void __launch_bounds__(ZO_THREADS, 1)
 zo_sweep_kernel(const ZoSweepArgs a_in) {
   ZoSweepArgs a = a_in;
-  if (a.seed1_dev) a.seed1 = *a.seed1_dev;     // a captured launch takes the step's seed from memory
+  if (a.seed1_dev) {
+    a.seed1 = *a.seed1_dev;     // a captured launch takes the step's seed from memory,
+    if (SR) a.sr_seed = a.seed1 * 0x9E3779B97F4A7C15ull + 1ull;   // and its rounding stream follows the seed
+  }
   extern __shared__ __align__(16) uint8_t zo_smem[];
-  __half* tab = reinterpret_cast<__half*>(zo_smem);
+  uint16_t* tab = reinterpret_cast<uint16_t*>(zo_smem);
   {
     const uint4* src = reinterpret_cast<const uint4*>(a.gauss_table);
     uint4* dst = reinterpret_cast<uint4*>(zo_smem);
@@ -186,6 +214,7 @@ zo_sweep_kernel(const ZoSweepArgs a_in) {
   float c1 = a.c1, c2 = a.c2;
   if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
   if (Z2 && a.c2_ptr) c2 *= __ldg(a.c2_ptr);
+  const uint32_t c1_pair = bf16x2_splat(c1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int WARPS = ZO_THREADS / 32;
@@ -221,13 +250,13 @@ zo_sweep_kernel(const ZoSweepArgs a_in) {
         raw[u] = *reinterpret_cast<const uint4*>(a.src + cpos + u * ZO_CHUNK + lane * 8);
 #pragma unroll
       for (int u = 0; u < ZO_UNROLL; ++u)
-        zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos + u * ZO_CHUNK, lane, raw[u], tab, c1, c2);
+        zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos + u * ZO_CHUNK, lane, raw[u], tab, c1, c2, c1_pair);
       chunk += ZO_UNROLL;
     } else {
       uint4 raw = make_uint4(0, 0, 0, 0);
       if (cpos - t.offset + lane * 8 < t.numel)
         raw = *reinterpret_cast<const uint4*>(a.src + cpos + lane * 8);
-      zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos, lane, raw, tab, c1, c2);
+      zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos, lane, raw, tab, c1, c2, c1_pair);
       chunk += 1;
     }
   }
@@ -264,7 +293,7 @@ __global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, f
                                   float* zbuf, float* alpha, unsigned long long seed, int iter,
                                   float delta, float tau, float eps, float step_size,
                                   const float* loss1, const float* loss2, int reinit,
-                                  const __half* gauss_table) {
+                                  const uint16_t* gauss_table) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float t;
@@ -281,7 +310,7 @@ __global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, f
     if (delta == 1.0f && iter >= 0) {
       Philox4 p = philox4x32<10>(static_cast<uint32_t>(i), static_cast<uint32_t>(iter), 2u, 0u,
                                  static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-      float z0 = __half2float(gauss_table[p.x & 0xffffu]);
+      float z0 = __uint_as_float(static_cast<uint32_t>(gauss_table[p.x & 0xffffu]) << 16);
       float lim = (tau / eps) * t;
       z = fminf(fmaxf(z0, -lim), lim);
       zbuf[i] = z;
@@ -308,12 +337,8 @@ static int launch_sweep(const ZoSweepArgs& a, cudaStream_t stream) {
   long long chunks = a.chunk_end - a.chunk_begin;
   if (chunks <= 0) return DZ_OK;
   auto kern = zo_sweep_kernel<Z2, BLEND, NORM, SR>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ZO_SMEM);
-    if (e != cudaSuccess) return cuda_rc(e);
-    configured = true;
-  }
+  static PerDeviceFlag configured;
+  if (int rc_cfg = ensure_dyn_smem(configured, kern, ZO_SMEM)) return rc_cfg;
   long long blocks = (chunks + ZO_THREADS / 32 - 1) / (ZO_THREADS / 32);
   int grid = (int)(blocks < sm_count() ? blocks : sm_count());
   kern<<<grid, ZO_THREADS, ZO_SMEM, stream>>>(a);
@@ -352,7 +377,7 @@ extern "C" int dz_zo_sweep_seeded(const void* src, void* dst, long long dst_shif
   a.t_begin = t_begin; a.t_end = t_end; a.chunk_begin = chunk_begin; a.chunk_end = chunk_end;
   a.seed1 = seed1; a.seed1_dev = seed1_dev; a.seed2 = seed2; a.c1 = c1; a.c2 = c2; a.c1_ptr = c1_ptr; a.c2_ptr = c2_ptr;
   a.alpha = alpha; a.chunk_sq = chunk_sq; a.sr_seed = sr_seed;
-  a.gauss_table = (const __half*)gauss_table;
+  a.gauss_table = (const uint16_t*)gauss_table;
   int key = (z2 ? 1 : 0) | (blend ? 2 : 0) | (norm ? 4 : 0) | (sr ? 8 : 0);
   switch (key) {
 #define DZ_CASE(K, A, B, C, D) case K: return launch_sweep<A, B, C, D>(a, stream);
@@ -396,7 +421,7 @@ extern "C" int dz_gamma_step(int n, int mode, const float* sq, float* ts, float*
   if (n <= 0 || !ts || !gamma || !zbuf || !alpha || !gauss_table) return DZ_ERR_ARG;
   gamma_step_kernel<<<(n + 127) / 128, 128, 0, stream>>>(n, mode, sq, ts, gamma, zbuf, alpha, seed,
                                                          iter, delta, tau, eps, step_size, loss1,
-                                                         loss2, reinit, (const __half*)gauss_table);
+                                                         loss2, reinit, (const uint16_t*)gauss_table);
   return cuda_rc(cudaGetLastError());
 }
 
@@ -409,7 +434,7 @@ extern "C" int dz_scalar_diff(const float* a, const float* b, float scale, float
 
 // z itself (fp32), for tests and for the CPU oracle that consumes the framework's stream.
 __global__ void zo_fill_z_kernel(float* out, long long numel, long long elem_base,
-                                 unsigned long long seed, int tensor_id, const __half* tab) {
+                                 unsigned long long seed, int tensor_id, const uint16_t* tab) {
   long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long e0 = g * 8;
   if (e0 >= numel) return;
@@ -423,6 +448,6 @@ extern "C" int dz_zo_fill_z(float* out, long long numel, long long elem_base,
   if (!out || !gauss_table || numel <= 0 || (elem_base & 7)) return DZ_ERR_ARG;
   long long groups = (numel + 7) / 8;
   zo_fill_z_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(out, numel, elem_base, seed,
-                                                                        tensor_id, (const __half*)gauss_table);
+                                                                        tensor_id, (const uint16_t*)gauss_table);
   return cuda_rc(cudaGetLastError());
 }

@@ -5,7 +5,7 @@ element index ``e`` inside the *full* tensor:
 
     words = Philox4x32-7(counter=(e >> 3, tensor_id, stream, 0), key=(seed_lo, seed_hi))
     w     = words[(e & 7) >> 1];  u = w & 0xffff for even e, w >> 16 for odd e
-    z     = T[u],   T[i] = float16(Phi^-1((i + 0.5) / 65536))
+    z     = T[u],   T[i] = bfloat16(Phi^-1((i + 0.5) / 65536))
 
 ``T`` (:func:`gauss_table`) is the same 65536-entry inverse-normal-CDF table the CUDA kernels
 stage into shared memory, so the host stream equals the device stream bit for bit.  The
@@ -50,15 +50,50 @@ def philox4x32(c0, c1, c2, c3, k0, k1, rounds: int = 10):
 
 
 _TABLE = None
+_TABLE_BITS = None
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bit patterns (uint16), round to nearest even."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    with np.errstate(over="ignore"):
+        r = (b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)
+    return r.astype(np.uint16)
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def f64_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float64 -> bf16 with ONE rounding (nearest even).  NumPy / PyTorch convert through float32,
+    which rounds twice; here the float32 step rounds to odd, which makes the second rounding exact.
+    This is the host statement of the device's ``fma.rn.bf16x2`` result rounding."""
+    x = np.ascontiguousarray(x, dtype=np.float64)
+    f = x.astype(np.float32)
+    inexact = f.astype(np.float64) != x
+    too_big = np.abs(f.astype(np.float64)) > np.abs(x)
+    f = np.where(inexact & too_big, np.nextafter(f, np.float32(0)), f).astype(np.float32)
+    b = f.view(np.uint32) | inexact.astype(np.uint32)         # sticky bit
+    return f32_to_bf16_bits(b.view(np.float32))
+
+
+def gauss_table_bits() -> np.ndarray:
+    """uint16[65536]: bf16 bit patterns of Phi^-1((i + 0.5) / 65536) (computed in float64); what the
+    kernels stage into shared memory."""
+    global _TABLE_BITS
+    if _TABLE_BITS is None:
+        from scipy.special import ndtri
+        u = (np.arange(65536, dtype=np.float64) + 0.5) / 65536.0
+        _TABLE_BITS = f64_to_bf16_bits(ndtri(u))
+    return _TABLE_BITS
 
 
 def gauss_table() -> np.ndarray:
-    """float16[65536]: T[i] = Phi^-1((i + 0.5) / 65536), computed in float64."""
+    """float32[65536] holding the bf16 table values."""
     global _TABLE
     if _TABLE is None:
-        from scipy.special import ndtri
-        u = (np.arange(65536, dtype=np.float64) + 0.5) / 65536.0
-        _TABLE = ndtri(u).astype(np.float16)
+        _TABLE = bf16_bits_to_f32(gauss_table_bits())
     return _TABLE
 
 
@@ -67,9 +102,17 @@ def gauss_words(words: np.ndarray) -> np.ndarray:
     w = words.astype(np.uint32)
     tab = gauss_table()
     out = np.empty(w.shape[:-1] + (8,), dtype=np.float32)
-    out[..., 0::2] = tab[w & np.uint32(0xFFFF)].astype(np.float32)
-    out[..., 1::2] = tab[w >> np.uint32(16)].astype(np.float32)
+    out[..., 0::2] = tab[w & np.uint32(0xFFFF)]
+    out[..., 1::2] = tab[w >> np.uint32(16)]
     return out
+
+
+def perturb_bf16(theta_bits: np.ndarray, coef: float, z: np.ndarray) -> np.ndarray:
+    """bf16 bits of ``theta + bf16(coef) * z`` rounded once: the packed perturbation of the sweep
+    kernel (``perturb8_packed`` in csrc/philox.cuh).  ``z`` holds bf16-representable values."""
+    c = bf16_bits_to_f32(f32_to_bf16_bits(np.float32(coef).reshape(1)))[0].astype(np.float64)
+    v = bf16_bits_to_f32(theta_bits).astype(np.float64)
+    return f64_to_bf16_bits(v + c * z.astype(np.float64))     # 8+8-bit product and the sum are exact in float64
 
 
 # Rounds of the perturbation stream z.  Philox4x32 is specified with 10 rounds by default and is

@@ -50,14 +50,36 @@ _tables: dict = {}
 
 
 def gauss_table_dev(device) -> torch.Tensor:
-    """The fp16 inverse-CDF table on ``device`` (uploaded once per device)."""
+    """The bf16 inverse-CDF table (as int16 bit patterns) on ``device`` (uploaded once per device)."""
     dev = torch.device(device)
     key = (dev.type, dev.index)
     t = _tables.get(key)
     if t is None:
-        t = torch.from_numpy(philox.gauss_table().copy()).to(dev)
+        t = torch.from_numpy(philox.gauss_table_bits().view(np.int16).copy()).to(dev)
         _tables[key] = t
     return t
+
+
+def sr_seed_for(seed: int) -> int:
+    """Seed of the stochastic-rounding stream that goes with perturbation seed ``seed`` (the sweep kernel
+    derives the same value on the device when it reads the seed from memory)."""
+    return (seed * 0x9E3779B97F4A7C15 + 1) & (2 ** 64 - 1)
+
+
+def fd_eps(eps: float, dtype) -> float:
+    """The perturbation scale a forward actually sees: bf16 arenas perturb with the coefficient rounded
+    to bf16 (packed ``fma.rn.bf16x2``), so the finite difference divides by that value."""
+    if dtype == torch.bfloat16:
+        return float(torch.tensor(eps, dtype=torch.float32).to(torch.bfloat16).float())
+    return float(eps)
+
+
+def perturb_reference(theta: torch.Tensor, coef: float, z: torch.Tensor) -> torch.Tensor:
+    """Host statement of the packed perturbation: bf16(theta + bf16(coef) * z), rounded once.  ``theta`` is
+    bf16, ``z`` holds the stream's (bf16-representable) values; returns bf16 on ``theta``'s device."""
+    bits = theta.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+    ob = philox.perturb_bf16(bits.reshape(-1), coef, z.detach().cpu().numpy().reshape(-1))
+    return torch.from_numpy(ob.view(np.int16).copy()).view(torch.bfloat16).view(theta.shape).to(theta.device)
 
 
 def _round_up(x: int, m: int) -> int:
@@ -197,7 +219,8 @@ class ParamArena:
         replaces ``seed1`` by a value read on the device (CUDA-graph replays).  ``alpha`` ([n_slots] fp32)
         switches on the blend ``theta_0 + alpha*(theta - theta_0)`` for slotted pieces;
         ``sq_out`` ([n_slots] fp32) receives ``||stored - theta_0||^2`` per slotted piece of
-        the range."""
+        the range.  With ``seed1_dev`` a given ``stochastic_round_seed`` only switches stochastic rounding
+        on: the stream's seed is then :func:`sr_seed_for` of the device seed."""
         t_end = len(self.pieces) if t_end is None else t_end
         if t_end <= t_begin:
             return
@@ -214,6 +237,8 @@ class ParamArena:
         if self.device.type != "cuda":
             if seed1_dev is not None:
                 seed1 = int(seed1_dev.item()) & (2 ** 64 - 1)
+                if stochastic_round_seed is not None:
+                    stochastic_round_seed = sr_seed_for(seed1)
             self._sweep_cpu(t_begin, t_end, out, shift, seed1, c1, c1_dev, seed2, c2, c2_dev,
                             use_z2, alpha, sq_out, stochastic_round_seed)
             return
@@ -258,6 +283,16 @@ class ParamArena:
                 an = self.anchor[p.anchor_offset:p.anchor_offset + p.numel].float()
             if alpha is not None and slotted:
                 v = an + float(alpha[p.slot]) * (v - an)
+            packed = (self.dtype == torch.bfloat16 and not use_z2 and alpha is None and sq_out is None
+                      and sr_seed is None)
+            if packed:
+                # the forward-pass perturbation: bf16 coefficient, exact fma, one rounding
+                if c1v != 0.0:
+                    stored = perturb_reference(src, c1v, self.z_for(p.name, seed1).reshape(-1))
+                else:
+                    stored = src
+                out[p.offset - shift:p.offset - shift + p.numel].copy_(stored)
+                continue
             if c1v != 0.0:
                 v = v + c1v * self.z_for(p.name, seed1).reshape(-1).to(v.device)
             if use_z2:

@@ -240,7 +240,7 @@ class OurTrainer:
         eng.loss1.copy_(l1.reshape(1))
         eng.loss2.copy_(l2.reshape(1))
         from .ops.zo import scalar_diff
-        scalar_diff(eng.loss1, eng.loss2, 1.0 / (2.0 * eps), eng.projected_grad)
+        scalar_diff(eng.loss1, eng.loss2, 1.0 / (2.0 * eng.eps_fd), eng.projected_grad)
         eng.reduce_scalar(eng.projected_grad)
         assert self.args.gradient_accumulation_steps == 1, "ZO does not accumulate gradients"
         return eng.loss1
@@ -281,7 +281,7 @@ class OurTrainer:
         a = self.args
         if not getattr(a, "zo_cuda_graph", False) or self.model.device.type != "cuda" or a.non_diff:
             return False
-        if self._world > 1 or self.engine.mode != "inflight" or self.engine.stochastic_rounding:
+        if self._world > 1 or self.engine.mode != "inflight":
             return False
         if type(self.model).hidden_states is not OPTModel.hidden_states:
             return False

@@ -93,3 +93,42 @@ def test_zo_training_reduces_loss_and_dizo_bounds():
     assert torch.allclose(gs.sq.sqrt(), gs.gamma, rtol=2e-2)
     torch.cuda.synchronize()
     _lib.check_device_errors()
+
+
+def test_reference_hyperparameters_need_stochastic_rounding():
+    """At the reference's learning rate and epsilon (1e-6, 1e-3) an update is far below half a bf16 ulp of
+    a weight: with round-to-nearest theta stays where it is, with stochastic rounding (the default for
+    bf16 parameters) the realised move follows the intended one and the loss on the training batch falls."""
+    from dizo_b200.ops.zo import fill_z
+    cfg = preset("opt-125m", num_hidden_layers=2)
+    fixed = synthetic_batch(0, 16, 32, cfg.vocab_size).to("cuda")
+    name = "model.decoder.layers.0.fc1.weight"
+    stats = {}
+    for label, sr in (("default", None), ("nearest", False)):
+        model = OPTModel(cfg, "cuda", torch.bfloat16).init_random_fast(0)
+        eng = ZOEngine(model, eps=1e-3, stochastic_rounding=sr)
+        assert eng.stochastic_rounding == (sr is None)
+        piece = model.arena.pieces[model.arena.index[name]]
+        w0 = model.arena.view(name).float().clone()
+        first = model.loss(fixed).item()
+        intended = torch.zeros_like(w0)
+        rng = np.random.RandomState(1)
+        for step in range(300):
+            seed = int(rng.randint(1 << 30))
+            eng.step(fixed, 1e-6, seed=seed)
+            if step < 40:
+                z = fill_z(piece.numel, seed, piece.tensor_id, "cuda", piece.elem_base).view(w0.shape)
+                intended -= 1e-6 * eng.projected_grad.item() * z
+            if step == 39:
+                moved = model.arena.view(name).float() - w0
+                stats[label] = dict(frac=(moved != 0).float().mean().item(),
+                                    corr=((moved * intended).sum() / (moved.norm() * intended.norm() + 1e-30)).item(),
+                                    bias=(moved.mean() - intended.mean()).abs().item())
+        stats[label]["drop"] = first - model.loss(fixed).item()
+    print(stats)
+    assert stats["default"]["frac"] > 0.02 and stats["default"]["corr"] > 0.05
+    assert stats["default"]["bias"] < 2e-7
+    assert stats["nearest"]["frac"] < 0.1 * stats["default"]["frac"]
+    assert stats["default"]["drop"] > 0 and stats["default"]["drop"] > stats["nearest"]["drop"]
+    torch.cuda.synchronize()
+    _lib.check_device_errors()

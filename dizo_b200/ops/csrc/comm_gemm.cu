@@ -100,7 +100,7 @@ struct CommGemmArgs {
   float push_coef;
   int push_tensor_id[3];
   long long push_elem_base[3];   // index of push_src[s][0,0] inside the full tensor
-  const uint16_t* gauss_table;
+  const uint32_t* gauss_table;
   // ---- bookkeeping
   int rank, world;
   unsigned int* counters;        // local [2 + CG_MAXC]: pushers done, gemm CTAs done, pushers done per
@@ -179,12 +179,10 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
   __shared__ int s_go;
   __shared__ int s_first_idle;     // first chunk counter this launch leaves untouched
   // stage the inverse-CDF table when the pushed rows are perturbed
-  const uint16_t* tab = nullptr;
+  const char* tab = nullptr;
   if (p.push_perturb) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.gauss_table);
-    uint4* dst = reinterpret_cast<uint4*>(smem_raw);
-    for (int i = threadIdx.x; i < GAUSS_TABLE_SIZE * 2 / 16; i += CG_THREADS) dst[i] = __ldg(src + i);
-    tab = reinterpret_cast<const uint16_t*>(smem_raw);
+    gauss_table_to_smem(smem_raw, p.gauss_table, threadIdx.x, CG_THREADS);
+    tab = reinterpret_cast<const char*>(smem_raw) + 4 * (threadIdx.x & 31);   // this lane's bank
   }
   if (threadIdx.x == 0) { s_go = 1; s_first_idle = 0; }
   __syncthreads();
@@ -283,7 +281,7 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
           const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
           const long long e = p.push_elem_base[seg] + r * p.push_cols + c;
           // the same packed bf16 fma as the staging sweep, so a pushed shard equals a swept one bit for bit
-          raw[u] = perturb8_packed(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3),
+          raw[u] = perturb8_packed<7>(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3),
                                    push_coef_pair, raw[u]);
         }
       }
@@ -715,7 +713,7 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.push_flag_ptrs = (uint32_t* const*)d->push_flag_ptrs; a.push_epoch = d->push_epoch;
   a.push_wait_acks = (const uint32_t*)d->push_wait_acks; a.push_wait_epoch = d->push_wait_epoch;
   a.push_perturb = d->push_perturb; a.push_seed = d->push_seed; a.push_coef = d->push_coef;
-  a.gauss_table = (const uint16_t*)d->gauss_table;
+  a.gauss_table = (const uint32_t*)d->gauss_table;
   a.rank = d->rank; a.world = d->world; a.counters = (unsigned int*)d->counters;
   a.push_target = d->push_target; a.gemm_target = d->gemm_target; a.err = err;
   if (!a.counters) return DZ_ERR_ARG;

@@ -34,7 +34,7 @@ namespace dz {
 constexpr int ZO_CHUNK = 256;    // elements; tensor starts are aligned to this (one warp pass)
 constexpr int ZO_THREADS = 768;  // one persistent CTA (24 warps) per SM
 constexpr int ZO_UNROLL = 4;     // 16-byte loads in flight per lane
-constexpr int ZO_SMEM = 65536 * 2; // the bf16 inverse-CDF table
+constexpr int ZO_SMEM = GAUSS_SMEM_BYTES; // the lane-replicated inverse-CDF table
 
 struct ZoTensor {
   long long offset;         // first element in the arena
@@ -75,7 +75,7 @@ struct ZoSweepArgs {
   const float* alpha;           // [slots] blend ratios
   float* chunk_sq;              // norm partials: [sq_base + chunk inside the piece]
   unsigned long long sr_seed;   // stochastic rounding stream
-  const uint16_t* gauss_table;  // [65536] bf16 bits of the inverse normal CDF (global memory)
+  const uint32_t* gauss_table;  // [1024] (a', b) pairs of the inverse normal CDF (global memory)
 };
 
 __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, long long pos) {
@@ -91,14 +91,14 @@ __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, 
 template <bool Z2, bool BLEND, bool NORM, bool SR>
 __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t, float alpha,
                                          long long cpos, int lane, const uint4 raw,
-                                         const uint16_t* tab, float c1, float c2, uint32_t c1_pair) {
+                                         const char* tab, float c1, float c2, uint32_t c1_pair) {
   const long long e0 = cpos - t.offset + lane * 8;  // element inside this piece
   float sq = 0.f;
   constexpr bool PACKED = !Z2 && !BLEND && !NORM && !SR;
   if (PACKED) {
     if (e0 < t.numel) {
       uint4 o = raw;
-      if (c1 != 0.f) o = perturb8_packed(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
+      if (c1 != 0.f) o = perturb8_packed<7>(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
       if (e0 + 8 > t.numel) {
         // ragged tail of a tensor: keep the padding elements as they were
         uint32_t ov[4] = {o.x, o.y, o.z, o.w};
@@ -134,13 +134,13 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
     const uint32_t grp = zo_group(t, e0);
     if (c1 != 0.f) {
       float z[8];
-      gauss8(tab, a.seed1, t.tensor_id, grp, 0u, z);
+      gauss8<7>(tab, a.seed1, t.tensor_id, grp, 0u, z);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = fmaf(c1, z[j], v[j]);
     }
     if (Z2) {
       float z[8];
-      gauss8(tab, a.seed2, t.tensor_id, grp, 0u, z);
+      gauss8<7>(tab, a.seed2, t.tensor_id, grp, 0u, z);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = fmaf(c2, z[j], v[j]);
     }
@@ -193,7 +193,7 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
 }
 
 // Persistent: one CTA of 32 warps per SM.  The inverse-CDF table sits in shared memory;
-// every warp owns a contiguous run of chunks and keeps ZO_UNROLL 16-byte loads per lane in
+// (replicated per lane, conflict-free); every warp owns a contiguous run of chunks and keeps ZO_UNROLL 16-byte loads per lane in
 // flight (64 KB per SM), which is what it takes to cover HBM latency at full bandwidth.
 template <bool Z2, bool BLEND, bool NORM, bool SR>
 __global__ void __launch_bounds__(ZO_THREADS, 1)
@@ -204,12 +204,8 @@ zo_sweep_kernel(const ZoSweepArgs a_in) {
     if (SR) a.sr_seed = a.seed1 * 0x9E3779B97F4A7C15ull + 1ull;   // and its rounding stream follows the seed
   }
   extern __shared__ __align__(16) uint8_t zo_smem[];
-  uint16_t* tab = reinterpret_cast<uint16_t*>(zo_smem);
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(a.gauss_table);
-    uint4* dst = reinterpret_cast<uint4*>(zo_smem);
-    for (int i = threadIdx.x; i < GAUSS_TABLE_SIZE * 2 / 16; i += ZO_THREADS) dst[i] = __ldg(src + i);
-  }
+  gauss_table_to_smem(zo_smem, a.gauss_table, threadIdx.x, ZO_THREADS);
+  const char* tab = reinterpret_cast<const char*>(zo_smem) + 4 * (threadIdx.x & 31);   // this lane's bank
   __syncthreads();
   float c1 = a.c1, c2 = a.c2;
   if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
@@ -293,7 +289,7 @@ __global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, f
                                   float* zbuf, float* alpha, unsigned long long seed, int iter,
                                   float delta, float tau, float eps, float step_size,
                                   const float* loss1, const float* loss2, int reinit,
-                                  const uint16_t* gauss_table) {
+                                  const uint32_t* gauss_table) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float t;
@@ -310,7 +306,7 @@ __global__ void gamma_step_kernel(int n, int mode, const float* sq, float* ts, f
     if (delta == 1.0f && iter >= 0) {
       Philox4 p = philox4x32<10>(static_cast<uint32_t>(i), static_cast<uint32_t>(iter), 2u, 0u,
                                  static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-      float z0 = __uint_as_float(static_cast<uint32_t>(gauss_table[p.x & 0xffffu]) << 16);
+      float z0 = gauss_scalar(gauss_table, p.x);
       float lim = (tau / eps) * t;
       z = fminf(fmaxf(z0, -lim), lim);
       zbuf[i] = z;
@@ -377,7 +373,7 @@ extern "C" int dz_zo_sweep_seeded(const void* src, void* dst, long long dst_shif
   a.t_begin = t_begin; a.t_end = t_end; a.chunk_begin = chunk_begin; a.chunk_end = chunk_end;
   a.seed1 = seed1; a.seed1_dev = seed1_dev; a.seed2 = seed2; a.c1 = c1; a.c2 = c2; a.c1_ptr = c1_ptr; a.c2_ptr = c2_ptr;
   a.alpha = alpha; a.chunk_sq = chunk_sq; a.sr_seed = sr_seed;
-  a.gauss_table = (const uint16_t*)gauss_table;
+  a.gauss_table = (const uint32_t*)gauss_table;
   int key = (z2 ? 1 : 0) | (blend ? 2 : 0) | (norm ? 4 : 0) | (sr ? 8 : 0);
   switch (key) {
 #define DZ_CASE(K, A, B, C, D) case K: return launch_sweep<A, B, C, D>(a, stream);
@@ -421,7 +417,7 @@ extern "C" int dz_gamma_step(int n, int mode, const float* sq, float* ts, float*
   if (n <= 0 || !ts || !gamma || !zbuf || !alpha || !gauss_table) return DZ_ERR_ARG;
   gamma_step_kernel<<<(n + 127) / 128, 128, 0, stream>>>(n, mode, sq, ts, gamma, zbuf, alpha, seed,
                                                          iter, delta, tau, eps, step_size, loss1,
-                                                         loss2, reinit, (const uint16_t*)gauss_table);
+                                                         loss2, reinit, (const uint32_t*)gauss_table);
   return cuda_rc(cudaGetLastError());
 }
 
@@ -434,12 +430,12 @@ extern "C" int dz_scalar_diff(const float* a, const float* b, float scale, float
 
 // z itself (fp32), for tests and for the CPU oracle that consumes the framework's stream.
 __global__ void zo_fill_z_kernel(float* out, long long numel, long long elem_base,
-                                 unsigned long long seed, int tensor_id, const uint16_t* tab) {
+                                 unsigned long long seed, int tensor_id, const uint32_t* tab) {
   long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long e0 = g * 8;
   if (e0 >= numel) return;
   float z[8];
-  gauss8(tab, seed, tensor_id, (uint32_t)((elem_base + e0) >> 3), 0u, z);
+  gauss8<2>(reinterpret_cast<const char*>(tab), seed, tensor_id, (uint32_t)((elem_base + e0) >> 3), 0u, z);
   for (int j = 0; j < 8 && e0 + j < numel; ++j) out[e0 + j] = z[j];
 }
 extern "C" int dz_zo_fill_z(float* out, long long numel, long long elem_base,
@@ -448,6 +444,6 @@ extern "C" int dz_zo_fill_z(float* out, long long numel, long long elem_base,
   if (!out || !gauss_table || numel <= 0 || (elem_base & 7)) return DZ_ERR_ARG;
   long long groups = (numel + 7) / 8;
   zo_fill_z_kernel<<<(unsigned)((groups + 255) / 256), 256, 0, stream>>>(out, numel, elem_base, seed,
-                                                                        tensor_id, (const uint16_t*)gauss_table);
+                                                                        tensor_id, (const uint32_t*)gauss_table);
   return cuda_rc(cudaGetLastError());
 }

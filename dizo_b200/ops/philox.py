@@ -5,10 +5,12 @@ element index ``e`` inside the *full* tensor:
 
     words = Philox4x32-7(counter=(e >> 3, tensor_id, stream, 0), key=(seed_lo, seed_hi))
     w     = words[(e & 7) >> 1];  u = w & 0xffff for even e, w >> 16 for odd e
-    z     = T[u],   T[i] = bfloat16(Phi^-1((i + 0.5) / 65536))
+    i = u & 1023 (quantile bin), k = u >> 10 (position inside the bin)
+    z = bfloat16(a'_i + b_i * (1 + (2k + 1)/128))          one fused multiply-add, one rounding
 
-``T`` (:func:`gauss_table`) is the same 65536-entry inverse-normal-CDF table the CUDA kernels
-stage into shared memory, so the host stream equals the device stream bit for bit.  The
+(:func:`gauss_table_entries`: the inverse normal CDF, piecewise linear over 1024 equal-probability bins).
+The CUDA kernels hold the same 1024 (a', b) pairs in shared memory and evaluate the same fused
+multiply-add, so the host stream equals the device stream bit for bit.  The
 reference instead calls ``torch.manual_seed(seed)`` and ``torch.normal`` per tensor
 (large_models/trainer.py:1438-1444); bit-matching that generator is not a goal.
 """
@@ -78,27 +80,52 @@ def f64_to_bf16_bits(x: np.ndarray) -> np.ndarray:
     return f32_to_bf16_bits(b.view(np.float32))
 
 
-def gauss_table_bits() -> np.ndarray:
-    """uint16[65536]: bf16 bit patterns of Phi^-1((i + 0.5) / 65536) (computed in float64); what the
-    kernels stage into shared memory."""
+GAUSS_BINS = 1024     # equal-probability bins of the piecewise-linear inverse CDF
+GAUSS_SUB = 64        # positions inside a bin
+
+
+def gauss_table_entries() -> np.ndarray:
+    """uint32[1024]: per quantile bin i the pair (a'_i, b_i) as bf16 bit patterns (a' in the low half, b in
+    the high half) with z = a'_i + b_i * m_k, m_k = 1 + (2k + 1)/128: the line with the mean and variance of
+    the 64 quantiles Phi^-1((i + (k + 0.5)/64)/1024), k = 0..63, of bin i (computed in float64), shifted by
+    1.5 b so that m_k comes straight from the index bits.  This is what the kernels hold in shared memory."""
     global _TABLE_BITS
     if _TABLE_BITS is None:
         from scipy.special import ndtri
-        u = (np.arange(65536, dtype=np.float64) + 0.5) / 65536.0
-        _TABLE_BITS = f64_to_bf16_bits(ndtri(u))
+        i = np.arange(GAUSS_BINS, dtype=np.float64)[:, None]
+        k = np.arange(GAUSS_SUB, dtype=np.float64)[None, :]
+        q = ndtri((i + (k + 0.5) / GAUSS_SUB) / GAUSS_BINS)                 # [1024, 64]
+        f = (2 * k + 1) / 128.0 - 0.5                                        # m_k - 1.5, mean zero
+        # line with the bin's own mean and variance (equal to the least-squares line except in the two
+        # tail bins, where it keeps the stream's variance at 1 instead of flattening the tail)
+        a = q.mean(1)
+        b = np.sqrt(q.var(1) / (f * f).mean())
+        b_bits = f64_to_bf16_bits(b)
+        a_bits = f64_to_bf16_bits(a - 1.5 * bf16_bits_to_f32(b_bits).astype(np.float64))
+        _TABLE_BITS = a_bits.astype(np.uint32) | (b_bits.astype(np.uint32) << np.uint32(16))
     return _TABLE_BITS
 
 
+def gauss_from_u16(u: np.ndarray) -> np.ndarray:
+    """16-bit indices -> normals (float32 holding bf16 values): bf16(b * m + a') with one rounding."""
+    u = u.astype(np.uint32)
+    e = gauss_table_entries()[u & np.uint32(GAUSS_BINS - 1)]
+    a = bf16_bits_to_f32((e & np.uint32(0xFFFF)).astype(np.uint16)).astype(np.float64)
+    b = bf16_bits_to_f32((e >> np.uint32(16)).astype(np.uint16)).astype(np.float64)
+    m = 1.0 + (2.0 * (u >> np.uint32(10)).astype(np.float64) + 1.0) / 128.0
+    return bf16_bits_to_f32(f64_to_bf16_bits(b * m + a))                     # product and sum exact in float64
+
+
 def gauss_table() -> np.ndarray:
-    """float32[65536] holding the bf16 table values."""
+    """float32[65536]: the normal for every 16-bit index (a view of the stream's quantile function)."""
     global _TABLE
     if _TABLE is None:
-        _TABLE = bf16_bits_to_f32(gauss_table_bits())
+        _TABLE = gauss_from_u16(np.arange(65536, dtype=np.uint32))
     return _TABLE
 
 
 def gauss_words(words: np.ndarray) -> np.ndarray:
-    """[..., 4] uint32 -> [..., 8] float32 normals (two table look-ups per word)."""
+    """[..., 4] uint32 -> [..., 8] float32 normals (two 16-bit indices per word)."""
     w = words.astype(np.uint32)
     tab = gauss_table()
     out = np.empty(w.shape[:-1] + (8,), dtype=np.float32)

@@ -50,12 +50,13 @@ _tables: dict = {}
 
 
 def gauss_table_dev(device) -> torch.Tensor:
-    """The bf16 inverse-CDF table (as int16 bit patterns) on ``device`` (uploaded once per device)."""
+    """The 1024 (a', b) pairs of the inverse-CDF table (int32 bit patterns) on ``device`` (uploaded once per
+    device)."""
     dev = torch.device(device)
     key = (dev.type, dev.index)
     t = _tables.get(key)
     if t is None:
-        t = torch.from_numpy(philox.gauss_table_bits().view(np.int16).copy()).to(dev)
+        t = torch.from_numpy(philox.gauss_table_entries().view(np.int32).copy()).to(dev)
         _tables[key] = t
     return t
 

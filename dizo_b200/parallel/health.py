@@ -24,6 +24,7 @@ class Heartbeat:
                  prefix: str = "dizo_hb"):
         self.store, self.rank, self.world = store, rank, world
         self.stale_after, self.max_lag, self.prefix = stale_after, max_lag, prefix
+        self._t_start = time.time()
 
     def _key(self, r: int) -> str:
         return f"{self.prefix}/{r}"
@@ -32,11 +33,17 @@ class Heartbeat:
         self.store.set(self._key(self.rank), f"{step}:{time.time():.3f}")
 
     def peers(self) -> dict[int, tuple[int, float]]:
+        """Last (step, time) of every peer; (-1, 0.0) for a peer that has never reported.  The key is
+        probed with ``store.check`` first: ``store.get`` of a missing key blocks until the store's own
+        timeout (minutes), which would hide a rank that died before its first heartbeat."""
         out = {}
         for r in range(self.world):
             if r == self.rank:
                 continue
             try:
+                if not self.store.check([self._key(r)]):
+                    out[r] = (-1, 0.0)
+                    continue
                 raw = self.store.get(self._key(r)).decode()
                 s, t = raw.split(":")
                 out[r] = (int(s), float(t))
@@ -47,6 +54,8 @@ class Heartbeat:
     def check(self, step: int) -> None:
         now = time.time()
         for r, (s, t) in self.peers().items():
+            if s < 0:
+                t = self._t_start            # never reported: silent since this monitor started
             if now - t > self.stale_after:
                 raise PeerLost(f"rank {r} has not reported for {now - t:.1f}s (last step {s})")
             if self.max_lag is not None and step - s > self.max_lag:

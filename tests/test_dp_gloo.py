@@ -146,6 +146,32 @@ def test_dead_peer_is_reported_by_heartbeat():
     assert rc0 == 9 and "PEER_LOST" in out0, out0[-2000:]
 
 
+SILENT_PEER_SCRIPT = textwrap.dedent('''
+    import datetime, os, sys, time, torch, torch.distributed as dist
+    from dizo_b200.parallel.health import Heartbeat, PeerLost
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=60))
+    rank = dist.get_rank()
+    hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, dist.get_world_size(), stale_after=2.0)
+    dist.barrier()
+    if rank == 1:
+        time.sleep(8)                     # alive but never reports a heartbeat
+        os._exit(0)
+    t0 = time.time()
+    try:
+        hb.sync(1)                        # must not block on the missing key until the store times out
+        print("NOT_DETECTED")
+    except PeerLost as e:
+        print("PEER_LOST after %.1f s" % (time.time() - t0), e)
+        os._exit(9 if time.time() - t0 < 6.0 else 10)
+''')
+
+
+def test_peer_that_never_reports_is_lost_within_the_stale_limit():
+    outs = _run_ranks(SILENT_PEER_SCRIPT, 2, timeout=120)
+    rc0, out0 = outs[0]
+    assert rc0 == 9 and "PEER_LOST" in out0, out0[-2000:]
+
+
 TRAINER_PEER_SCRIPT = textwrap.dedent('''
     import datetime, os, sys, time, torch, torch.distributed as dist
     dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=60))

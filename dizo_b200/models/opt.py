@@ -453,7 +453,7 @@ class OPTModel:
             return ar.view(name)
         return get
 
-    def _sweep_group(self, group: int, transform: Transform, dst: torch.Tensor) -> int:
+    def _sweep_group(self, group: int, transform: Transform, dst: torch.Tensor, small: bool = False) -> int:
         lo, hi = self.arena.group_range(group)
         r = self._blend_range(group, transform)
         if r is not None:
@@ -461,7 +461,8 @@ class OPTModel:
             if lo == hi:
                 return 0
         self.arena.sweep(t_begin=lo, t_end=hi, dst=dst, seed1=transform.seed, c1=transform.coef,
-                         c1_dev=transform.coef_dev, seed1_dev=transform.seed_dev, alpha=transform.alpha)
+                         c1_dev=transform.coef_dev, seed1_dev=transform.seed_dev, alpha=transform.alpha,
+                         small=small)
         return self.arena.span(lo, hi)[0]
 
     def _layer_weights(self, i: int, get: Callable[[str], torch.Tensor]) -> SimpleNamespace:
@@ -553,7 +554,8 @@ class OPTModel:
                 with torch.cuda.stream(self._side):
                     if free[k] is not None:
                         self._side.wait_event(free[k])
-                    shift = self._sweep_group(i, transform, buf)
+                    # the small-footprint sweep: shares the SMs with the previous layer's GEMMs
+                    shift = self._sweep_group(i, transform, buf, small=True)
                     ev = torch.cuda.Event()
                     ev.record(self._side)
                 ready[k] = ev

@@ -62,7 +62,8 @@ constexpr int GAUSS_BINS = 1024;                   // (a', b) pairs: low half a'
 constexpr int GAUSS_SMEM_BYTES = GAUSS_BINS * 128;  // replicated per lane (bank) in shared memory
 // Rounds of the z stream: Philox4x32 is Crush-resistant from 7 rounds (Salmon et al., SC'11; 10 is the
 // library default) and the sweep spends a third of its instructions in them.  Must equal Z_PHILOX_ROUNDS
-// of ops/philox.py (the host oracle).  Other streams (gamma draws, stochastic rounding, sampling) keep 10.
+// of ops/philox.py (the host oracle); the stochastic-rounding stream of the update uses the same count.
+// Other streams (gamma draws, sampling) keep 10.
 constexpr int Z_PHILOX_ROUNDS = 7;
 
 // The Philox words of group `grp` (= element index >> 3) of tensor `tid`.

@@ -33,6 +33,8 @@ namespace dz {
 
 constexpr int ZO_CHUNK = 256;    // elements; tensor starts are aligned to this (one warp pass)
 constexpr int ZO_THREADS = 768;  // one persistent CTA (24 warps) per SM
+constexpr int ZO_THREADS_SMALL = 512;  // the variant that shares an SM with a GEMM CTA
+constexpr int ZO_SMEM_SMALL = GAUSS_BINS * 4;
 constexpr int ZO_UNROLL = 4;     // 16-byte loads in flight per lane
 constexpr int ZO_SMEM = GAUSS_SMEM_BYTES; // the lane-replicated inverse-CDF table
 
@@ -88,7 +90,7 @@ __device__ __forceinline__ int find_tensor(const ZoTensor* tab, int lo, int hi, 
 }
 
 // One 256-element chunk: lane l owns elements [8l, 8l+8).  `raw` was loaded by the caller.
-template <bool Z2, bool BLEND, bool NORM, bool SR>
+template <bool Z2, bool BLEND, bool NORM, bool SR, int TS>
 __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t, float alpha,
                                          long long cpos, int lane, const uint4 raw,
                                          const char* tab, float c1, float c2, uint32_t c1_pair) {
@@ -98,7 +100,7 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
   if (PACKED) {
     if (e0 < t.numel) {
       uint4 o = raw;
-      if (c1 != 0.f) o = perturb8_packed<7>(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
+      if (c1 != 0.f) o = perturb8_packed<TS>(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
       if (e0 + 8 > t.numel) {
         // ragged tail of a tensor: keep the padding elements as they were
         uint32_t ov[4] = {o.x, o.y, o.z, o.w};
@@ -134,20 +136,20 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
     const uint32_t grp = zo_group(t, e0);
     if (c1 != 0.f) {
       float z[8];
-      gauss8<7>(tab, a.seed1, t.tensor_id, grp, 0u, z);
+      gauss8<TS>(tab, a.seed1, t.tensor_id, grp, 0u, z);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = fmaf(c1, z[j], v[j]);
     }
     if (Z2) {
       float z[8];
-      gauss8<7>(tab, a.seed2, t.tensor_id, grp, 0u, z);
+      gauss8<TS>(tab, a.seed2, t.tensor_id, grp, 0u, z);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = fmaf(c2, z[j], v[j]);
     }
     uint32_t o[4];
     if (SR) {
       // stochastic rounding: add 16 random bits below the bf16 mantissa, truncate
-      Philox4 rb = philox4x32<10>(grp, t.tensor_id, 1u, 0u, static_cast<uint32_t>(a.sr_seed),
+      Philox4 rb = philox4x32<Z_PHILOX_ROUNDS>(grp, t.tensor_id, 1u, 0u, static_cast<uint32_t>(a.sr_seed),
                                   static_cast<uint32_t>(a.sr_seed >> 32));
       uint32_t rw[4] = {rb.x, rb.y, rb.z, rb.w};
 #pragma unroll
@@ -192,20 +194,36 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
   }
 }
 
-// Persistent: one CTA of 32 warps per SM.  The inverse-CDF table sits in shared memory;
-// (replicated per lane, conflict-free); every warp owns a contiguous run of chunks and keeps ZO_UNROLL 16-byte loads per lane in
-// flight (64 KB per SM), which is what it takes to cover HBM latency at full bandwidth.
-template <bool Z2, bool BLEND, bool NORM, bool SR>
-__global__ void __launch_bounds__(ZO_THREADS, 1)
+// Persistent: one CTA of 24 warps per SM.  The inverse-CDF table sits in shared memory (replicated per
+// lane, conflict-free); every warp owns a contiguous run of chunks and works on ZO_UNROLL chunks at a
+// time while the loads of the next ZO_UNROLL chunks are already in flight (register double buffering:
+// 2 x 64 bytes per lane, ~100 KB per SM), so HBM latency is covered while z is computed.
+//
+// SMALL: the variant that runs beside a GEMM.  Its table is the plain 4 KB copy (bank conflicts
+// instead of 128 KB of shared memory) and it is bounded to 512 threads x 64 registers, so one of its
+// CTAs fits on an SM that already holds a GEMM CTA (~200 KB of shared memory, 192 threads): launched on
+// a second stream it sweeps the next layer in the shadow of the tensor-core work, which leaves the
+// issue slots and HBM almost idle.
+template <bool Z2, bool BLEND, bool NORM, bool SR, bool SMALL>
+__global__ void __launch_bounds__(SMALL ? ZO_THREADS_SMALL : ZO_THREADS, SMALL ? 2 : 1)
 zo_sweep_kernel(const ZoSweepArgs a_in) {
+  constexpr int THREADS = SMALL ? ZO_THREADS_SMALL : ZO_THREADS;
+  constexpr int TS = SMALL ? 2 : 7;                 // log2 bytes between table entries
   ZoSweepArgs a = a_in;
   if (a.seed1_dev) {
     a.seed1 = *a.seed1_dev;     // a captured launch takes the step's seed from memory,
     if (SR) a.sr_seed = a.seed1 * 0x9E3779B97F4A7C15ull + 1ull;   // and its rounding stream follows the seed
   }
   extern __shared__ __align__(16) uint8_t zo_smem[];
-  gauss_table_to_smem(zo_smem, a.gauss_table, threadIdx.x, ZO_THREADS);
-  const char* tab = reinterpret_cast<const char*>(zo_smem) + 4 * (threadIdx.x & 31);   // this lane's bank
+  const char* tab;
+  if (SMALL) {
+    for (int i = threadIdx.x; i < GAUSS_BINS; i += THREADS)
+      reinterpret_cast<uint32_t*>(zo_smem)[i] = __ldg(a.gauss_table + i);
+    tab = reinterpret_cast<const char*>(zo_smem);
+  } else {
+    gauss_table_to_smem(zo_smem, a.gauss_table, threadIdx.x, THREADS);
+    tab = reinterpret_cast<const char*>(zo_smem) + 4 * (threadIdx.x & 31);   // this lane's bank
+  }
   __syncthreads();
   float c1 = a.c1, c2 = a.c2;
   if (a.c1_ptr) c1 *= __ldg(a.c1_ptr);
@@ -213,7 +231,7 @@ zo_sweep_kernel(const ZoSweepArgs a_in) {
   const uint32_t c1_pair = bf16x2_splat(c1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int WARPS = ZO_THREADS / 32;
+  constexpr int WARPS = THREADS / 32;
   const long long total = a.chunk_end - a.chunk_begin;
   const long long nwarps = (long long)gridDim.x * WARPS;
   const long long per = (total + nwarps - 1) / nwarps;
@@ -227,6 +245,8 @@ zo_sweep_kernel(const ZoSweepArgs a_in) {
   float alpha = 1.f;
   if (BLEND && t.slot >= 0) alpha = __ldg(a.alpha + t.slot);
 
+  uint4 nxt[ZO_UNROLL];
+  bool have = false;           // nxt holds the chunks [chunk, chunk + ZO_UNROLL)
   while (chunk < chunk_stop) {
     const long long cpos = chunk * ZO_CHUNK;
     if (cpos >= t_next) {
@@ -236,24 +256,33 @@ zo_sweep_kernel(const ZoSweepArgs a_in) {
       t_next = (cur + 1 < a.t_end) ? a.table[cur + 1].offset : (1ll << 62);
       if (BLEND && t.slot >= 0) alpha = __ldg(a.alpha + t.slot);
     }
-    const long long in_tensor = (min(t_next, t.offset + ((t.numel + ZO_CHUNK - 1) / ZO_CHUNK) * ZO_CHUNK) - cpos) / ZO_CHUNK;
-    if (chunk + ZO_UNROLL <= chunk_stop && in_tensor >= ZO_UNROLL &&
-        cpos - t.offset + ZO_UNROLL * ZO_CHUNK <= t.numel) {
-      // fast path: ZO_UNROLL full chunks of the same tensor, all loads issued first
+    // ZO_UNROLL full chunks of this tensor, inside this warp's run, start at chunk c
+    const long long full_end = t.offset + (t.numel / ZO_CHUNK) * ZO_CHUNK;
+    const bool fast = chunk + ZO_UNROLL <= chunk_stop && cpos + ZO_UNROLL * ZO_CHUNK <= full_end;
+    if (fast) {
       uint4 raw[ZO_UNROLL];
 #pragma unroll
       for (int u = 0; u < ZO_UNROLL; ++u)
-        raw[u] = *reinterpret_cast<const uint4*>(a.src + cpos + u * ZO_CHUNK + lane * 8);
+        raw[u] = have ? nxt[u] : *reinterpret_cast<const uint4*>(a.src + cpos + u * ZO_CHUNK + lane * 8);
+      const long long npos = cpos + ZO_UNROLL * ZO_CHUNK;
+      // (the small variant has time to spare and registers to save: it does not prefetch)
+      have = !SMALL && chunk + 2 * ZO_UNROLL <= chunk_stop && npos + ZO_UNROLL * ZO_CHUNK <= full_end;
+      if (have) {
+#pragma unroll
+        for (int u = 0; u < ZO_UNROLL; ++u)
+          nxt[u] = *reinterpret_cast<const uint4*>(a.src + npos + u * ZO_CHUNK + lane * 8);
+      }
 #pragma unroll
       for (int u = 0; u < ZO_UNROLL; ++u)
-        zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos + u * ZO_CHUNK, lane, raw[u], tab, c1, c2, c1_pair);
+        zo_chunk<Z2, BLEND, NORM, SR, TS>(a, t, alpha, cpos + u * ZO_CHUNK, lane, raw[u], tab, c1, c2, c1_pair);
       chunk += ZO_UNROLL;
     } else {
       uint4 raw = make_uint4(0, 0, 0, 0);
       if (cpos - t.offset + lane * 8 < t.numel)
         raw = *reinterpret_cast<const uint4*>(a.src + cpos + lane * 8);
-      zo_chunk<Z2, BLEND, NORM, SR>(a, t, alpha, cpos, lane, raw, tab, c1, c2, c1_pair);
+      zo_chunk<Z2, BLEND, NORM, SR, TS>(a, t, alpha, cpos, lane, raw, tab, c1, c2, c1_pair);
       chunk += 1;
+      have = false;
     }
   }
 }
@@ -328,16 +357,20 @@ __global__ void scalar_diff_kernel(const float* a, const float* b, float scale, 
   out[0] = (a[0] - b[0]) * scale;
 }
 
-template <bool Z2, bool BLEND, bool NORM, bool SR>
+template <bool Z2, bool BLEND, bool NORM, bool SR, bool SMALL = false>
 static int launch_sweep(const ZoSweepArgs& a, cudaStream_t stream) {
   long long chunks = a.chunk_end - a.chunk_begin;
   if (chunks <= 0) return DZ_OK;
-  auto kern = zo_sweep_kernel<Z2, BLEND, NORM, SR>;
-  static PerDeviceFlag configured;
-  if (int rc_cfg = ensure_dyn_smem(configured, kern, ZO_SMEM)) return rc_cfg;
-  long long blocks = (chunks + ZO_THREADS / 32 - 1) / (ZO_THREADS / 32);
+  auto kern = zo_sweep_kernel<Z2, BLEND, NORM, SR, SMALL>;
+  constexpr int threads = SMALL ? ZO_THREADS_SMALL : ZO_THREADS;
+  constexpr int smem = SMALL ? ZO_SMEM_SMALL : ZO_SMEM;
+  if (!SMALL) {
+    static PerDeviceFlag configured;
+    if (int rc_cfg = ensure_dyn_smem(configured, kern, smem)) return rc_cfg;
+  }
+  long long blocks = (chunks + threads / 32 - 1) / (threads / 32);
   int grid = (int)(blocks < sm_count() ? blocks : sm_count());
-  kern<<<grid, ZO_THREADS, ZO_SMEM, stream>>>(a);
+  kern<<<grid, threads, smem, stream>>>(a);
   return cuda_rc(cudaGetLastError());
 }
 
@@ -350,7 +383,8 @@ extern "C" int dz_zo_tensor_struct_bytes() { return (int)sizeof(ZoTensor); }
 
 // One sweep over arena chunks [chunk_begin, chunk_end) (tensors [t_begin, t_end) of the
 // table).  flags: bit0 second z term, bit1 blend with anchor, bit2 emit norm partials,
-// bit3 stochastic rounding.
+// bit3 stochastic rounding, bit4 the small-footprint variant that can share SMs with a GEMM
+// (plain perturbation or blend only).
 // seed1_dev (optional): device word holding seed1, read by the kernel instead of the argument, so
 // that a launch captured in a CUDA graph perturbs with a new seed at every replay.
 extern "C" int dz_zo_sweep_seeded(const void* src, void* dst, long long dst_shift, const void* anchor,
@@ -363,7 +397,7 @@ extern "C" int dz_zo_sweep_seeded(const void* src, void* dst, long long dst_shif
                                   cudaStream_t stream) {
   if (!src || !dst || !table || !gauss_table || t_end <= t_begin) return DZ_ERR_ARG;
   if (reinterpret_cast<uintptr_t>(gauss_table) & 15) return DZ_ERR_ALIGN;
-  const bool z2 = flags & 1, blend = flags & 2, norm = flags & 4, sr = flags & 8;
+  const bool z2 = flags & 1, blend = flags & 2, norm = flags & 4, sr = flags & 8, small = flags & 16;
   if ((blend || norm) && !anchor) return DZ_ERR_ARG;
   if (blend && !alpha) return DZ_ERR_ARG;
   if (norm && !chunk_sq) return DZ_ERR_ARG;
@@ -375,6 +409,11 @@ extern "C" int dz_zo_sweep_seeded(const void* src, void* dst, long long dst_shif
   a.alpha = alpha; a.chunk_sq = chunk_sq; a.sr_seed = sr_seed;
   a.gauss_table = (const uint32_t*)gauss_table;
   int key = (z2 ? 1 : 0) | (blend ? 2 : 0) | (norm ? 4 : 0) | (sr ? 8 : 0);
+  if (small) {
+    if (key == 0) return launch_sweep<false, false, false, false, true>(a, stream);
+    if (key == 2) return launch_sweep<false, true, false, false, true>(a, stream);
+    return DZ_ERR_ARG;
+  }
   switch (key) {
 #define DZ_CASE(K, A, B, C, D) case K: return launch_sweep<A, B, C, D>(a, stream);
     DZ_CASE(0, false, false, false, false) DZ_CASE(1, true, false, false, false)

@@ -144,8 +144,8 @@ def perturb_bf16(theta_bits: np.ndarray, coef: float, z: np.ndarray) -> np.ndarr
 
 # Rounds of the perturbation stream z.  Philox4x32 is specified with 10 rounds by default and is
 # "Crush-resistant" from 7 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11); the
-# sweep spends a third of its time in the rounds, so z uses 7 (4.7 -> 5.1 TB/s).  The scalar draws of the
-# gamma search and the stochastic-rounding stream keep 10.  Must equal Z_PHILOX_ROUNDS in csrc/philox.cuh.
+# sweep spends a third of its instructions in the rounds, so z and the stochastic-rounding stream of the
+# update use 7.  The scalar draws of the gamma search keep 10.  Must equal Z_PHILOX_ROUNDS in csrc/philox.cuh.
 Z_PHILOX_ROUNDS = 7
 
 

@@ -211,7 +211,7 @@ class ParamArena:
               seed1: int = 0, c1: float = 0.0, c1_dev: torch.Tensor | None = None,
               seed1_dev: torch.Tensor | None = None, seed2: int = 0, c2: float = 0.0, c2_dev: torch.Tensor | None = None,
               alpha: torch.Tensor | None = None, sq_out: torch.Tensor | None = None,
-              stochastic_round_seed: int | None = None) -> None:
+              stochastic_round_seed: int | None = None, small: bool = False) -> None:
         """dst[range] = round(blend(theta) + c1*z(seed1) + c2*z(seed2)); optional norms.
 
         ``dst=None`` writes the arena in place; otherwise ``dst`` is a staging buffer whose
@@ -221,7 +221,9 @@ class ParamArena:
         switches on the blend ``theta_0 + alpha*(theta - theta_0)`` for slotted pieces;
         ``sq_out`` ([n_slots] fp32) receives ``||stored - theta_0||^2`` per slotted piece of
         the range.  With ``seed1_dev`` a given ``stochastic_round_seed`` only switches stochastic rounding
-        on: the stream's seed is then :func:`sr_seed_for` of the device seed."""
+        on: the stream's seed is then :func:`sr_seed_for` of the device seed.  ``small`` picks the kernel variant
+        with a 4 KB table and a bounded register count that fits on an SM beside a GEMM CTA (for sweeps issued
+        on a side stream; plain perturbation or blend only)."""
         t_end = len(self.pieces) if t_end is None else t_end
         if t_end <= t_begin:
             return
@@ -247,6 +249,8 @@ class ParamArena:
         L = _lib.lib()
         flags = (1 if use_z2 else 0) | (2 if blend else 0) | (4 if norm else 0) | \
                 (8 if stochastic_round_seed is not None else 0)
+        if small and not (use_z2 or norm or stochastic_round_seed is not None):
+            flags |= 16
         if norm and self._chunk_sq is None:
             self._chunk_sq = torch.zeros(max(self._n_sq_chunks, 1), dtype=torch.float32,
                                          device=self.device)
@@ -314,7 +318,7 @@ def _stochastic_round_bf16(v: torch.Tensor, seed: int, p: Piece) -> torch.Tensor
     g0 = p.elem_base >> 3
     grp = (np.arange(g0, g0 + ngroups, dtype=np.uint64) & np.uint64(0xFFFFFFFF)).astype(np.uint32)
     c = philox.philox4x32(grp, np.uint32(p.tensor_id), np.uint32(1), np.uint32(0),
-                          seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+                          seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF, rounds=philox.Z_PHILOX_ROUNDS)
     words = np.stack(c, axis=-1)                      # [groups, 4]
     lo = (words & np.uint32(0xFFFF)).astype(np.uint32)
     hi = (words >> np.uint32(16)).astype(np.uint32)

@@ -196,6 +196,23 @@ def test_sweep_staging_range_and_two_terms():
     assert (k.cpu().float() - want).abs().max().item() < 3e-4
 
 
+def test_small_footprint_sweep_equals_the_regular_one():
+    """The variant that shares SMs with a GEMM (4 KB table, 512 threads) writes the same bits."""
+    ga = _arena(DEV)
+    ga.set_dizo(["l0.k", "l0.v", "l1.k", "l1.v"])
+    ga.sweep(seed1=1, c1=5e-3)
+    lo, hi = ga.group_range(1)
+    n = ga.group_numel(1)
+    alpha = torch.tensor([0.8, 1.2, 1.0, 0.9], dtype=torch.float32, device=DEV)
+    for kw in (dict(seed1=5, c1=1e-3), dict(seed1=5, c1=-1e-3), dict(alpha=alpha), dict(seed1=7, c1=1e-3, alpha=alpha)):
+        a = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+        b = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+        ga.sweep(t_begin=lo, t_end=hi, dst=a, **kw)
+        ga.sweep(t_begin=lo, t_end=hi, dst=b, small=True, **kw)
+        _sync_ok()
+        assert torch.equal(a, b), kw
+
+
 def test_perturb_restore_replay_and_update():
     a = _arena(DEV)
     ref = a.data.clone()

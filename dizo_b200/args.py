@@ -132,6 +132,7 @@ class OurArguments:
     dizo_l1: float = 1e-3                   # L1 weight on gamma in the FO search (:739)
     zo_log_steps: int = 50                  # (:1321)
     zo_eval_steps: int = 100                # in-loop dev evaluation period (:1327)
+    random_init: bool = False               # build --model_name's shape with random weights (no checkpoint needed)
     zo_mode: str = "inflight"               # inflight (theta never rewritten for a forward) | inplace
     zo_stochastic_rounding: Optional[bool] = None   # unbiased bf16 update; default: on for bf16 parameters
     dp: int = 0                             # data-parallel ranks (0 = WORLD_SIZE)

@@ -70,29 +70,59 @@ class Framework:
     # ------------------------------------------------------------------ model / tokenizer
     def _dtype(self) -> torch.dtype:
         a = self.args
-        if a.load_bfloat16 or (self.device.type == "cuda" and (a.load_float16 or a.load_int8)):
-            # the kernels are bf16; fp16/int8 requests run in bf16 on the GPU
-            if a.load_float16 or a.load_int8:
-                logger.warning("fp16 / int8 loading requested: the sm_100a kernels compute in bf16")
-            return torch.bfloat16
         if self.device.type == "cuda":
+            # the sm_100a kernels compute in bf16; an fp16 / int8 request is honoured as a one-time
+            # conversion of the loaded weights to bf16 (same 16-bit footprint, wider exponent)
+            if (a.load_float16 or a.load_int8) and not getattr(Framework, "_told_dtype", False):
+                Framework._told_dtype = True
+                logger.info("--load_float16 / --load_int8: weights are converted once to bfloat16, the "
+                            "precision the sm_100a kernels compute in")
             return torch.bfloat16
-        return torch.float32
+        return torch.bfloat16 if a.load_bfloat16 else torch.float32
+
+    @staticmethod
+    def resolve_model_dir(name: str) -> Optional[str]:
+        """Directory holding ``config.json`` for ``--model_name``: the path itself, or the snapshot of a
+        hub id (``facebook/opt-13b``) in the local Hugging Face cache (``HF_HOME``); None if neither
+        exists.  Nothing is downloaded."""
+        if os.path.isdir(name) and os.path.exists(os.path.join(name, "config.json")):
+            return name
+        if os.path.isdir(name):
+            return None
+        try:
+            from transformers.utils import cached_file
+            cfg = cached_file(name, "config.json", local_files_only=True,
+                              _raise_exceptions_for_missing_entries=False,
+                              _raise_exceptions_for_connection_errors=False)
+        except Exception:  # noqa: BLE001  (malformed ids, cache layout problems)
+            cfg = None
+        return os.path.dirname(cfg) if cfg else None
 
     def load_model(self):
         a = self.args
         with count_time("Loading model with FP%d" % (16 if self._dtype() != torch.float32 else 32)):
-            path = a.model_name
             state = None
-            cfg_path = os.path.join(path, "config.json") if os.path.isdir(path) else None
-            if cfg_path and os.path.exists(cfg_path):
-                with open(cfg_path) as f:
+            path = self.resolve_model_dir(a.model_name)
+            if path is not None:
+                with open(os.path.join(path, "config.json")) as f:
                     cfg = OPTConfig.from_hf(json.load(f))
-                state = load_weights(path, lazy=True)       # one tensor at a time: every rank keeps its slice
+                if cfg.model_type != "opt":
+                    raise NotImplementedError(f"{a.model_name}: model_type {cfg.model_type!r}; the kernels "
+                                              "implement the OPT decoder family")
+                if not a.random_init:
+                    state = load_weights(path, lazy=True)   # one tensor at a time: every rank keeps its slice
             else:
-                key = os.path.basename(path.rstrip("/")).lower().replace("opt1p3b", "opt-1.3b")
+                # no checkpoint: only an explicit --random_init may train on random weights
+                key = os.path.basename(a.model_name.rstrip("/")).lower().replace("opt1p3b", "opt-1.3b")
+                if not a.random_init:
+                    raise FileNotFoundError(
+                        f"--model_name {a.model_name!r} is neither a checkpoint directory nor a model in the "
+                        "local Hugging Face cache (nothing is downloaded). Pass --random_init to build a "
+                        "randomly initialised model of that shape on purpose.")
+                if key not in PRESETS:
+                    raise KeyError(f"--random_init needs a known shape; {key!r} is not one of {sorted(PRESETS)}")
                 cfg = preset(key)
-                logger.warning("no checkpoint at %s: random-init %s", path, key)
+                logger.info("--random_init: %s with random weights", key)
             mode = "full"
             if a.head_tuning:
                 mode = "head"
@@ -141,14 +171,25 @@ class Framework:
             peft_wiring.init_prefix_by_real_activations(model, seed=a.seed)
         return model, tokenizer
 
-    def _load_tokenizer(self, path: str, cfg: OPTConfig):
+    def _load_tokenizer(self, path: Optional[str], cfg: OPTConfig):
+        """The checkpoint's tokenizer (``use_fast=False`` as the reference).  The word-level stub stands in
+        only for ``--random_init`` models, whose vocabulary has no meaning anyway; a checkpoint whose
+        tokenizer does not load is an error, not a silent fallback."""
+        a = self.args
         tok = None
-        if os.path.isdir(path):
+        tok_files = ("tokenizer_config.json", "tokenizer.json", "vocab.json", "tokenizer.model")
+        if path is not None and any(os.path.exists(os.path.join(path, f)) for f in tok_files):
             try:
                 from transformers import AutoTokenizer
-                tok = AutoTokenizer.from_pretrained(path, use_fast=False)
-            except Exception as e:  # pragma: no cover - depends on local files
-                logger.warning("tokenizer load failed (%s): using the stub tokenizer", e)
+                tok = AutoTokenizer.from_pretrained(path, use_fast=False, local_files_only=True)
+            except Exception as e:  # noqa: BLE001
+                if not a.random_init:
+                    raise RuntimeError(f"tokenizer of {path} does not load: {e}. (With --random_init the "
+                                       "stub tokenizer is used instead.)") from e
+                logger.info("tokenizer of %s does not load (%s): --random_init uses the stub tokenizer", path, e)
+        elif path is not None:
+            logger.info("%s holds weights but no tokenizer files (a directory written by save_model of a "
+                        "stub-tokenizer run): using the stub tokenizer", path)
         if tok is None:
             words = ["terrible", "great", "Yes", "No", "Maybe", "It", "was"]
             tok = StubTokenizer(words, vocab_size=cfg.vocab_size)

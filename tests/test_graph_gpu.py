@@ -49,7 +49,7 @@ def test_graph_replay_equals_eager_steps():
 def test_cli_flag_uses_graph(tmp_path, monkeypatch):
     from dizo_b200.run import main
     monkeypatch.chdir(tmp_path)
-    args = ["--task_name", "Synthetic", "--model_name", "opt-125m", "--trainer", "zo", "--num_train", "32",
+    args = ["--task_name", "Synthetic", "--model_name", "opt-125m", "--random_init", "--trainer", "zo", "--num_train", "32",
             "--num_dev", "8", "--num_eval", "16", "--train_set_seed", "0", "--max_steps", "6",
             "--learning_rate", "1e-5", "--per_device_train_batch_size", "8", "--train_as_classification",
             "--save_steps", "0", "--zo_eval_steps", "3", "--max_length", "64", "--enhanced", "zo",

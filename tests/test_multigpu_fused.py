@@ -50,7 +50,7 @@ def test_cli_training_on_two_gpus(tmp_path, layout):
     out = tmp_path / "out"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29537", "-m", "dizo_b200.run",
-           "--task_name", "Synthetic", "--model_name", "opt-125m", "--trainer", "zo", "--enhanced", "zo",
+           "--task_name", "Synthetic", "--model_name", "opt-125m", "--random_init", "--trainer", "zo", "--enhanced", "zo",
            "--num_train", "32", "--num_dev", "8", "--num_eval", "16", "--train_set_seed", "0",
            "--max_steps", "6", "--learning_rate", "1e-5", "--per_device_train_batch_size", "8",
            "--train_as_classification", "--output_dir", str(out), "--save_steps", "4",

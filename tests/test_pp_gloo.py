@@ -57,7 +57,7 @@ CLI_SCRIPT = textwrap.dedent('''
     from dizo_b200.run import main
     tmp = os.environ["PP_TMP"]
     os.chdir(tmp)
-    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--trainer", "zo", "--enhanced", "zo",
+    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--random_init", "--trainer", "zo", "--enhanced", "zo",
                "--num_train", "16", "--num_dev", "4", "--num_eval", "8", "--train_set_seed", "0", "--max_steps", "4",
                "--learning_rate", "1e-4", "--per_device_train_batch_size", "4", "--train_as_classification",
                "--output_dir", os.path.join(tmp, "out"), "--save_steps", "2", "--zo_eval_steps", "2",

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _common(tmp, *extra):
-    return ["--task_name", "Synthetic", "--model_name", "opt-125m", "--trainer", "zo", "--num_train", "32",
+    return ["--task_name", "Synthetic", "--model_name", "opt-125m", "--random_init", "--trainer", "zo", "--num_train", "32",
             "--num_dev", "8", "--num_eval", "16", "--train_set_seed", "0", "--max_steps", "6",
             "--learning_rate", "1e-5", "--per_device_train_batch_size", "8", "--train_as_classification",
             "--output_dir", str(tmp / "out"), "--save_steps", "0", "--zo_eval_steps", "3", "--max_length", "64",

@@ -223,7 +223,7 @@ def test_generation_controls():
 
 def test_run_main_end_to_end(tmp_path, monkeypatch):
     monkeypatch.chdir(tmp_path)
-    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--trainer", "zo", "--num_train", "24",
+    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--random_init", "--trainer", "zo", "--num_train", "24",
                "--num_dev", "8", "--num_eval", "8", "--train_set_seed", "0", "--max_steps", "4",
                "--learning_rate", "1e-3", "--per_device_train_batch_size", "4", "--train_as_classification",
                "--enhanced", "zo", "--dizo_interval", "2", "--dizo_max_iters", "1", "--output_dir",
@@ -240,7 +240,7 @@ def test_run_main_end_to_end(tmp_path, monkeypatch):
     assert "accuracy" in m and "dev_accuracy" in m
     assert os.path.exists(tmp_path / "loss_acc" / "Synthetic_zo_ft_enhanced_zo" / "accuracy_seed_42.npy")
     # zero-shot / ICL path: one demonstration set per evaluation sample
-    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--num_train", "2", "--num_eval", "4",
+    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--random_init", "--num_train", "2", "--num_eval", "4",
                "--max_length", "128"])
     assert rc == 0
     assert result_file_tag(OurArguments(task_name="X", model_name="a/b", num_train=3, tag="t")) == "X-b-ntrain3-t"
@@ -304,7 +304,7 @@ def test_linear_probing_end_to_end(tmp_path, monkeypatch):
     """--linear_probing: features from the forward, logistic regression on the host, coefficients
     written into the LM-head rows of the class tokens (large_models/trainer.py:855-957)."""
     monkeypatch.chdir(tmp_path)
-    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--trainer", "zo", "--linear_probing",
+    rc = main(["--task_name", "Synthetic", "--model_name", "opt-tiny", "--random_init", "--trainer", "zo", "--linear_probing",
                "--lp_early_stopping", "--num_train", "40", "--num_dev", "8", "--num_eval", "16",
                "--train_set_seed", "0", "--per_device_train_batch_size", "8", "--train_as_classification", "False",
                "--output_dir", str(tmp_path / "out"), "--max_length", "64", "--max_steps", "1"])
@@ -329,7 +329,7 @@ def test_non_differentiable_objective_end_to_end(tmp_path, monkeypatch):
                                     "answers": {"text": [ans], "answer_start": [0]}}) + "\n")
     monkeypatch.setenv("DIZO_DATA_DIR", str(tmp_path / "data"))
     monkeypatch.chdir(tmp_path)
-    rc = main(["--task_name", "SQuAD", "--model_name", "opt-tiny", "--trainer", "zo", "--non_diff",
+    rc = main(["--task_name", "SQuAD", "--model_name", "opt-tiny", "--random_init", "--trainer", "zo", "--non_diff",
                "--num_train", "16", "--num_dev", "4", "--num_eval", "4", "--train_set_seed", "0", "--max_steps", "2",
                "--learning_rate", "1e-4", "--per_device_train_batch_size", "4", "--train_as_classification", "False",
                "--output_dir", str(tmp_path / "out"), "--max_length", "96", "--max_new_tokens", "3",

@@ -50,6 +50,9 @@ def parse():
                          "(one global batch of --prompts x --seq)")
     ap.add_argument("--baseline-candidates", type=int, default=2)
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-sharded", action="store_true",
+                    help="N >= 2: do not time the FSDP / tensor-parallel steps (fused kernels vs NCCL composition)")
+    ap.add_argument("--sharded-steps", type=int, default=3)
     return ap.parse_args()
 
 
@@ -147,6 +150,8 @@ def run_ours(a, world, rank, local):
     dev = torch.device("cuda", local)
     cfg = preset(a.model)
     par = a.parallelism if world > 1 else "dp"
+    if par != "dp" and a.enhanced == "fo":
+        raise SystemExit("--enhanced fo runs on replicated parameters (--parallelism dp) only")
     if par == "fsdp":
         from dizo_b200.parallel.fsdp import FSDPOPTModel
         model = FSDPOPTModel(cfg, dev)
@@ -276,6 +281,126 @@ def run_ours(a, world, rank, local):
         "perturb_update_gbs": sweep_gbs,
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
     }
+    if world > 1 and par == "dp" and a.mode == "full" and not a.skip_sharded:
+        # free the replicated model first: the sharded models need the memory
+        del engine, projector, model, resident
+        if not a.skip_e2e:
+            del tr, hb
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        out["extra"] = run_sharded_extras(a, world, rank, local)
+    return out
+
+
+# ------------------------------------------------------------------------------- sharded layouts
+NVLINK_GBS = 770.0            # measured peer copy rate per direction per GPU on this pool (900 nominal)
+
+
+def _peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def run_sharded_extras(a, world, rank, local):
+    """The communication-bound layouts under the same clock as the headline (N >= 2 only): one full ZO
+    step (two forwards, scalar all-reduce, update sweep) of
+
+    * OPT-13B, parameters row-sharded over the N ranks (FSDP), 8 prompts x 1024 tokens per rank: the
+      fused gather + perturb + GEMM launches against the composition perturb -> NCCL all-gather
+      (prefetched on a second stream) -> GEMM;
+    * at N = 8, OPT-66B tensor parallel over the 8 ranks, 16 prompts x 512 tokens in total: fused
+      all-gather -> GEMM and GEMM -> reduce-scatter -> LayerNorm against NCCL all-gather /
+      reduce-scatter between the stand-alone kernels.
+
+    Both arms use this repository's sweep, GEMM and attention kernels; only the collectives differ.
+    Roofline of a step = the slower of (GEMM FLOPs per rank / measured sustained bf16 rate) and (bytes a
+    rank receives over NVLink / 770 GB/s)."""
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import ZOEngine
+    from dizo_b200.models.opt import preset
+    from dizo_b200.ops import _lib
+    from dizo_b200.parallel.composition import FSDPCompositionModel, TPCompositionModel
+    from dizo_b200.parallel.fsdp import FSDPOPTModel
+    from dizo_b200.parallel.tp import TPOPTModel
+    import gc
+
+    dev = torch.device("cuda", local)
+    peaks, peak_kind = _peaks()
+    flops_rate = peaks["bf16_tflops_sustained"] * 1e12
+    K, W = max(1, a.sharded_steps), 2
+    out = {"peaks": peak_kind, "nvlink_gbs": NVLINK_GBS, "steps": K, "warmup": W}
+
+    def time_model(build, prompts, seq, vocab, data_rank, dp_group):
+        model = build()
+        model.init_random_fast(seed=0)
+        eng = ZOEngine(model, eps=1e-3, dp_group=dp_group)
+        bs = [synthetic_batch(s, prompts, seq, vocab, seed=1, rank=data_rank).to(dev) for s in range(W + K)]
+        for s in range(W):
+            eng.step(bs[s], 1e-6, seed=500 + s)
+        barrier(world)
+        _lib.check_device_errors()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(W, W + K):
+            eng.step(bs[s], 1e-6, seed=500 + s)
+        e1.record()
+        barrier(world)
+        _lib.check_device_errors()
+        ms = max_over_ranks(e0.elapsed_time(e1) / K, world)
+        loss = float(eng.loss1.item())
+        del eng, model, bs
+        gc.collect()
+        torch.cuda.empty_cache()
+        return ms, loss
+
+    def record(key, cfg, prompts, seq, arms, tokens, flops_per_rank, nvlink_bytes_per_rank, data_rank, dp_group):
+        rec = {"model": key, "tokens_per_step": tokens}
+        for arm, build in arms:
+            try:
+                ms, loss = time_model(build, prompts, seq, cfg.vocab_size, data_rank, dp_group)
+                rec[f"{arm}_ms"] = ms
+                rec[f"{arm}_loss"] = loss
+            except Exception as e:  # noqa: BLE001  (the headline number must survive a failure here)
+                rec[f"{arm}_error"] = f"{type(e).__name__}: {e}"[:300]
+        roof_ms = max(flops_per_rank / flops_rate, nvlink_bytes_per_rank / (NVLINK_GBS * 1e9)) * 1e3
+        rec["roofline_ms"] = roof_ms
+        if "fused_ms" in rec:
+            rec["fused_of_roofline"] = roof_ms / rec["fused_ms"]
+            rec["fused_tokens_per_sec"] = tokens / (rec["fused_ms"] / 1e3)
+        if "fused_ms" in rec and "composition_ms" in rec:
+            rec["fused_over_composition"] = rec["composition_ms"] / rec["fused_ms"]
+        return rec
+
+    # ---- FSDP, OPT-13B, 8 x 1024 per rank
+    cfg = preset("opt-13b")
+    d, F, nl = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers
+    mat_params = nl * (4 * d * d + 2 * d * F)
+    tokens_rank = 8 * 1024
+    out["fsdp"] = record(
+        "opt-13b", cfg, 8, 1024,
+        [("fused", lambda: FSDPOPTModel(cfg, dev)), ("composition", lambda: FSDPCompositionModel(cfg, dev))],
+        tokens=tokens_rank * world, flops_per_rank=2 * 2.0 * mat_params * tokens_rank,
+        nvlink_bytes_per_rank=2 * 2.0 * mat_params * (world - 1) / world, data_rank=rank, dp_group=None)
+    out["fsdp"]["parallelism"] = f"fsdp{world}"
+
+    # ---- tensor parallel, OPT-66B, 16 x 512 in total (8 GPUs)
+    if world == 8:
+        cfg = preset("opt-66b")
+        d, F, nl = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers
+        mat_params = nl * (4 * d * d + 2 * d * F)
+        tokens = 16 * 512
+        out["tp"] = record(
+            "opt-66b", cfg, 16, 512,
+            [("fused", lambda: TPOPTModel(cfg, dev, max_tokens=tokens)),
+             ("composition", lambda: TPCompositionModel(cfg, dev, max_tokens=tokens))],
+            tokens=tokens, flops_per_rank=2 * 2.0 * mat_params * tokens / world,
+            nvlink_bytes_per_rank=2 * nl * 4 * (tokens * d * 2.0) * (world - 1) / world,
+            data_rank=0, dp_group=False)
+        out["tp"]["parallelism"] = f"tp{world}"
     return out
 
 

@@ -11,6 +11,7 @@ from dizo_b200.data.synthetic import synthetic_batch  # noqa: E402
 from dizo_b200.engine import DiZOProjector, ZOEngine  # noqa: E402
 from dizo_b200.models.opt import OPTModel, Transform, preset  # noqa: E402
 from dizo_b200.ops import _lib  # noqa: E402
+from dizo_b200.parallel.composition import FSDPCompositionModel  # noqa: E402
 from dizo_b200.parallel.fsdp import FSDPOPTModel  # noqa: E402
 
 
@@ -29,9 +30,15 @@ def main():
         assert torch.equal(sd[n], t), n
     # every rank has its own batch shard; the reference sees this rank's shard too
     b = synthetic_batch(0, 4, 192, cfg.vocab_size, rank=rank, cand_ids=(17, 29)).to(dev)
+    # the NCCL composition (sweep -> all-gather -> GEMM) of the same sharded model
+    comp = FSDPCompositionModel(cfg, dev, n_push=8).init_random_fast(0)
+    assert torch.equal(comp.arena.data, fs.arena.data)
     for t in (None, Transform(seed=5, coef=1e-2), Transform(seed=5, coef=-1e-2)):
-        l_fs, l_ref = fs.loss(b, t).item(), ref.loss(b, t).item()
+        l_fs, l_ref, l_comp = fs.loss(b, t).item(), ref.loss(b, t).item(), comp.loss(b, t).item()
         assert abs(l_fs - l_ref) < 2e-2, (t, l_fs, l_ref)
+        # same perturbed bits, same GEMM tiles up to the kernel variant: the two sharded arms agree closely
+        assert abs(l_fs - l_comp) < 5e-3, (t, l_fs, l_comp)
+    del comp
     # data-parallel ZO steps over sharded parameters: g is all-reduced, shards updated locally
     e_fs = ZOEngine(fs, eps=1e-2)
     for step in range(3):

@@ -11,6 +11,7 @@ from dizo_b200.data.synthetic import synthetic_batch  # noqa: E402
 from dizo_b200.engine import DiZOProjector, ZOEngine  # noqa: E402
 from dizo_b200.models.opt import OPTModel, Transform, preset  # noqa: E402
 from dizo_b200.ops import _lib  # noqa: E402
+from dizo_b200.parallel.composition import TPCompositionModel  # noqa: E402
 from dizo_b200.parallel.tp import TPOPTModel  # noqa: E402
 
 
@@ -28,9 +29,14 @@ def main():
     for n, t in ref.state_dict().items():
         assert torch.equal(sd[n], t), n
     b = synthetic_batch(0, 4, 256, cfg.vocab_size, cand_ids=(17, 29)).to(dev)     # 1024 token rows
+    # the NCCL composition (all-gather / reduce-scatter between the stand-alone kernels)
+    comp = TPCompositionModel(cfg, dev, max_tokens=1024, n_push=8).init_random_fast(0)
+    assert torch.equal(comp.arena.data, tp.arena.data)
     for t in (None, Transform(seed=5, coef=1e-2), Transform(seed=5, coef=-1e-2)):
-        l_tp, l_ref = tp.loss(b, t).item(), ref.loss(b, t).item()
+        l_tp, l_ref, l_comp = tp.loss(b, t).item(), ref.loss(b, t).item(), comp.loss(b, t).item()
         assert abs(l_tp - l_ref) < 2e-2, (t, l_tp, l_ref)
+        assert abs(l_tp - l_comp) < 2e-2, (t, l_tp, l_comp)
+    del comp
     # ZO steps: same z on shards as on the full tensors
     e_tp, e_ref = ZOEngine(tp, eps=1e-2, dp_group=False), ZOEngine(ref, eps=1e-2, dp_group=False)
     for step in range(3):

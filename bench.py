@@ -150,8 +150,8 @@ def run_ours(a, world, rank, local):
     dev = torch.device("cuda", local)
     cfg = preset(a.model)
     par = a.parallelism if world > 1 else "dp"
-    if par != "dp" and a.enhanced == "fo":
-        raise SystemExit("--enhanced fo runs on replicated parameters (--parallelism dp) only")
+    if par in ("tp", "pp") and a.enhanced == "fo":
+        raise SystemExit("--enhanced fo runs on replicated or FSDP-sharded parameters (--parallelism dp | fsdp)")
     if par == "fsdp":
         from dizo_b200.parallel.fsdp import FSDPOPTModel
         model = FSDPOPTModel(cfg, dev)

@@ -3,12 +3,16 @@
 //   out = epilogue( A[M,K] * W[N,K]^T )       tcgen05 / TMEM / TMA, as gemm_sm100.cu
 //
 // plus any of
-//   * PUSH role (the first n_push CTAs): copy a block of local rows into every peer's staging
-//     buffer with plain posted stores (all-gather by push), optionally transforming it on the
-//     way: theta + c * z(seed) regenerated from Philox for the pushed shard (FSDP parameter
+//   * PUSH role (four extra warps in EVERY CTA): copy a block of local rows into every peer's
+//     staging buffer with plain posted stores (all-gather by push), optionally transforming it on
+//     the way: theta + c * z(seed) regenerated from Philox for the pushed shard (FSDP parameter
 //     all-gather fused with the perturbation - the owner perturbs its shard once, nobody
-//     materialises z).  When a CTA has pushed its slice it fences at system scope; the last
-//     one raises the `ready` flag of this rank at every peer.
+//     materialises z).  The push warps of CTA b move slice b of the rows while the producer, MMA
+//     and epilogue warps of the same CTA run GEMM tiles: a tcgen05 GEMM leaves the issue slots and
+//     the load/store path of its SM almost idle, so the transfer rides along without taking SMs
+//     away from the tensor-core work (dedicating whole CTAs to it cost 16 of 148 SMs).  When a
+//     CTA has pushed its slice it fences at system scope; the last one raises the `ready` flag of
+//     this rank at every peer.
 //   * GATHERED OPERAND: rows of A (tensor parallel: sequence-sharded activations) or of W
 //     (FSDP: row-sharded weights) arrive from peers in this rank's staging buffer; the TMA
 //     producer polls the source rank's `ready` flag (bounded) before its first load of rows
@@ -35,13 +39,20 @@ constexpr int CG_BN = 256;
 constexpr int CG_BK = 64;
 constexpr int CG_STAGES_PUSH = 4;   // ring depth with the reduce-scatter epilogue (plus 32 KB of row staging)
 constexpr int CG_STAGES_PLAIN = 4;
-constexpr int CG_THREADS = 192;
+constexpr int CG_GEMM_THREADS = 192;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue
+constexpr int CG_PUSH_THREADS = 128;   // warps 6-9: the push role
+constexpr int CG_THREADS = CG_GEMM_THREADS + CG_PUSH_THREADS;
+constexpr int CG_TABLE_BYTES = GAUSS_BINS * 4;   // plain copy of the inverse-CDF pairs for perturbing pushes
 constexpr int CG_A_BYTES = CG_BM * CG_BK * 2;
 constexpr int CG_B_BYTES = CG_BN * CG_BK * 2;
 constexpr int CG_STAGE_BYTES = CG_A_BYTES + CG_B_BYTES;
 constexpr int CG_OUT_STAGE_BYTES = 4 * 32 * 256;                // per epilogue warp: 32 rows x 128 bf16 columns
+// behind the operand ring: the row staging of the push epilogue, or the table of a perturbing push
+// (never both in one launch)
 constexpr int CG_SMEM_PUSH = CG_STAGES_PUSH * CG_STAGE_BYTES + CG_OUT_STAGE_BYTES + 1024;
-constexpr int CG_SMEM_PLAIN = CG_STAGES_PLAIN * CG_STAGE_BYTES + 1024;   // both >= the 128 KB Gaussian table
+constexpr int CG_SMEM_PLAIN = CG_STAGES_PLAIN * CG_STAGE_BYTES + CG_TABLE_BYTES + 1024;
+static_assert(CG_STAGES_PUSH == CG_STAGES_PLAIN, "one kernel instantiation expected");
+static_assert(CG_TABLE_BYTES <= CG_OUT_STAGE_BYTES, "the table must fit where the row staging sits");
 constexpr uint32_t CG_TMEM_COLS = 2 * CG_BN;
 constexpr int CG_MAX_WORLD = 16;
 constexpr int CG_MAXC = 16;            // progress chunks per source in a gathered operand
@@ -65,7 +76,6 @@ struct CommGemmArgs {
                                  // (fused q|k|v: d); 0 = no repetition
   int wait_self;                 // own rows are also produced by this launch's push role
   int chunk_tiles;               // gather 1: row tiles per progress chunk of a source (0 = one chunk)
-  int join_tiles;                // tiles at the end of the order left to the push CTAs (0 = none)
   const uint32_t* ready_flags;   // local [world][CG_MAXC]: flag[s][c] >= ready_epoch once rank s has
                                  // pushed chunk c of its rows (unchunked pushes use c = 0 only)
   uint32_t ready_epoch;
@@ -80,7 +90,7 @@ struct CommGemmArgs {
   uint32_t* const* rs_flag_ptrs; // per rank: its [world] "partials ready" words
   uint32_t rs_epoch;
   // ---- push role
-  int n_push;                    // CTAs doing the push (0 = none)
+  int n_push;                    // > 0: this launch pushes (every CTA's push warps take one slice)
   int push_nseg;                 // 1..3 row segments of equal shape (e.g. the q, k, v shards)
   const __nv_bfloat16* push_src[3]; // local rows [push_rows, push_cols], row stride push_ld
   long long push_ld;
@@ -175,27 +185,37 @@ __device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, 
   }
 }
 
-__device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* smem_raw) {
+// Barrier of the push warps only (named barrier 1); the GEMM warps never wait on it.
+__device__ __forceinline__ void cg_push_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(CG_PUSH_THREADS) : "memory");
+}
+
+// Executed by the CG_PUSH_THREADS push threads of every CTA; `pt` is the thread's index among them,
+// slice `blockIdx.x` of `gridDim.x` equal slices of the rows is this CTA's share.
+__device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* table_smem, const int pt) {
+  const int n_slices = (int)gridDim.x;
   __shared__ int s_go;
   __shared__ int s_first_idle;     // first chunk counter this launch leaves untouched
   // stage the inverse-CDF table when the pushed rows are perturbed
-  const char* tab = nullptr;
+  const char* tab = reinterpret_cast<const char*>(table_smem);
   if (p.push_perturb) {
-    gauss_table_to_smem(smem_raw, p.gauss_table, threadIdx.x, CG_THREADS);
-    tab = reinterpret_cast<const char*>(smem_raw) + 4 * (threadIdx.x & 31);   // this lane's bank
+    // the plain 4 KB table (the lane-replicated 128 KB copy of the sweep kernel does not fit beside the
+    // GEMM's operand ring; the bank conflicts cost nothing here, the transfer is NVLink-bound)
+    for (int i = pt; i < GAUSS_BINS; i += CG_PUSH_THREADS)
+      reinterpret_cast<uint32_t*>(table_smem)[i] = __ldg(p.gauss_table + i);
   }
-  if (threadIdx.x == 0) { s_go = 1; s_first_idle = 0; }
-  __syncthreads();
+  if (pt == 0) { s_go = 1; s_first_idle = 0; }
+  cg_push_sync();
   // the peers must have consumed what this buffer held before
-  if (p.push_wait_epoch != 0 && (int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
-    if (!cg_wait_flag(p.push_wait_acks + threadIdx.x, p.push_wait_epoch, nullptr, p.err)) s_go = 0;
+  if (p.push_wait_epoch != 0 && pt < p.world && pt != p.rank) {
+    if (!cg_wait_flag(p.push_wait_acks + pt, p.push_wait_epoch, nullptr, p.err)) s_go = 0;
   }
-  __syncthreads();
+  cg_push_sync();
   if (s_go) {
     const long long vec_per_row = p.push_cols >> 3;
     const long long seg_total = p.push_rows * vec_per_row;
     const long long total = seg_total * p.push_nseg;
-    const long long per = (total + p.n_push - 1) / p.n_push;
+    const long long per = (total + n_slices - 1) / n_slices;
     const long long v0 = (long long)blockIdx.x * per;
     const long long v1 = min(v0 + per, total);
     if (!p.push_perturb) {
@@ -210,16 +230,16 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
         const long long rows_c = min(crows, p.push_rows - row_lo);
         const long long seg_c = rows_c * vec_per_row;
         const long long total_c = seg_c * p.push_nseg;
-        const long long per_c = (total_c + p.n_push - 1) / p.n_push;
+        const long long per_c = (total_c + n_slices - 1) / n_slices;
         const long long c0 = (long long)blockIdx.x * per_c;
         const long long c1 = min(c0 + per_c, total_c);
-        for (long long base = c0; base < c1; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
+        for (long long base = c0; base < c1; base += (long long)CG_PUSH_THREADS * CG_PUSH_UNROLL) {
           uint4 raw[CG_PUSH_UNROLL];
           long long doff[CG_PUSH_UNROLL];
           bool live[CG_PUSH_UNROLL];
 #pragma unroll
           for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
-            const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
+            const long long vv = base + (long long)u * CG_PUSH_THREADS + pt;
             live[u] = vv < c1;
             if (live[u]) {
               const int seg = (int)(vv / seg_c);
@@ -239,8 +259,8 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
           }
         }
         __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) {
+        cg_push_sync();
+        if (pt == 0) {
           unsigned int old = atomicAdd(p.counters + 2 + c, 1u);
           if (old + 1u == p.push_target) {
             __threadfence_system();
@@ -254,13 +274,13 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
     // Perturbed push: z is generated once per element, then stored to every destination.
     // CG_PUSH_UNROLL independent 16-byte loads per thread are in flight before the first store:
     // a copy loop with one load at a time is bound by local-memory latency, not by NVLink.
-    for (long long base = v0; base < v1; base += (long long)CG_THREADS * CG_PUSH_UNROLL) {
+    for (long long base = v0; base < v1; base += (long long)CG_PUSH_THREADS * CG_PUSH_UNROLL) {
       uint4 raw[CG_PUSH_UNROLL];
       long long doff[CG_PUSH_UNROLL];
       bool live[CG_PUSH_UNROLL];
 #pragma unroll
       for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
-        const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
+        const long long vv = base + (long long)u * CG_PUSH_THREADS + pt;
         live[u] = vv < v1;
         if (live[u]) {
           const int seg = (int)(vv / seg_total);
@@ -275,13 +295,13 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
 #pragma unroll
         for (int u = 0; u < CG_PUSH_UNROLL; ++u) {
           if (!live[u]) continue;
-          const long long vv = base + (long long)u * CG_THREADS + threadIdx.x;
+          const long long vv = base + (long long)u * CG_PUSH_THREADS + pt;
           const int seg = (int)(vv / seg_total);
           const long long v = vv - seg * seg_total;
           const long long r = v / vec_per_row, c = (v - r * vec_per_row) << 3;
           const long long e = p.push_elem_base[seg] + r * p.push_cols + c;
           // the same packed bf16 fma as the staging sweep, so a pushed shard equals a swept one bit for bit
-          raw[u] = perturb8_packed<7>(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3),
+          raw[u] = perturb8_packed<2>(tab, p.push_seed, (uint32_t)p.push_tensor_id[seg], (uint32_t)(e >> 3),
                                    push_coef_pair, raw[u]);
         }
       }
@@ -298,8 +318,8 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* sme
     }
   }
   __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  cg_push_sync();
+  if (pt == 0) {
     unsigned int old = atomicAdd(p.counters + 0, 1u);
     // the chunk counters this launch did not use stay in step with the common one
     for (int c = s_first_idle; c < CG_MAXC; ++c) atomicAdd(p.counters + 2 + c, 1u);
@@ -323,24 +343,16 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
 
-  // Push CTAs finish their copy long before the GEMM CTAs finish their tiles; with join_tiles > 0
-  // they then take the LAST join_tiles tiles of the tile order (the rows that arrive last anyway)
-  // instead of leaving their SMs idle.
-  const bool pusher = (int)blockIdx.x < p.n_push;
-  if (pusher) {
-    cg_push_role(p, smem_raw);
-    if (p.join_tiles <= 0) return;
-    __syncthreads();
-  }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int num_tiles = p.num_m * p.num_n;
   const int num_kb = (p.K + CG_BK - 1) / CG_BK;
-  const int reg_tiles = p.num_m * p.num_n - p.join_tiles;      // tiles of the CTAs that only multiply
-  const int cta = pusher ? reg_tiles + (int)blockIdx.x : (int)blockIdx.x - p.n_push;
-  const int n_cta = pusher ? p.n_push : (int)gridDim.x - p.n_push;
-  const int tile_end = pusher ? num_tiles : reg_tiles;
+  const int cta = (int)blockIdx.x;
+  const int n_cta = (int)gridDim.x;
+  const int tile_end = num_tiles;
+  // the table of the push warps sits behind the operand ring (where a push epilogue stages its rows)
+  uint8_t* table_smem = smem_raw + ((smem_base - smem_u32(smem_raw)) + CG_STAGES * CG_STAGE_BYTES);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -353,8 +365,10 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(smem_u32(&bar_acc_empty[a]), 4);
     }
     fence_mbar_init();
-    prefetch_tmap(&tmA);
-    prefetch_tmap(&tmB);
+    if (num_tiles > 0) {          // a push-only launch carries no tensor maps
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&s_tmem_base), CG_TMEM_COLS);
@@ -365,7 +379,10 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
 
-  if (warp == 0) {
+  if (warp >= CG_GEMM_THREADS / 32) {
+    // ------------------------------------------------------------ push warps
+    if (p.n_push > 0) cg_push_role(p, table_smem, (int)threadIdx.x - CG_GEMM_THREADS);
+  } else if (warp == 0) {
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
@@ -636,12 +653,21 @@ struct DzCommGemmDesc {
   long long push_elem_base[3]; const void* gauss_table;
   // bookkeeping
   int rank, world; void* counters; unsigned int push_target, gemm_target;
-  int gemm_ctas;                 // 0 = all remaining SMs
+  int gemm_ctas;                 // (unused)
   int chunk_rows;                // all-gather -> GEMM: rows per progress chunk of a source (0 = one chunk)
-  int join_tiles;                // tiles the push CTAs multiply after pushing (0 = they exit)
+  int join_tiles;                // (unused)
 };
 
 extern "C" int dz_comm_gemm_desc_bytes() { return (int)sizeof(DzCommGemmDesc); }
+
+// CTAs of a launch of this shape: one per SM when it pushes (every CTA carries a slice of the push),
+// otherwise one per output tile up to the SM count.  The host keeps its completion counters in step with it.
+extern "C" int dz_comm_gemm_grid(int M, int N, int pushes) {
+  const int sms = sm_count();
+  if (pushes) return sms;
+  const long long tiles = (long long)((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
+  return (int)(tiles < sms ? tiles : sms);
+}
 
 extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t stream) {
   if (!d) return DZ_ERR_ARG;
@@ -676,7 +702,7 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
       if (!d->push_src[sgi]) return DZ_ERR_ARG;
       if (d->push_perturb && (d->push_elem_base[sgi] & 7)) return DZ_ERR_ARG;
     }
-    if (d->push_perturb && !d->gauss_table) return DZ_ERR_ARG;
+    if (d->push_perturb && (!d->gauss_table || d->push_out)) return DZ_ERR_ARG;
   }
   a.out = d->out; a.ldo = d->ldo;
   a.bias = (const __nv_bfloat16*)d->bias; a.residual = (const __nv_bfloat16*)d->residual; a.ldr = d->ldr;
@@ -719,30 +745,12 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   if (!a.counters) return DZ_ERR_ARG;
   static PerDeviceFlag configured;
   if (int rc_cfg = ensure_dyn_smem(configured, comm_gemm_kernel<CG_STAGES_PUSH>, CG_SMEM_PUSH)) return rc_cfg;
-  int gemm_ctas = 0;
-  if (has_gemm) {
-    int tiles = a.num_m * a.num_n;
-    int avail = sm_count() - a.n_push;
-    if (avail < 1) return DZ_ERR_ARG;
-    int join = (a.n_push > 0 && d->join_tiles > 0) ? d->join_tiles : 0;
-    if (join >= tiles) return DZ_ERR_ARG;
-    a.join_tiles = join;
-    gemm_ctas = d->gemm_ctas > 0 ? d->gemm_ctas : avail;
-    if (gemm_ctas > avail) gemm_ctas = avail;
-    if (gemm_ctas > tiles - join) gemm_ctas = tiles - join;
-  }
-  // every CTA must be resident at once (the roles wait on one another through flags)
-  if (a.n_push + gemm_ctas > sm_count()) return DZ_ERR_TOO_LARGE;
+  // one CTA per SM at most: every CTA must be resident at once (the roles wait on one another through flags)
+  const int grid = dz_comm_gemm_grid(has_gemm ? d->M : 0, has_gemm ? d->N : 0, a.n_push > 0);
+  if (grid < 1 || grid > sm_count()) return DZ_ERR_TOO_LARGE;
   if (a.push_out)
-    comm_gemm_kernel<CG_STAGES_PUSH><<<a.n_push + gemm_ctas, CG_THREADS, CG_SMEM_PUSH, stream>>>(tmA, tmB, a);
+    comm_gemm_kernel<CG_STAGES_PUSH><<<grid, CG_THREADS, CG_SMEM_PUSH, stream>>>(tmA, tmB, a);
   else
-    comm_gemm_kernel<CG_STAGES_PLAIN><<<a.n_push + gemm_ctas, CG_THREADS, CG_SMEM_PLAIN, stream>>>(tmA, tmB, a);
+    comm_gemm_kernel<CG_STAGES_PLAIN><<<grid, CG_THREADS, CG_SMEM_PLAIN, stream>>>(tmA, tmB, a);
   return cuda_rc(cudaGetLastError());
-}
-
-// CTAs that only multiply, for a launch of this shape whose push CTAs take join_tiles tiles themselves
-extern "C" int dz_comm_gemm_ctas(int M, int N, int n_push, int join_tiles) {
-  int tiles = ((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN) - (join_tiles > 0 ? join_tiles : 0);
-  int avail = sm_count() - n_push;
-  return tiles < avail ? tiles : avail;
 }

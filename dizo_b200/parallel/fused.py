@@ -89,11 +89,7 @@ class FusedComm:
         total = 2 * ag_bytes + 2 * rs_bytes + 2 * w_bytes + 64 * 1024 + 8 * norm_slots * (self.world + 1)
         self.region = SymmRegion(total + 16 * 4096, self.group, device)
         self.device = self.region.device
-        self.n_push = n_push
-        # Optional: push CTAs multiply tail tiles once their copy is out.  Off by default: on 8 GPUs the
-        # estimate of when the push ends was too optimistic and the joiners became the critical path
-        # (all-gather -> GEMM, OPT-66B shapes: 0.69 ms with, 0.61 ms without).
-        self.join = False
+        self.n_push = n_push          # kept for callers; the push now rides in every CTA (see comm_gemm.cu)
         self.ag = [_Channel(self.region, ag_bytes) for _ in range(2)] if ag_bytes else []
         self.rs = [_Channel(self.region, rs_bytes) for _ in range(2)] if rs_bytes else []
         self.wst = [_Channel(self.region, w_bytes) for _ in range(2)] if w_bytes else []
@@ -117,38 +113,17 @@ class FusedComm:
         assert ctypes.sizeof(_Desc) == L.dz_comm_gemm_desc_bytes(), "launch descriptor out of step with the library"
         d.rank, d.world = self.rank, self.world
         d.counters = self.counters.data_ptr()
+        # every CTA of a pushing launch carries a slice of the push (four extra warps beside its GEMM
+        # warps), and every CTA of any launch reports its completion: the counters advance by the grid size
+        grid = L.dz_comm_gemm_grid(M, N, int(push))
+        d.n_push = 1 if push else 0
         if push:
-            d.n_push = self.n_push
-            self._push_total += self.n_push
+            self._push_total += grid
             d.push_target = self._push_total & 0xFFFFFFFF
-        else:
-            d.n_push = 0
-        if M > 0:
-            join = self._join_tiles(d, M, N) if (push and self.join) else 0
-            ctas = L.dz_comm_gemm_ctas(M, N, d.n_push, join)
-            d.join_tiles = join
-            self._gemm_total += ctas + (d.n_push if join else 0)
-            d.gemm_target = self._gemm_total & 0xFFFFFFFF
-            d.gemm_ctas = ctas
+        self._gemm_total += grid
+        d.gemm_target = self._gemm_total & 0xFFFFFFFF
         rc = L.dz_comm_gemm(ctypes.byref(d), _lib.ptr(_lib.err_word(self.device)), _lib.stream_ptr())
         _lib.check(rc, "dz_comm_gemm")
-
-    def _join_tiles(self, d: _Desc, M: int, N: int) -> int:
-        """How many tiles at the end of the tile order the push CTAs take after their copy, so that
-        they and the CTAs that only multiply finish together.  Estimated from the bytes pushed (at the
-        rate a handful of CTAs reaches over NVLink) and the tensor-core time of one 128x256 tile."""
-        if d.push_perturb:
-            return 0                                   # the perturbing push keeps its CTAs busy
-        tiles = -(-M // 128) * -(-N // 256)
-        P = self.n_push
-        G = min(_SM_COUNT - P, tiles)
-        if tiles <= G + P:
-            return 0
-        t_tile = 2.0 * 128 * 256 * d.K / 8.0e12                               # seconds on one SM
-        out_bytes = d.push_nseg * d.push_rows * d.push_cols * 2 * max(1, self.world - 1)
-        tau = out_bytes / 350e9
-        j = (tiles / G - tau / t_tile) / (1.0 / G + 1.0 / P)
-        return int(max(0, min(0.8 * j, tiles - G)))
 
     def barrier(self) -> None:
         """All ranks have reached this point of their current streams (P2P flags, bounded wait)."""

@@ -48,7 +48,6 @@ def main():
     ap.add_argument("--ffn-dim", dest="ffn", type=int, default=36864)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--push-ctas", dest="n_push", type=int, default=16)
-    ap.add_argument("--join", action="store_true", help="push CTAs multiply tail tiles after pushing instead of exiting")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -59,7 +58,6 @@ def main():
     M, d, F = a.m, a.d, a.ffn
     Fl, rows = F // world, M // world
     fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2, n_push=a.n_push)
-    fc.join = a.join
     g = torch.Generator(device=dev).manual_seed(1)
     x_local = torch.randn(rows, d, device=dev, generator=g).bfloat16()
     w1 = (torch.randn(Fl, d, device=dev, generator=g) * 0.02).bfloat16()

@@ -144,8 +144,8 @@ class Framework:
                                    untie_emb=a.untie_emb)
                 self.dp_group = False
             elif a.tp > 1 or a.fsdp_shard:
-                assert a.enhanced != "fo", \
-                    "the first-order gamma search runs on replicated parameters (data parallel) only"
+                assert a.enhanced != "fo" or (a.fsdp_shard and a.tp <= 1), \
+                    "the first-order gamma search runs on replicated or FSDP-sharded parameters"
                 # sharded layouts (full-parameter ZO, fused collectives over NVLink peer memory)
                 assert mode == "full" and self.device.type == "cuda" and world > 1, \
                     "--tp / --fsdp_shard need full-parameter mode on >= 2 GPUs"

@@ -343,8 +343,11 @@ class OurTrainer:
         self.base_model = self.model.arena.anchor
         fo_loss = None
         if a.enhanced == "fo":
-            from .models.opt_autograd import make_fo_loss
-            fo_loss = make_fo_loss(self.model)
+            from .models import gamma_grad
+            if not gamma_grad.supported(self.model):
+                # configurations the kernel backward does not cover (prefix rows): autograd statement
+                from .models.opt_autograd import make_fo_loss
+                fo_loss = make_fo_loss(self.model)
         self._dizo_seed_rng = np.random.RandomState(a.seed + 7919)
         self.dizo_trainer = DizoTrainerView(proj, self._next_pgm_batch,
                                             lambda: int(self._dizo_seed_rng.randint(1_000_000_000)), fo_loss)

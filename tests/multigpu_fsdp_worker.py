@@ -63,6 +63,23 @@ def main():
     al = torch.full_like(p_fs.gs.alpha, 0.9)
     l_fs, l_ref = fs.loss(b, Transform(alpha=al)).item(), ref.loss(b, Transform(alpha=al)).item()
     assert abs(l_fs - l_ref) < 2e-2, (l_fs, l_ref)
+    # first-order gamma search over the shards: the kernel backward with every weight (and theta - theta_0 of
+    # the k / v shards) assembled by pushes equals the replicated kernel backward on the same batch
+    from dizo_b200.models.gamma_grad import GammaGrad, supported
+    assert supported(fs)
+    g = torch.Generator(device=dev).manual_seed(11)
+    al = torch.rand(p_fs.n, device=dev, generator=g) * 0.5 + 0.6
+    lf, gf = GammaGrad(fs).loss_and_grad(b, al.clone())
+    lr_, gr = GammaGrad(ref).loss_and_grad(b, al.clone())
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    assert abs(lf.item() - lr_.item()) < 2e-2, (lf, lr_)
+    cos = torch.nn.functional.cosine_similarity(gf, gr, dim=0).item()
+    assert cos > 0.98 and 0.8 < (gf.norm() / gr.norm()).item() < 1.25, (cos, gf, gr)
+    p_fs.max_iters = 2
+    p_fs.search_fo(lambda: b)
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
     p_fs.search_zo(lambda: b, seed=1)
     torch.cuda.synchronize()
     _lib.check_device_errors()

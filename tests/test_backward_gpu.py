@@ -181,3 +181,39 @@ def test_gamma_grad_kernel_backward_matches_autograd(kind):
     cos = torch.nn.functional.cosine_similarity(grad, a.grad.float(), dim=0).item()
     assert cos > 0.98, (cos, grad, a.grad)
     assert _rel(grad, a.grad) < 0.2
+
+
+@pytest.mark.parametrize("variant", ["lora", "post_ln"])
+def test_gamma_grad_kernel_backward_other_layouts(variant):
+    """The kernel backward for LoRA (the adapter factors are the constrained tensors: rank-8 GEMMs)
+    and for the post-LayerNorm layout with project_in / project_out (opt-350m), against autograd."""
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import DiZOProjector
+    from dizo_b200.models.gamma_grad import GammaGrad, supported
+    from dizo_b200.models.opt import OPTModel, preset
+    from dizo_b200.models.opt_autograd import make_fo_loss
+
+    if variant == "lora":
+        cfg = preset("opt-125m", num_hidden_layers=4)
+        m = OPTModel(cfg, DEV, torch.bfloat16, mode="lora").init_random_fast(seed=0)
+        scale = 0.05
+    else:
+        cfg = preset("opt-350m", num_hidden_layers=4)
+        m = OPTModel(cfg, DEV, torch.bfloat16, mode="full").init_random_fast(seed=0)
+        scale = 0.02
+    assert supported(m)
+    proj = DiZOProjector(m)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    for n in m.arena.slot_names:
+        p = m.param(n)
+        p.add_((torch.randn(p.shape, device=DEV, generator=g) * scale).to(p.dtype))
+    b = synthetic_batch(0, 2, 160, cfg.vocab_size, seed=1, pad_left=17).to(DEV)
+    alpha = torch.rand(proj.n, device=DEV, generator=g) * 0.5 + 0.5
+    loss, grad = GammaGrad(m).loss_and_grad(b, alpha)
+    _sync_ok()
+    a = alpha.clone().requires_grad_(True)
+    ref_loss = make_fo_loss(m)(b, a)
+    ref_loss.backward()
+    assert abs(loss.item() - ref_loss.item()) < 3e-2 * max(1.0, abs(ref_loss.item()))
+    cos = torch.nn.functional.cosine_similarity(grad, a.grad.float(), dim=0).item()
+    assert cos > 0.97, (cos, grad, a.grad)

@@ -6,17 +6,26 @@ large_models/trainer.py:1554-1561): same knobs (``do_sample``, ``temperature``, 
 The prompt is one forward through the training kernels with the per-layer QKV activations
 captured as the cache; each new token then runs the same GEMM / LayerNorm kernels on a
 [batch, d] activation and a small attention over the cache.
+
+Sharded models decode without moving weights.  Tensor parallel: every rank keeps the K / V cache of
+its own heads, runs ``decode_attn_kernel`` on them and the row-reduced projections (out_proj, fc2)
+are summed with one small all-reduce each.  FSDP: every matrix is sharded by output rows, so a rank
+computes its slice of each projection from the replicated [batch, d] activation and the slices are
+all-gathered (a few KB per token); attention runs on the full heads on every rank.  All ranks of the
+group must call :func:`generate` together (same batch size); the stop test is agreed by all-reduce.
+Pipeline-parallel models are not decoded (candidate scoring and training cover them).
 """
 from __future__ import annotations
 
 from typing import List, Optional, Sequence
 
 import torch
+import torch.distributed as dist
 
 from ..ops import attention as attn_ops
 from ..ops import decode as decode_ops
 from ..ops import gemm, norm
-from .opt import _P, Batch, OPTModel, make_batch
+from .opt import _P, Batch, OPTModel, layer_prefix, make_batch
 
 
 def filter_logits(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] = None,
@@ -63,7 +72,10 @@ class _Decoder:
             self.k[i][:, :L].copy_(q3[:, :, d:2 * d])
             self.v[i][:, :L].copy_(q3[:, :, 2 * d:])
         self.len = L
-        return h[:, -1, :]                                       # left padded: last column is real
+        return _head_logits(m, h[:, -1, :])                      # left padded: last column is real
+
+    def all_done(self, done: torch.Tensor) -> bool:
+        return bool(done.all())
 
     def reorder(self, index: torch.Tensor) -> None:
         for i in range(len(self.k)):
@@ -71,7 +83,7 @@ class _Decoder:
             self.v[i] = self.v[i].index_select(0, index)
 
     def step(self, tokens: torch.Tensor, positions: torch.Tensor, pad_left: torch.Tensor) -> torch.Tensor:
-        """tokens, positions: int32 [B]; returns the new last hidden state [B, d]."""
+        """tokens, positions: int32 [B]; returns the next-token logits [B, V] (fp32)."""
         m, cfg = self.m, self.m.config
         d = cfg.hidden_size
         get = m._resolver(-1, None, None, 0)
@@ -100,7 +112,7 @@ class _Decoder:
             if not pre:
                 h = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
         self.len = t + 1
-        return h
+        return _head_logits(m, h)
 
 
 def _head_logits(model: OPTModel, h_last: torch.Tensor) -> torch.Tensor:
@@ -116,6 +128,141 @@ def _head_logits(model: OPTModel, h_last: torch.Tensor) -> torch.Tensor:
     return gemm.linear(x.contiguous(), table, out_dtype=torch.float32).float()
 
 
+
+
+def _bias_residual(part: torch.Tensor, bias: torch.Tensor, res: torch.Tensor) -> torch.Tensor:
+    return (part.float() + bias.float() + res.float()).to(res.dtype)
+
+
+class _TPDecoder(_Decoder):
+    """Tensor parallel: this rank's heads only; the activation [B, d] is replicated."""
+
+    def __init__(self, model, B: int, max_len: int):
+        self.m = model
+        cfg = model.config
+        dl = cfg.hidden_size // model.tp
+        dev, dt = model.device, model.dtype
+        self.k = [torch.zeros(B, max_len, dl, dtype=dt, device=dev) for _ in range(cfg.num_hidden_layers)]
+        self.v = [torch.zeros(B, max_len, dl, dtype=dt, device=dev) for _ in range(cfg.num_hidden_layers)]
+        self.len = 0
+        self.pad_extra = 0
+
+    def prefill(self, batch: Batch) -> torch.Tensor:
+        m = self.m
+        dl = m.config.hidden_size // m.tp
+        B, L = batch.input_ids.shape
+        m.kv_capture = []
+        try:
+            h = m.hidden_states(batch)                         # pads to whole 128-row tiles per rank
+        finally:
+            cap, m.kv_capture = m.kv_capture, None
+        Lp = m._row_map[1] if m._row_map is not None else L
+        for i, qkv in enumerate(cap):
+            q3 = qkv.view(-1, Lp, 3 * dl)[:B]
+            self.k[i][:, :Lp].copy_(q3[:, :, dl:2 * dl])
+            self.v[i][:, :Lp].copy_(q3[:, :, 2 * dl:])
+        self.len, self.pad_extra = Lp, Lp - L
+        rows = (torch.arange(B, device=h.device, dtype=torch.int32) * L + (L - 1))
+        x = m.final_rows(h, rows)                              # final LayerNorm applied, replicated
+        return gemm.linear(x.contiguous(), m.lm_head_weight(), out_dtype=torch.float32).float()
+
+    def step(self, tokens, positions, pad_left) -> torch.Tensor:
+        m, cfg = self.m, self.m.config
+        d, n = cfg.hidden_size, m.tp
+        dl = d // n
+        get = m._resolver(-1, None, None, 0)
+        h = norm.embed(tokens.view(-1, 1), positions.view(-1, 1), get(_P + "embed_tokens.weight"),
+                       get(_P + "embed_positions.weight")).view(-1, d)
+        t = self.len
+        pl = pad_left + self.pad_extra
+        for i in range(cfg.num_hidden_layers):
+            w = m._layer_weights(i, m._resolver(i, None, None, 0))
+            x = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
+            qkv = gemm.linear(x, w.qkv_w, w.qkv_b)                            # [B, 3 d/n]: own heads
+            self.k[i][:, t].copy_(qkv[:, dl:2 * dl])
+            self.v[i][:, t].copy_(qkv[:, 2 * dl:])
+            ctx = decode_ops.decode_attention(qkv[:, :dl], self.k[i], self.v[i], t + 1,
+                                              cfg.num_attention_heads // n, pl)
+            part = gemm.linear(ctx.contiguous(), w.out_w, out_dtype=torch.float32)
+            dist.all_reduce(part, group=m.group)
+            h = _bias_residual(part, w.out_b, h)
+            x = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
+            f = gemm.linear(x, w.fc1_w, w.fc1_b, act=cfg.activation_function)
+            part = gemm.linear(f, w.fc2_w, out_dtype=torch.float32)
+            dist.all_reduce(part, group=m.group)
+            h = _bias_residual(part, w.fc2_b, h)
+        self.len = t + 1
+        return _head_logits(m, h)
+
+    def all_done(self, done: torch.Tensor) -> bool:
+        return bool(done.all())                                # every rank decodes the same batch
+
+
+class _FSDPDecoder(_Decoder):
+    """FSDP: weights sharded by output rows; a rank computes its slice of every projection from the
+    replicated activation and the slices are all-gathered."""
+
+    def _gathered(self, x: torch.Tensor, w_shard: torch.Tensor, bias=None, act=None, residual=None):
+        m = self.m
+        y = gemm.linear(x, w_shard)                                           # [B, out / n]
+        parts = torch.empty((m.n,) + tuple(y.shape), dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(parts, y.contiguous(), group=m.group)
+        full = parts.permute(1, 0, 2).reshape(y.shape[0], -1).float()
+        if bias is not None:
+            full = full + bias.float()
+        if act == "relu":
+            full = torch.relu(full)
+        elif act == "gelu":
+            full = torch.nn.functional.gelu(full)
+        if residual is not None:
+            full = full + residual.float()
+        return full.to(x.dtype)
+
+    def step(self, tokens, positions, pad_left) -> torch.Tensor:
+        m, cfg = self.m, self.m.config
+        d = cfg.hidden_size
+        get = m._resolver(-1, None, None, 0)
+        h = norm.embed(tokens.view(-1, 1), positions.view(-1, 1), get(_P + "embed_tokens.weight"),
+                       get(_P + "embed_positions.weight")).view(-1, d)
+        t = self.len
+        for i in range(cfg.num_hidden_layers):
+            g = m._resolver(i, None, None, 0)
+            lp = layer_prefix(i)
+            a = lp + "self_attn."
+            x = norm.layernorm(h, g(lp + "self_attn_layer_norm.weight"), g(lp + "self_attn_layer_norm.bias"),
+                               cfg.layer_norm_eps)
+            q = self._gathered(x, g(a + "q_proj.weight"), g(a + "q_proj.bias"))
+            k = self._gathered(x, g(a + "k_proj.weight"), g(a + "k_proj.bias"))
+            v = self._gathered(x, g(a + "v_proj.weight"), g(a + "v_proj.bias"))
+            self.k[i][:, t].copy_(k)
+            self.v[i][:, t].copy_(v)
+            ctx = decode_ops.decode_attention(q, self.k[i], self.v[i], t + 1, cfg.num_attention_heads, pad_left)
+            h = self._gathered(ctx.contiguous(), g(a + "out_proj.weight"), g(a + "out_proj.bias"), residual=h)
+            x = norm.layernorm(h, g(lp + "final_layer_norm.weight"), g(lp + "final_layer_norm.bias"),
+                               cfg.layer_norm_eps)
+            f = self._gathered(x, g(lp + "fc1.weight"), g(lp + "fc1.bias"), act=cfg.activation_function)
+            h = self._gathered(f, g(lp + "fc2.weight"), g(lp + "fc2.bias"), residual=h)
+        self.len = t + 1
+        return _head_logits(m, h)
+
+    def all_done(self, done: torch.Tensor) -> bool:
+        flag = done.all().to(torch.int32).reshape(1)           # ranks decode different batches: agree on the stop
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.m.group)
+        return bool(flag.item())
+
+
+def _make_decoder(model, B: int, max_len: int) -> _Decoder:
+    kind = type(model).__name__
+    if type(model).hidden_states is OPTModel.hidden_states:
+        return _Decoder(model, B, max_len)
+    if kind in ("TPOPTModel", "TPCompositionModel"):
+        return _TPDecoder(model, B, max_len)
+    if kind in ("FSDPOPTModel", "FSDPCompositionModel"):
+        return _FSDPDecoder(model, B, max_len)
+    raise NotImplementedError("autoregressive decoding covers replicated, tensor-parallel and FSDP models; "
+                              "pipeline-parallel models are scored and trained only")
+
+
 @torch.no_grad()
 def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
              max_new_tokens: int = 50, do_sample: bool = False, temperature: float = 1.0,
@@ -126,9 +273,6 @@ def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[
     which is kept, as Hugging Face does).  ``transform`` is accepted for API symmetry and must
     be None: perturb in place around the call when decoding under a perturbation."""
     assert transform is None, "decode under a perturbation by perturbing in place around generate()"
-    if type(model).hidden_states is not OPTModel.hidden_states:
-        raise NotImplementedError("autoregressive decoding runs on replicated parameters; the tensor-parallel, "
-                                  "FSDP and pipeline layouts cover training and candidate scoring only")
     dev = model.device
     ids = torch.as_tensor(input_ids).long()
     B0, L0 = ids.shape
@@ -141,8 +285,8 @@ def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[
         mask = mask.repeat_interleave(nb, 0)
     B = ids.shape[0]
     batch = make_batch(ids, mask).to(dev)
-    dec = _Decoder(model, B, L0 + max_new_tokens)
-    h_last = dec.prefill(batch)
+    dec = _make_decoder(model, B, L0 + max_new_tokens + 128)   # + room for the tile padding of sharded prefill
+    logits = dec.prefill(batch)
     n_real = mask.sum(dim=1).to(dev)
     pad_left = batch.pad_left
     gen = torch.Generator(device=dev)
@@ -154,7 +298,6 @@ def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[
     if nb > 1:
         beam_score.view(B0, nb)[:, 1:] = float("-inf")            # identical beams at step 0
     for t in range(max_new_tokens):
-        logits = _head_logits(model, h_last)
         if nb == 1:
             if do_sample and dev.type != "cuda":
                 probs = torch.softmax(filter_logits(logits, temperature, top_k, top_p), dim=-1)
@@ -185,11 +328,11 @@ def generate(model: OPTModel, input_ids: torch.Tensor, attention_mask: Optional[
             if not dl[i]:
                 out[i].append(toks[i])
         done = done | torch.tensor([tk in eos for tk in toks], dtype=torch.bool, device=dev)
-        if bool(done.all()) or t + 1 == max_new_tokens:
+        if dec.all_done(done) or t + 1 == max_new_tokens:
             break
         pos = (n_real + 2).to(torch.int32)                         # OPT positions: index + 2
         n_real = n_real + 1
-        h_last = dec.step(nxt.to(torch.int32), pos, pad_left)
+        logits = dec.step(nxt.to(torch.int32), pos, pad_left)
     if nb > 1:
         best = beam_score.view(B0, nb).argmax(dim=-1) + torch.arange(B0, device=dev) * nb
         out = [out[i] for i in best.tolist()]

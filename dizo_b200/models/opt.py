@@ -260,6 +260,8 @@ class OPTModel:
         self._staging: dict = {}
         self._side = None
         self._merge_buf: dict = {}
+        # LoRA: k_proj.weight is frozen, so its copy inside a layer's merged QKV operand stays valid
+        self._k_frozen = self.use_lora
         self.kv_capture: list | None = None      # set to [] to record per-layer qkv (generation)
 
     # ------------------------------------------------------------------ sharding hooks
@@ -336,6 +338,7 @@ class OPTModel:
             t.copy_(self.local_slice(n, v).to(self.dtype))
         if self.untied and "lm_head.weight" in self._where:
             self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
+        self._merge_buf = {}                     # cached merged operands hold copies of frozen weights
         return self
 
     @torch.no_grad()
@@ -362,6 +365,7 @@ class OPTModel:
                     flat[s:e].copy_((torch.randn(e - s, generator=g, device=self.device) * std).to(self.dtype))
         if self.untied and "lm_head.weight" in self._where:
             self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
+        self._merge_buf = {}                     # cached merged operands hold copies of frozen weights
         return self
 
     def state_dict(self) -> dict[str, torch.Tensor]:
@@ -390,6 +394,7 @@ class OPTModel:
                         raise KeyError(f"state dict lacks {n}")
                     continue
             self.param(n).copy_(self.local_slice(n, src).to(self.dtype))
+        self._merge_buf = {}                     # cached merged operands hold copies of frozen weights
         return missing
 
     # ------------------------------------------------------------------ weight resolution
@@ -465,6 +470,29 @@ class OPTModel:
                          small=small)
         return self.arena.span(lo, hi)[0]
 
+    def _lora_qkv_buffer(self, i: int) -> tuple[torch.Tensor, bool]:
+        """The [3d, d] operand that receives W_q + s B_q A_q | W_k | W_v + s B_v A_v of layer ``i`` and
+        whether its k section still has to be written.  With room to spare every layer keeps its own
+        buffer, so the frozen k weight is copied once and only q and v are re-merged per forward; when
+        memory is short one buffer is shared and k is copied along every time."""
+        d = self.config.hidden_size
+        if self._merge_buf.get("per_layer") is None:
+            need = self.config.num_hidden_layers * 3 * d * d * torch.finfo(self.dtype).bits // 8
+            free = torch.cuda.mem_get_info(self.device)[0] if self.device.type == "cuda" else 1 << 62
+            self._merge_buf["per_layer"] = free > 4 * need
+        if self._merge_buf["per_layer"]:
+            buf = self._merge_buf.get(i)
+            if buf is None:
+                buf = torch.empty((3 * d, d), dtype=self.dtype, device=self.device)
+                self._merge_buf[i] = buf
+                return buf, True
+            return buf, not self._k_frozen
+        buf = self._merge_buf.get("qkv")
+        if buf is None:
+            buf = torch.empty((3 * d, d), dtype=self.dtype, device=self.device)
+            self._merge_buf["qkv"] = buf
+        return buf, True
+
     def _layer_weights(self, i: int, get: Callable[[str], torch.Tensor]) -> SimpleNamespace:
         lp = layer_prefix(i)
         a = lp + "self_attn."
@@ -472,13 +500,12 @@ class OPTModel:
         qw, kw, vw = get(a + "q_proj.weight"), get(a + "k_proj.weight"), get(a + "v_proj.weight")
         if self.use_lora:
             d = self.config.hidden_size
-            buf = self._merge_buf.get("qkv")
-            if buf is None:
-                buf = torch.empty((3 * d, d), dtype=self.dtype, device=self.device)
-                self._merge_buf["qkv"] = buf
+            buf, fresh = self._lora_qkv_buffer(i)
             peft_ops.lora_merge(qw, get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"),
                                 self.lora_scaling, out=buf[:d])
-            buf[d:2 * d].copy_(kw)
+            if fresh:
+                # the frozen k weight: copied by the merge kernel with a zero scale (W + 0 * B A)
+                peft_ops.lora_merge(kw, get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"), 0.0, out=buf[d:2 * d])
             peft_ops.lora_merge(vw, get(a + "v_proj.lora_A"), get(a + "v_proj.lora_B"),
                                 self.lora_scaling, out=buf[2 * d:])
             w.qkv_w = buf

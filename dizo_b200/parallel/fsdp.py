@@ -197,6 +197,8 @@ class FSDPOPTModel(OPTModel):
             p, N2, rps2, per2 = push_of(i, "out", get)
             slot2, qkv = fc.fsdp_launch(push=p, gemm=dict(slot=pending[0], N=pending[1], x=x, bias=qkv_b,
                                                           rows_per_src=pending[2], src_period=pending[3]))
+            if self.kv_capture is not None:
+                self.kv_capture.append(qkv)                                  # generation: the prompt's K / V
             ctx = attn_ops.attention(qkv.view(B, L, 3 * d), cfg.num_attention_heads, batch.pad_left)
             # GEMM out_proj (+bias +residual) + push fc1
             p, N3, rps3, per3 = push_of(i, "fc1", get)

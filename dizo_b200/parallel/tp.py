@@ -170,6 +170,8 @@ class TPOPTModel(OPTModel):
                 nxt = stage(i + 1)
                 nxt_w = self._layer_weights(i + 1, self._resolver(i + 1, transform, *nxt))
             qkv = fc.ag_gemm(x_full, w.qkv_w, w.qkv_b)                       # [M, 3 d/n]
+            if self.kv_capture is not None:
+                self.kv_capture.append(qkv)                                  # this rank's heads (generation)
             ctx = attn_ops.attention(qkv.view(B, L, qkv.shape[1]), cfg.num_attention_heads // n,
                                      batch.pad_left)
             idx = fc.gemm_rs(ctx.view(M, d // n), w.out_w)

@@ -39,6 +39,27 @@ def main():
         # same perturbed bits, same GEMM tiles up to the kernel variant: the two sharded arms agree closely
         assert abs(l_fs - l_comp) < 5e-3, (t, l_fs, l_comp)
     del comp
+    # autoregressive decoding without moving weights: next-token logits of the prompt and of two more
+    # steps against the replicated model, then a whole generate() call
+    from dizo_b200.models.generate import _make_decoder, generate
+    from dizo_b200.models.opt import make_batch
+    gen = torch.Generator().manual_seed(5)
+    ids = torch.randint(4, cfg.vocab_size, (3, 37), generator=gen)
+    mask = torch.ones_like(ids)
+    mask[1, :9] = 0
+    ids[1, :9] = 1
+    gb = make_batch(ids, mask).to(dev)
+    d_sh, d_ref = _make_decoder(fs, 3, 37 + 8 + 128), _make_decoder(ref, 3, 37 + 8 + 128)
+    l_sh, l_ref = d_sh.prefill(gb), d_ref.prefill(gb)
+    n_real = mask.sum(1).to(dev)
+    for stepi in range(3):
+        assert (l_sh - l_ref).abs().max().item() < 0.15, (stepi, (l_sh - l_ref).abs().max().item())
+        nxt = l_ref.argmax(-1).to(torch.int32)
+        pos = (n_real + 2).to(torch.int32)
+        n_real = n_real + 1
+        l_sh, l_ref = d_sh.step(nxt, pos, gb.pad_left), d_ref.step(nxt, pos, gb.pad_left)
+    out = generate(fs, ids, attention_mask=mask, max_new_tokens=6, eos_token_id=[2])
+    assert len(out) == 3 and all(len(o) >= int(m.sum()) + 1 for o, m in zip(out, mask))
     # data-parallel ZO steps over sharded parameters: g is all-reduced, shards updated locally
     e_fs = ZOEngine(fs, eps=1e-2)
     for step in range(3):

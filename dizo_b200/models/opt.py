@@ -129,7 +129,12 @@ def base_param_specs(cfg: OPTConfig) -> list[tuple[str, tuple, int]]:
     return specs
 
 
-def adapter_param_specs(cfg: OPTConfig, lora_r: int, num_prefix: int) -> list[tuple[str, tuple, int]]:
+def adapter_param_specs(cfg: OPTConfig, lora_r: int, num_prefix: int, reparam: bool = False,
+                        embed_dim: int = 512, mid_dim: int = 512) -> list[tuple[str, tuple, int]]:
+    """LoRA factors and prefix tensors.  With ``reparam`` the prefix rows are not parameters but the
+    output of a per-layer two-layer MLP over shared input embeddings (large_models/prefix.py:177-197):
+    ``prefix_input_embeds`` [P, embed_dim] lives with layer 0, every layer owns ``prefix_mlp_keys`` and
+    ``prefix_mlp_values`` (Linear(embed, mid) - tanh - Linear(mid, d), names as ``nn.Sequential`` gives)."""
     d = cfg.hidden_size
     specs = []
     for i in range(cfg.num_hidden_layers):
@@ -138,9 +143,17 @@ def adapter_param_specs(cfg: OPTConfig, lora_r: int, num_prefix: int) -> list[tu
             for proj in ("q_proj", "v_proj"):
                 specs += [(f"{lp}self_attn.{proj}.lora_A", (lora_r, d), i),
                           (f"{lp}self_attn.{proj}.lora_B", (d, lora_r), i)]
-        if num_prefix:
+        if num_prefix and not reparam:
             specs += [(lp + "self_attn.prefix_keys", (num_prefix, d), i),
                       (lp + "self_attn.prefix_values", (num_prefix, d), i)]
+        if num_prefix and reparam:
+            if i == 0:
+                specs.append((lp + "self_attn.prefix_input_embeds", (num_prefix, embed_dim), i))
+            for kv in ("keys", "values"):
+                specs += [(f"{lp}self_attn.prefix_mlp_{kv}.0.weight", (mid_dim, embed_dim), i),
+                          (f"{lp}self_attn.prefix_mlp_{kv}.0.bias", (mid_dim,), i),
+                          (f"{lp}self_attn.prefix_mlp_{kv}.2.weight", (d, mid_dim), i),
+                          (f"{lp}self_attn.prefix_mlp_{kv}.2.bias", (d,), i)]
     return specs
 
 
@@ -153,7 +166,9 @@ _LAYER_ORDER = ["self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn
                 "final_layer_norm.weight", "final_layer_norm.bias",
                 "self_attn.q_proj.lora_A", "self_attn.q_proj.lora_B",
                 "self_attn.v_proj.lora_A", "self_attn.v_proj.lora_B",
-                "self_attn.prefix_keys", "self_attn.prefix_values"]
+                "self_attn.prefix_keys", "self_attn.prefix_values", "self_attn.prefix_input_embeds"] + \
+               [f"self_attn.prefix_mlp_{kv}.{j}.{wb}" for kv in ("keys", "values") for j in (0, 2)
+                for wb in ("weight", "bias")]
 
 
 def _arena_sort_key(name: str, group: int):
@@ -218,7 +233,8 @@ class OPTModel:
 
     def __init__(self, config: OPTConfig, device="cpu", dtype=torch.float32, mode: str = "full",
                  lora_r: int = 8, lora_alpha: int = 16, num_prefix: int = 5, untie_emb: bool = False,
-                 overlap_transform: bool = False):
+                 overlap_transform: bool = False, prefix_reparam: bool = False, prefix_embed_dim: int = 512,
+                 prefix_mid_dim: int = 512):
         self.config = config
         self.device = torch.device(device)
         self.dtype = dtype
@@ -228,6 +244,7 @@ class OPTModel:
         self.lora_r = lora_r if self.use_lora else 0
         self.lora_scaling = (lora_alpha / lora_r) if self.use_lora else 0.0
         self.num_prefix = num_prefix if self.use_prefix else 0
+        self.prefix_reparam = bool(prefix_reparam) and self.use_prefix
         self.untied = untie_emb or mode == "head" or not config.tie_word_embeddings
         self.overlap_transform = overlap_transform and self.device.type == "cuda"
 
@@ -235,10 +252,13 @@ class OPTModel:
         extra = []
         if self.untied:
             extra.append(("lm_head.weight", (config.vocab_size, config.word_embed_proj_dim), -1))
-        adapters = adapter_param_specs(config, self.lora_r, self.num_prefix)
-        # canonical RNG stream ids: independent of mode, sharding and arena order
+        adapters = adapter_param_specs(config, self.lora_r, self.num_prefix, self.prefix_reparam,
+                                       prefix_embed_dim, prefix_mid_dim)
+        # canonical RNG stream ids: independent of mode, sharding and arena order (new kinds of tensors
+        # are appended, so the ids of the existing ones never move)
         canon = [n for n, _, _ in base] + ["lm_head.weight"] + \
-                [n for n, _, _ in adapter_param_specs(config, 8, 5)]
+                [n for n, _, _ in adapter_param_specs(config, 8, 5)] + \
+                [n for n, _, _ in adapter_param_specs(config, 0, 5, True)]
         self.tensor_ids = {n: i for i, n in enumerate(canon)}
         self.all_specs = [sp for sp in base + extra + adapters if self.owns(sp[0])]
         self.hf_order = [n for n, _, _ in self.all_specs]
@@ -324,6 +344,9 @@ class OPTModel:
                 v = (torch.rand(shape, generator=g) * 2 - 1) * bound
             elif "lora_B" in n:
                 v = torch.zeros(shape)
+            elif "prefix_mlp_" in n:
+                fan_in = shape[1] if len(shape) == 2 else self._mlp_fan_in(n)
+                v = (torch.rand(shape, generator=g) * 2 - 1) * (1.0 / fan_in) ** 0.5     # nn.Linear's default
             elif "prefix_" in n:
                 v = torch.randn(shape, generator=g)
             elif "layer_norm.weight" in n:
@@ -347,7 +370,11 @@ class OPTModel:
         g = torch.Generator(device=self.device).manual_seed(seed)
         for n, shape, _ in self.all_specs:
             t = self.param(n)
-            if "lora_B" in n or n.endswith(".bias"):
+            if "prefix_mlp_" in n:
+                fan_in = shape[1] if len(shape) == 2 else self._mlp_fan_in(n)
+                t.copy_(((torch.rand(shape, generator=g, device=self.device) * 2 - 1) *
+                         (1.0 / fan_in) ** 0.5).to(self.dtype))
+            elif "lora_B" in n or n.endswith(".bias"):
                 t.zero_()
             elif "layer_norm.weight" in n:
                 t.fill_(1.0)
@@ -367,6 +394,9 @@ class OPTModel:
             self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
         self._merge_buf = {}                     # cached merged operands hold copies of frozen weights
         return self
+
+    def _mlp_fan_in(self, bias_name: str) -> int:
+        return self.param(bias_name[:-len("bias")] + "weight").shape[1]
 
     def state_dict(self) -> dict[str, torch.Tensor]:
         """Hugging Face OPT names (plus ``lora_A/B`` and ``prefix_keys/values``)."""
@@ -497,6 +527,10 @@ class OPTModel:
         lp = layer_prefix(i)
         a = lp + "self_attn."
         w = SimpleNamespace()
+        if self.use_prefix and self.prefix_reparam and i == 0:
+            # the shared embeddings are a tensor of layer 0: read them through layer 0's resolver (so a
+            # transform applies) and keep a copy for the layers above, whose staging buffers rotate
+            self._prefix_embeds = get(a + "prefix_input_embeds").clone()
         qw, kw, vw = get(a + "q_proj.weight"), get(a + "k_proj.weight"), get(a + "v_proj.weight")
         if self.use_lora:
             d = self.config.hidden_size
@@ -517,9 +551,18 @@ class OPTModel:
         w.fc1_w, w.fc1_b = get(lp + "fc1.weight"), get(lp + "fc1.bias")
         w.fc2_w, w.fc2_b = get(lp + "fc2.weight"), get(lp + "fc2.bias")
         w.ln2_w, w.ln2_b = get(lp + "final_layer_norm.weight"), get(lp + "final_layer_norm.bias")
-        w.prefix_k = get(a + "prefix_keys") if self.use_prefix else None
-        w.prefix_v = get(a + "prefix_values") if self.use_prefix else None
+        if self.use_prefix and self.prefix_reparam:
+            # prefix rows = MLP(shared input embeddings), recomputed from the (perturbed) MLP parameters
+            emb = self._prefix_embeds
+            w.prefix_k, w.prefix_v = (self._prefix_mlp(emb, a + f"prefix_mlp_{kv}.", get) for kv in ("keys", "values"))
+        else:
+            w.prefix_k = get(a + "prefix_keys") if self.use_prefix else None
+            w.prefix_v = get(a + "prefix_values") if self.use_prefix else None
         return w
+
+    def _prefix_mlp(self, emb: torch.Tensor, stem: str, get) -> torch.Tensor:
+        h = torch.tanh(gemm.linear(emb, get(stem + "0.weight"), get(stem + "0.bias")).float()).to(self.dtype)
+        return gemm.linear(h, get(stem + "2.weight"), get(stem + "2.bias"))
 
     # ------------------------------------------------------------------ forward
     def _layer_forward(self, h: torch.Tensor, w: SimpleNamespace, batch: Batch) -> torch.Tensor:

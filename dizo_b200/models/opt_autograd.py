@@ -86,8 +86,16 @@ def functional_loss(model: OPTModel, batch: Batch, weight_fn: Optional[Callable]
                 cfg.layer_norm_eps) if pre else h
         qkv = torch.cat([F.linear(x, qw, W(a + "q_proj.bias")), F.linear(x, kw, W(a + "k_proj.bias")),
                          F.linear(x, vw, W(a + "v_proj.bias"))], dim=-1)
-        pk = W(a + "prefix_keys") if model.use_prefix else None
-        pv = W(a + "prefix_values") if model.use_prefix else None
+        if model.use_prefix and model.prefix_reparam:
+            emb = W(layer_prefix(0) + "self_attn.prefix_input_embeds")
+
+            def mlp(stem):
+                mid = torch.tanh(F.linear(emb, W(stem + "0.weight"), W(stem + "0.bias")))
+                return F.linear(mid, W(stem + "2.weight"), W(stem + "2.bias"))
+            pk, pv = mlp(a + "prefix_mlp_keys."), mlp(a + "prefix_mlp_values.")
+        else:
+            pk = W(a + "prefix_keys") if model.use_prefix else None
+            pv = W(a + "prefix_values") if model.use_prefix else None
         ctx = _attention(qkv, cfg.num_attention_heads, batch.pad_left, pk, pv)
         h = h + F.linear(ctx, W(a + "out_proj.weight"), W(a + "out_proj.bias"))
         if not pre:

@@ -53,6 +53,7 @@ class PPOPTModel(OPTModel):
         self.lo, self.hi = stage_bounds(config.num_hidden_layers, self.n)[self.stage]
         self.micro_batches = micro_batches            # 0 = one micro-batch per stage
         assert config.word_embed_proj_dim == config.hidden_size, "project_in/out models are not staged"
+        assert not kw.get("prefix_reparam"), "the shared prefix embeddings live with the first block: not staged"
         super().__init__(config, device, dtype, **kw)
 
     # ------------------------------------------------------------------ ownership

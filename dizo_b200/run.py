@@ -140,7 +140,7 @@ class Framework:
                 assert a.enhanced != "fo", "the first-order gamma search is not staged over a pipeline"
                 from .parallel.pp import PPOPTModel
                 model = PPOPTModel(cfg, self.device, self._dtype(), micro_batches=a.pp_micro_batches, mode=mode,
-                                   lora_r=a.lora_r, lora_alpha=a.lora_alpha, num_prefix=a.num_prefix,
+                                   lora_r=a.lora_r, lora_alpha=a.lora_alpha, num_prefix=a.num_prefix, prefix_reparam=not a.no_reparam,
                                    untie_emb=a.untie_emb)
                 self.dp_group = False
             elif a.tp > 1 or a.fsdp_shard:
@@ -160,14 +160,14 @@ class Framework:
                     model = FSDPOPTModel(cfg, self.device, self._dtype(), untie_emb=a.untie_emb)
             else:
                 model = OPTModel(cfg, self.device, self._dtype(), mode=mode, lora_r=a.lora_r,
-                                 lora_alpha=a.lora_alpha, num_prefix=a.num_prefix, untie_emb=a.untie_emb)
+                                 lora_alpha=a.lora_alpha, num_prefix=a.num_prefix, prefix_reparam=not a.no_reparam, untie_emb=a.untie_emb)
             if state is not None:
                 model.init_random(a.seed)          # adapters; base weights are overwritten below
                 model.load_state_dict(state, strict=False)
             else:
                 (model.init_random_fast if self.device.type == "cuda" else model.init_random)(0)
         tokenizer = self._load_tokenizer(path, cfg)
-        if a.prefix_tuning and a.prefix_init_by_real_act:
+        if a.prefix_tuning and a.prefix_init_by_real_act and a.no_reparam:
             peft_wiring.init_prefix_by_real_activations(model, seed=a.seed)
         return model, tokenizer
 

@@ -1,0 +1,49 @@
+"""LoRALinear and the prefix re-parameterisation MLP on CPU (fp32) against plain PyTorch statements."""
+import torch
+
+from dizo_b200.data.synthetic import synthetic_batch
+from dizo_b200.engine import ZOEngine
+from dizo_b200.models.opt import OPTModel, Transform, layer_prefix, preset
+from dizo_b200.models.opt_autograd import functional_loss
+from dizo_b200.models.peft import LoRALinear, PrefixTuning
+
+
+def test_lora_linear_matches_the_reference_formula():
+    lin = LoRALinear(48, 32, r=4, lora_alpha=8, seed=1)
+    lin.lora_B.copy_(torch.randn(32, 4, generator=torch.Generator().manual_seed(2)) * 0.1)
+    x = torch.randn(5, 7, 48, generator=torch.Generator().manual_seed(3))
+    want = torch.nn.functional.linear(x, lin.weight, lin.bias) + (x @ lin.lora_A.t() @ lin.lora_B.t()) * lin.scaling
+    assert torch.allclose(lin(x), want, atol=1e-5)
+    w0 = lin.weight.clone()
+    lin.merge()
+    assert lin.merged and torch.allclose(lin(x), want, atol=1e-5)
+    lin.unmerge()
+    assert not lin.merged and torch.allclose(lin.weight, w0, atol=1e-6)
+    assert set(lin.trainable()) == {"lora_A", "lora_B"}
+    assert LoRALinear(8, 8).trainable() == {}
+
+
+def test_prefix_reparameterisation_mlp_trains_the_mlp_and_matches_autograd_forward():
+    cfg = preset("opt-tiny")
+    m = OPTModel(cfg, "cpu", torch.float32, mode="prefix", num_prefix=5, prefix_reparam=True,
+                 prefix_embed_dim=16, prefix_mid_dim=24).init_random(0)
+    pt = PrefixTuning(m, num_prefix=5, reparam=True, embed_dim=16, mid_dim=24, init_by_real_act=False)
+    names = set(pt.names)
+    assert layer_prefix(0) + "self_attn.prefix_input_embeds" in names
+    assert layer_prefix(1) + "self_attn.prefix_mlp_values.2.weight" in names
+    assert not any(n.endswith("prefix_keys") for n in names)
+    assert m.param(layer_prefix(1) + "self_attn.prefix_mlp_keys.0.weight").shape == (24, 16)
+    b = synthetic_batch(0, 3, 24, cfg.vocab_size, pad_left=4, cand_ids=(17, 29))
+    ref = functional_loss(m, b, use_checkpoint=False).item()
+    assert abs(m.loss(b).item() - ref) < 1e-4
+    # the perturbation reaches the loss through the MLP parameters
+    assert abs(m.loss(b, Transform(seed=3, coef=1e-2)).item() - ref) > 1e-6
+    eng = ZOEngine(m, eps=1e-3)
+    before = m.arena.data.clone()
+    eng.step(b, 1e-2, seed=5)
+    assert not torch.equal(before, m.arena.data)
+    sd = m.state_dict()
+    m2 = OPTModel(cfg, "cpu", torch.float32, mode="prefix", num_prefix=5, prefix_reparam=True,
+                  prefix_embed_dim=16, prefix_mid_dim=24).init_random(9)
+    m2.load_state_dict(sd)
+    assert abs(m2.loss(b).item() - m.loss(b).item()) < 1e-6

@@ -7,7 +7,11 @@ points taking raw device pointers and a ``cudaStream_t``; Python binds them with
 ``ctypes`` (see ``dizo_b200/ops/_lib.py``).  There is no JIT cache: the built ``.so``
 sits beside the sources, and a stale library (older than any source) is rebuilt.
 
-Run ``python -m dizo_b200.ops.build [--force] [--verbose]``.
+``--debug-bounds`` builds a second library, ``libdizo_b200_dbg.so``, with ``-DDZ_DEBUG_BOUNDS``: every
+global store of the instrumented kernels is checked against the address ranges the host registered and
+skipped (and recorded) when it falls outside them; ``DIZO_DEBUG_BOUNDS=1`` makes the package load it.
+
+Run ``python -m dizo_b200.ops.build [--force] [--verbose] [--debug-bounds]``.
 """
 from __future__ import annotations
 
@@ -24,6 +28,8 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD = HERE / "_build"
 LIB = HERE / "libdizo_b200.so"
+BUILD_DBG = HERE / "_build_dbg"
+LIB_DBG = HERE / "libdizo_b200_dbg.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -46,22 +52,22 @@ def _sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def _digest(src: Path) -> str:
+def _digest(src: Path, flags) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(flags).encode())
     h.update(src.read_bytes())
     for hdr in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(hdr.read_bytes())
     return h.hexdigest()[:16]
 
 
-def _compile_one(src: Path, verbose: bool) -> Path:
-    obj = BUILD / f"{src.stem}.{_digest(src)}.o"
+def _compile_one(src: Path, verbose: bool, build_dir: Path, flags) -> Path:
+    obj = build_dir / f"{src.stem}.{_digest(src, flags)}.o"
     if obj.exists():
         return obj
-    for old in BUILD.glob(f"{src.stem}.*.o"):
+    for old in build_dir.glob(f"{src.stem}.*.o"):
         old.unlink()
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -73,36 +79,45 @@ def _compile_one(src: Path, verbose: bool) -> Path:
     return obj
 
 
-def stale() -> bool:
-    if not LIB.exists():
+def _variant(debug_bounds: bool):
+    if debug_bounds:
+        return BUILD_DBG, LIB_DBG, NVCC_FLAGS + ["-DDZ_DEBUG_BOUNDS"]
+    return BUILD, LIB, NVCC_FLAGS
+
+
+def stale(debug_bounds: bool = False) -> bool:
+    build_dir, lib, flags = _variant(debug_bounds)
+    if not lib.exists():
         return True
-    stamp = BUILD / "link.stamp"
-    want = "\n".join(f"{s.stem}.{_digest(s)}" for s in _sources())
+    stamp = build_dir / "link.stamp"
+    want = "\n".join(f"{s.stem}.{_digest(s, flags)}" for s in _sources())
     return not stamp.exists() or stamp.read_text() != want
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
     """Compile every kernel for sm_100a and link the shared library. Returns its path."""
-    BUILD.mkdir(exist_ok=True)
+    build_dir, lib, flags = _variant(debug_bounds)
+    build_dir.mkdir(exist_ok=True)
     if force:
-        for old in BUILD.glob("*.o"):
+        for old in build_dir.glob("*.o"):
             old.unlink()
-    elif not stale():
-        return LIB
+    elif not stale(debug_bounds):
+        return lib
     srcs = _sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
-        objs = list(ex.map(lambda s: _compile_one(s, verbose), srcs))
-    cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs)]
+        objs = list(ex.map(lambda s: _compile_one(s, verbose, build_dir, flags), srcs))
+    cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    (BUILD / "link.stamp").write_text("\n".join(f"{s.stem}.{_digest(s)}" for s in srcs))
-    return LIB
+    (build_dir / "link.stamp").write_text("\n".join(f"{s.stem}.{_digest(s, flags)}" for s in srcs))
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/smem usage")
+    ap.add_argument("--debug-bounds", action="store_true", help="build the checked-store library instead")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, debug_bounds=a.debug_bounds))

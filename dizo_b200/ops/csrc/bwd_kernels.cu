@@ -91,7 +91,8 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy, const
     uint4 r;
     r.x = pack_bf16x2(o[0], o[1]); r.y = pack_bf16x2(o[2], o[3]);
     r.z = pack_bf16x2(o[4], o[5]); r.w = pack_bf16x2(o[6], o[7]);
-    *reinterpret_cast<uint4*>(dx + row * lddx + i * 8) = r;
+    uint4* dp = reinterpret_cast<uint4*>(dx + row * lddx + i * 8);
+    if (DZ_STORE_OK(dp, 16)) *dp = r;
   }
 }
 
@@ -113,7 +114,7 @@ softmax_ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const f
     for (int j = 0; j < 8; ++j) e[j] = c * ((j0 + j == t ? 1.f : 0.f) - __expf(e[j] - l));
     v.x = pack_bf16x2(e[0], e[1]); v.y = pack_bf16x2(e[2], e[3]);
     v.z = pack_bf16x2(e[4], e[5]); v.w = pack_bf16x2(e[6], e[7]);
-    *reinterpret_cast<uint4*>(lr + j0) = v;
+    if (DZ_STORE_OK(lr + j0, 16)) *reinterpret_cast<uint4*>(lr + j0) = v;
   } else {
     for (int j = j0; j < V; ++j)
       lr[j] = __float2bfloat16(c * ((j == t ? 1.f : 0.f) - __expf(__bfloat162float(lr[j]) - l)));
@@ -160,7 +161,8 @@ __global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, long 
   const long long t = idx[r];
   if (t < 0 || t >= n_dst) return;
   for (int i = threadIdx.x; i < (d >> 3); i += blockDim.x)
-    *reinterpret_cast<uint4*>(dst + t * ldd + i * 8) = *reinterpret_cast<const uint4*>(src + r * lds + i * 8);
+    if (DZ_STORE_OK(dst + t * ldd + i * 8, 16))
+      *reinterpret_cast<uint4*>(dst + t * ldd + i * 8) = *reinterpret_cast<const uint4*>(src + r * lds + i * 8);
 }
 
 __global__ void diff_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
@@ -174,7 +176,7 @@ __global__ void diff_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bflo
     r.y = pack_bf16x2(bf16_lo(x.y) - bf16_lo(y.y), bf16_hi(x.y) - bf16_hi(y.y));
     r.z = pack_bf16x2(bf16_lo(x.z) - bf16_lo(y.z), bf16_hi(x.z) - bf16_hi(y.z));
     r.w = pack_bf16x2(bf16_lo(x.w) - bf16_lo(y.w), bf16_hi(x.w) - bf16_hi(y.w));
-    *reinterpret_cast<uint4*>(out + i * 8) = r;
+    if (DZ_STORE_OK(out + i * 8, 16)) *reinterpret_cast<uint4*>(out + i * 8) = r;
   }
 }
 
@@ -183,6 +185,7 @@ static inline bool bk_al16(const void* p) { return (reinterpret_cast<uintptr_t>(
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(bwd)
 
 // dx[rows, d] = LayerNorm input gradient for output gradient dy and input x (+ add when given).
 extern "C" int dz_layernorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const void* w,

@@ -3,16 +3,20 @@
 //   out = epilogue( A[M,K] * W[N,K]^T )       tcgen05 / TMEM / TMA, as gemm_sm100.cu
 //
 // plus any of
-//   * PUSH role (four extra warps in EVERY CTA): copy a block of local rows into every peer's
+//   * PUSH role (four extra warps in the first n_push CTAs): copy a block of local rows into every peer's
 //     staging buffer with plain posted stores (all-gather by push), optionally transforming it on
 //     the way: theta + c * z(seed) regenerated from Philox for the pushed shard (FSDP parameter
 //     all-gather fused with the perturbation - the owner perturbs its shard once, nobody
 //     materialises z).  The push warps of CTA b move slice b of the rows while the producer, MMA
 //     and epilogue warps of the same CTA run GEMM tiles: a tcgen05 GEMM leaves the issue slots and
 //     the load/store path of its SM almost idle, so the transfer rides along without taking SMs
-//     away from the tensor-core work (dedicating whole CTAs to it cost 16 of 148 SMs).  When a
-//     CTA has pushed its slice it fences at system scope; the last one raises the `ready` flag of
-//     this rank at every peer.
+//     away from the tensor-core work (dedicating whole CTAs to it cost 16 of 148 SMs).  How many
+//     CTAs push is the host's choice per launch, from the bytes to move and the time the GEMM
+//     gives them: posted stores from all 148 SMs saturate NVLink within a fraction of the launch
+//     and the back-pressure then stalls the TMA loads of every GEMM (measured on 8 GPUs), so the
+//     rate is held near what the transfer needs, and the pushing CTAs take a smaller share of the
+//     tiles (`join_tiles`, at the end of the tile order).  When a CTA has pushed its slice it
+//     fences at system scope; the last one raises the `ready` flag of this rank at every peer.
 //   * GATHERED OPERAND: rows of A (tensor parallel: sequence-sharded activations) or of W
 //     (FSDP: row-sharded weights) arrive from peers in this rank's staging buffer; the TMA
 //     producer polls the source rank's `ready` flag (bounded) before its first load of rows
@@ -76,6 +80,7 @@ struct CommGemmArgs {
                                  // (fused q|k|v: d); 0 = no repetition
   int wait_self;                 // own rows are also produced by this launch's push role
   int chunk_tiles;               // gather 1: row tiles per progress chunk of a source (0 = one chunk)
+  int join_tiles;                // tiles at the end of the order that the pushing CTAs multiply
   const uint32_t* ready_flags;   // local [world][CG_MAXC]: flag[s][c] >= ready_epoch once rank s has
                                  // pushed chunk c of its rows (unchunked pushes use c = 0 only)
   uint32_t ready_epoch;
@@ -90,7 +95,7 @@ struct CommGemmArgs {
   uint32_t* const* rs_flag_ptrs; // per rank: its [world] "partials ready" words
   uint32_t rs_epoch;
   // ---- push role
-  int n_push;                    // > 0: this launch pushes (every CTA's push warps take one slice)
+  int n_push;                    // CTAs whose push warps are active (the first n_push; 0 = no push)
   int push_nseg;                 // 1..3 row segments of equal shape (e.g. the q, k, v shards)
   const __nv_bfloat16* push_src[3]; // local rows [push_rows, push_cols], row stride push_ld
   long long push_ld;
@@ -191,9 +196,9 @@ __device__ __forceinline__ void cg_push_sync() {
 }
 
 // Executed by the CG_PUSH_THREADS push threads of every CTA; `pt` is the thread's index among them,
-// slice `blockIdx.x` of `gridDim.x` equal slices of the rows is this CTA's share.
+// slice `blockIdx.x` of `n_push` equal slices of the rows is this CTA's share.
 __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* table_smem, const int pt) {
-  const int n_slices = (int)gridDim.x;
+  const int n_slices = p.n_push;
   __shared__ int s_go;
   __shared__ int s_first_idle;     // first chunk counter this launch leaves untouched
   // stage the inverse-CDF table when the pushed rows are perturbed
@@ -255,7 +260,7 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* tab
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]);
 #pragma unroll
             for (int u = 0; u < CG_PUSH_UNROLL; ++u)
-              if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
+              if (live[u] && DZ_STORE_OK(dst + doff[u], 16)) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
           }
         }
         __threadfence_system();
@@ -312,7 +317,7 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* tab
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.push_dst_ptrs[d]);
 #pragma unroll
         for (int u = 0; u < CG_PUSH_UNROLL; ++u)
-          if (live[u]) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
+          if (live[u] && DZ_STORE_OK(dst + doff[u], 16)) *reinterpret_cast<uint4*>(dst + doff[u]) = raw[u];
       }
     }
     }
@@ -348,9 +353,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int num_tiles = p.num_m * p.num_n;
   const int num_kb = (p.K + CG_BK - 1) / CG_BK;
-  const int cta = (int)blockIdx.x;
-  const int n_cta = (int)gridDim.x;
-  const int tile_end = num_tiles;
+  // CTAs that also push take the last join_tiles tiles of the order, the others the rest
+  const bool pusher = (int)blockIdx.x < p.n_push;
+  const bool split = p.n_push > 0 && p.n_push < (int)gridDim.x && p.join_tiles > 0;
+  const int reg_tiles = split ? num_tiles - p.join_tiles : num_tiles;
+  const int cta = !split ? (int)blockIdx.x : (pusher ? reg_tiles + (int)blockIdx.x : (int)blockIdx.x - p.n_push);
+  const int n_cta = !split ? (int)gridDim.x : (pusher ? p.n_push : (int)gridDim.x - p.n_push);
+  const int tile_end = (split && !pusher) ? reg_tiles : num_tiles;
   // the table of the push warps sits behind the operand ring (where a push epilogue stages its rows)
   uint8_t* table_smem = smem_raw + ((smem_base - smem_u32(smem_raw)) + CG_STAGES * CG_STAGE_BYTES);
 
@@ -381,7 +390,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp >= CG_GEMM_THREADS / 32) {
     // ------------------------------------------------------------ push warps
-    if (p.n_push > 0) cg_push_role(p, table_smem, (int)threadIdx.x - CG_GEMM_THREADS);
+    if (pusher) cg_push_role(p, table_smem, (int)threadIdx.x - CG_GEMM_THREADS);
   } else if (warp == 0) {
     if (elect_one()) {
       int stage = 0;
@@ -536,7 +545,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (orow_f32) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (full_chunk || col0 + j < p.N) orow_f32[col0 + j] = v[j];
+              if ((full_chunk || col0 + j < p.N) && DZ_STORE_OK(orow_f32 + col0 + j, 4)) orow_f32[col0 + j] = v[j];
           } else if (p.push_out) {
             // stage this warp's 32 rows x 128 columns (one half of the tile's width) in its own
             // shared-memory block, 16-byte units XOR-swizzled by the row against bank conflicts
@@ -558,12 +567,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
               o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
               o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              op4[q] = o;
+              if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) orow_bf[col0 + j] = __float2bfloat16(v[j]);
+              if (col0 + j < p.N && DZ_STORE_OK(orow_bf + col0 + j, 2)) orow_bf[col0 + j] = __float2bfloat16(v[j]);
           }
         }
         }
@@ -588,7 +597,8 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               uint4 o;
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                            : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(addr) : "memory");
-              *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + unit * 8) = o;
+              if (DZ_STORE_OK(obase + (long long)rr * p.ldo + unit * 8, 16))
+                *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + unit * 8) = o;
             }
           }
           __syncwarp();
@@ -631,6 +641,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(commgemm)
 
 // Plain-C mirror of the launch description (filled by Python through ctypes).
 struct DzCommGemmDesc {
@@ -655,18 +666,22 @@ struct DzCommGemmDesc {
   int rank, world; void* counters; unsigned int push_target, gemm_target;
   int gemm_ctas;                 // (unused)
   int chunk_rows;                // all-gather -> GEMM: rows per progress chunk of a source (0 = one chunk)
-  int join_tiles;                // (unused)
+  int join_tiles;                // tiles at the end of the order left to the pushing CTAs (0 = no split)
 };
 
 extern "C" int dz_comm_gemm_desc_bytes() { return (int)sizeof(DzCommGemmDesc); }
 
-// CTAs of a launch of this shape: one per SM when it pushes (every CTA carries a slice of the push),
-// otherwise one per output tile up to the SM count.  The host keeps its completion counters in step with it.
-extern "C" int dz_comm_gemm_grid(int M, int N, int pushes) {
+// CTAs of a launch of this shape with n_push pushing CTAs: one per output tile up to the SM count, and
+// at least the pushing ones.  The host keeps its completion counters in step with it.
+extern "C" int dz_comm_gemm_grid(int M, int N, int n_push) {
   const int sms = sm_count();
-  if (pushes) return sms;
   const long long tiles = (long long)((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
-  return (int)(tiles < sms ? tiles : sms);
+  long long g = tiles < sms ? tiles : sms;
+  if (n_push > g) g = n_push < sms ? n_push : sms;
+  return (int)g;
+}
+extern "C" int dz_comm_gemm_tiles(int M, int N) {
+  return ((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
 }
 
 extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t stream) {
@@ -715,6 +730,7 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.out_slot_stride = d->out_slot_stride; a.rows_per_owner = d->rows_per_owner;
   a.rs_flag_ptrs = (uint32_t* const*)d->rs_flag_ptrs; a.rs_epoch = d->rs_epoch;
   a.n_push = d->n_push > 0 ? d->n_push : 0;
+  if (a.n_push > sm_count()) a.n_push = sm_count();
   a.push_nseg = d->push_nseg;
   for (int sgi = 0; sgi < 3; ++sgi) {
     a.push_src[sgi] = (const __nv_bfloat16*)d->push_src[sgi];
@@ -746,8 +762,13 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   static PerDeviceFlag configured;
   if (int rc_cfg = ensure_dyn_smem(configured, comm_gemm_kernel<CG_STAGES_PUSH>, CG_SMEM_PUSH)) return rc_cfg;
   // one CTA per SM at most: every CTA must be resident at once (the roles wait on one another through flags)
-  const int grid = dz_comm_gemm_grid(has_gemm ? d->M : 0, has_gemm ? d->N : 0, a.n_push > 0);
-  if (grid < 1 || grid > sm_count()) return DZ_ERR_TOO_LARGE;
+  const int grid = dz_comm_gemm_grid(has_gemm ? d->M : 0, has_gemm ? d->N : 0, a.n_push);
+  if (grid < 1 || grid > sm_count() || a.n_push > grid) return DZ_ERR_TOO_LARGE;
+  if (has_gemm && a.n_push > 0 && a.n_push < grid && d->join_tiles > 0) {
+    // without a split (join_tiles 0) when the pushing CTAs are left no tile, every CTA strides over all tiles
+    if (d->join_tiles >= a.num_m * a.num_n) return DZ_ERR_ARG;
+    a.join_tiles = d->join_tiles;
+  }
   if (a.push_out)
     comm_gemm_kernel<CG_STAGES_PUSH><<<grid, CG_THREADS, CG_SMEM_PUSH, stream>>>(tmA, tmB, a);
   else

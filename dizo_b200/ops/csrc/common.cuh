@@ -31,6 +31,50 @@ enum : uint32_t {
 #define DZ_WAIT_TIMEOUT_NS 2000000000ull  // 2 s per wait, then the kernel gives up
 #endif
 
+// ---------------------------------------------------------------- debug build: checked stores
+// Compiled with -DDZ_DEBUG_BOUNDS (python -m dizo_b200.ops.build --debug-bounds) every global store of
+// the kernels first checks that its bytes fall inside one of the address ranges the host registered
+// for the launch (the tensors handed to the entry points and the peers' symmetric regions).  A store
+// outside every range is SKIPPED, counted, and its address and source line kept; nothing traps and the
+// context stays usable.  The host reads the record back after synchronising (ops/_lib.py).  This stands
+// in for compute-sanitizer's memcheck on boxes where that tool is closed.  One state per translation
+// unit (no relocatable device code needed); DZ_DEBUG_TU(name) exports its set / get entry points.
+#ifdef DZ_DEBUG_BOUNDS
+constexpr int DZ_DBG_MAX_RANGES = 256;
+struct DzDebugState {
+  unsigned long long lo[DZ_DBG_MAX_RANGES], hi[DZ_DBG_MAX_RANGES];
+  int n;                         // 0 = not armed: every store passes
+  unsigned int violations;
+  unsigned long long first_addr;
+  int first_line;
+  int pad;
+};
+static __device__ DzDebugState g_dz_dbg;
+__device__ __forceinline__ bool dz_store_ok(const void* p, unsigned long long bytes, int line) {
+  const int n = g_dz_dbg.n;
+  if (n == 0) return true;
+  const unsigned long long a = reinterpret_cast<unsigned long long>(p);
+  for (int i = 0; i < n; ++i)
+    if (a >= g_dz_dbg.lo[i] && a + bytes <= g_dz_dbg.hi[i]) return true;
+  if (atomicAdd(&g_dz_dbg.violations, 1u) == 0u) {
+    g_dz_dbg.first_addr = a;
+    g_dz_dbg.first_line = line;
+  }
+  return false;
+}
+#define DZ_STORE_OK(p, bytes) (dz::dz_store_ok((p), (bytes), __LINE__))
+#define DZ_DEBUG_TU(name)                                                                              \
+  extern "C" int dz_debug_set_##name(const void* host_state) {                                         \
+    return (int)cudaMemcpyToSymbol(dz::g_dz_dbg, host_state, sizeof(dz::DzDebugState));                \
+  }                                                                                                    \
+  extern "C" int dz_debug_get_##name(void* host_state) {                                               \
+    return (int)cudaMemcpyFromSymbol(host_state, dz::g_dz_dbg, sizeof(dz::DzDebugState));              \
+  }
+#else
+#define DZ_STORE_OK(p, bytes) (true)
+#define DZ_DEBUG_TU(name)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

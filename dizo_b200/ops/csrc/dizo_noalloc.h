@@ -17,7 +17,12 @@
 // Behaviour to know about:
 //  * The first call on each device looks up the device address of the scratch array
 //    (cudaGetSymbolAddress) with that device current; make that first call outside any stream
-//    capture.  Later calls only launch kernels and one cudaMemsetAsync on `stream`.
+//    capture.  Later calls only launch kernels and one cudaMemsetAsync on `stream`.  Two host
+//    threads that both make the first call on one device may both do this lookup; each stores the
+//    same address into the per-device slot, so the outcome is the same (the stores are plain, not
+//    atomic: if that matters to a race detector, make the first call from one thread).  The
+//    kernel launch attributes and the SM count are cached per device as well, so one process may
+//    use the entry point on several GPUs.
 //  * It never calls cudaMalloc, cudaFree or any allocating library routine.
 //  * Every call on a device shares the one scratch array, which still holds the previous
 //    call's partials; the part that must start clean is cleared on `stream` by the call itself.

@@ -341,11 +341,11 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               float4* op4 = reinterpret_cast<float4*>(op);
 #pragma unroll
               for (int q = 0; q < 8; ++q)
-                op4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                if (DZ_STORE_OK(op4 + q, 16)) op4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) op[j] = v[j];
+                if (col0 + j < p.N && DZ_STORE_OK(op + j, 4)) op[j] = v[j];
             }
           } else {
             __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
@@ -358,12 +358,12 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
                 o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
                 o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                op4[q] = o;
+                if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) op[j] = __float2bfloat16(v[j]);
+                if (col0 + j < p.N && DZ_STORE_OK(op + j, 2)) op[j] = __float2bfloat16(v[j]);
             }
           }
         }
@@ -393,6 +393,7 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(gemm2)
 
 // Same contract as dz_gemm_bf16_tn (gemm_sm100.cu); computed by pairs of SMs.
 extern "C" int dz_gemm2_bf16_tn(const void* A, long long lda, const void* W, long long ldw, void* out,

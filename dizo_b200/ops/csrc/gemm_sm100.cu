@@ -288,11 +288,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 float4* op4 = reinterpret_cast<float4*>(op);
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
-                  op4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                  if (DZ_STORE_OK(op4 + q, 16)) op4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N) op[j] = v[j];
+                  if (col0 + j < p.N && DZ_STORE_OK(op + j, 4)) op[j] = v[j];
               }
             } else {
               __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
@@ -305,12 +305,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
                   o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
                   o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                  op4[q] = o;
+                  if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
                 }
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N) op[j] = __float2bfloat16(v[j]);
+                  if (col0 + j < p.N && DZ_STORE_OK(op + j, 2)) op[j] = __float2bfloat16(v[j]);
               }
             }
           }
@@ -392,6 +392,7 @@ static int check_common(const void* A, const void* W, int M, int N, int K, long 
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(gemm1)
 
 // out[M,N] = act((A W^T + bias) * out_scale) + residual.  bf16 inputs; out is bf16 or fp32.
 // tile_n: 0 = choose, 128 or 256.

@@ -30,8 +30,8 @@ __global__ void lse_combine_kernel(const float* __restrict__ part_max,
   float s = 0.f;
   for (int j = 0; j < num_tiles; ++j) s += ps[j] * expf(pm[j] - m);
   float lse = m + logf(s);
-  if (lse_out) lse_out[r] = lse;
-  if (logprob) logprob[r] = tgt_logit[r] - lse;
+  if (lse_out && DZ_STORE_OK(lse_out + r, 4)) lse_out[r] = lse;
+  if (logprob && DZ_STORE_OK(logprob + r, 4)) logprob[r] = tgt_logit[r] - lse;
 }
 
 // One block.  mode 0: classification over candidates; mode 1: token-level CE.
@@ -119,6 +119,7 @@ verbalizer_ce_kernel(const __nv_bfloat16* __restrict__ h, long long ldh,
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(lmhead)
 
 extern "C" int dz_lse_combine(const float* part_max, const float* part_sum, const float* tgt_logit,
                               int num_tiles, int rows, float* logprob, float* lse_out,

@@ -84,7 +84,7 @@ layernorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                         (bf16_hi(v[i].z) - mean) * rstd * bf16_hi(wv.z) + bf16_hi(bv.z));
       o.w = pack_bf16x2((bf16_lo(v[i].w) - mean) * rstd * bf16_lo(wv.w) + bf16_lo(bv.w),
                         (bf16_hi(v[i].w) - mean) * rstd * bf16_hi(wv.w) + bf16_hi(bv.w));
-      yr[idx] = o;
+      if (DZ_STORE_OK(yr + idx, 16)) yr[idx] = o;
     }
   }
 }
@@ -110,10 +110,11 @@ embed_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
       o.y = pack_bf16x2(bf16_lo(a.y) + bf16_lo(c.y), bf16_hi(a.y) + bf16_hi(c.y));
       o.z = pack_bf16x2(bf16_lo(a.z) + bf16_lo(c.z), bf16_hi(a.z) + bf16_hi(c.z));
       o.w = pack_bf16x2(bf16_lo(a.w) + bf16_lo(c.w), bf16_hi(a.w) + bf16_hi(c.w));
-      orow[i] = o;
+      if (DZ_STORE_OK(orow + i, 16)) orow[i] = o;
     }
   } else {
-    for (int i = threadIdx.x; i < (d_tok >> 3); i += blockDim.x) orow[i] = __ldg(tr + i);
+    for (int i = threadIdx.x; i < (d_tok >> 3); i += blockDim.x)
+      if (DZ_STORE_OK(orow + i, 16)) orow[i] = __ldg(tr + i);
   }
   (void)d_pos;
 }
@@ -134,7 +135,7 @@ add_rows_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const int* _
     o.y = pack_bf16x2(bf16_lo(x.y) + bf16_lo(c.y), bf16_hi(x.y) + bf16_hi(c.y));
     o.z = pack_bf16x2(bf16_lo(x.z) + bf16_lo(c.z), bf16_hi(x.z) + bf16_hi(c.z));
     o.w = pack_bf16x2(bf16_lo(x.w) + bf16_lo(c.w), bf16_hi(x.w) + bf16_hi(c.w));
-    orow[i] = o;
+    if (DZ_STORE_OK(orow + i, 16)) orow[i] = o;
   }
 }
 
@@ -147,12 +148,14 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, const i
   s = s < 0 ? 0 : (s >= n_src ? n_src - 1 : s);
   const uint4* sr = reinterpret_cast<const uint4*>(src + s * lds);
   uint4* orow = reinterpret_cast<uint4*>(out + r * ldo);
-  for (int i = threadIdx.x; i < (d >> 3); i += blockDim.x) orow[i] = sr[i];
+  for (int i = threadIdx.x; i < (d >> 3); i += blockDim.x)
+    if (DZ_STORE_OK(orow + i, 16)) orow[i] = sr[i];
 }
 
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(norm)
 
 static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

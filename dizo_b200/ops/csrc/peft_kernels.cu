@@ -38,12 +38,13 @@ lora_merge_kernel(const __nv_bfloat16* __restrict__ W, long long ldw,
   uint4 o;
   o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
   o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-  *reinterpret_cast<uint4*>(out + (long long)n * ldo + k0) = o;
+  if (DZ_STORE_OK(out + (long long)n * ldo + k0, 16)) *reinterpret_cast<uint4*>(out + (long long)n * ldo + k0) = o;
 }
 
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(peft)
 
 extern "C" int dz_lora_merge(const void* W, long long ldw, const void* A, long long lda,
                              const void* B, long long ldb, void* out, long long ldo, int N, int K,

@@ -114,7 +114,8 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
         }
         o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
       }
-      *reinterpret_cast<uint4*>(a.dst + (cpos + lane * 8 - a.dst_shift)) = o;
+      uint4* dp = reinterpret_cast<uint4*>(a.dst + (cpos + lane * 8 - a.dst_shift));
+      if (DZ_STORE_OK(dp, 16)) *dp = o;
     }
     return;
   }
@@ -173,7 +174,8 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
         }
       }
     }
-    *reinterpret_cast<uint4*>(a.dst + (pos - a.dst_shift)) = make_uint4(o[0], o[1], o[2], o[3]);
+    uint4* dp = reinterpret_cast<uint4*>(a.dst + (pos - a.dst_shift));
+    if (DZ_STORE_OK(dp, 16)) *dp = make_uint4(o[0], o[1], o[2], o[3]);
     if (NORM && slotted) {
       // norm of what was stored (the bf16 values), so it equals a later re-read
 #pragma unroll
@@ -190,7 +192,10 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
     // fixed-order warp reduction -> one partial per chunk (deterministic)
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-    if (lane == 0 && t.sq_base >= 0) a.chunk_sq[t.sq_base + (cpos - t.offset) / ZO_CHUNK] = sq;
+    if (lane == 0 && t.sq_base >= 0) {
+      float* sp = a.chunk_sq + t.sq_base + (cpos - t.offset) / ZO_CHUNK;
+      if (DZ_STORE_OK(sp, 4)) *sp = sq;
+    }
   }
 }
 
@@ -305,7 +310,7 @@ __global__ void zo_reduce_chunks_kernel(const ZoTensor* table, int num_tensors,
     if (threadIdx.x < s) s_red[threadIdx.x] += s_red[threadIdx.x + s];
     __syncthreads();
   }
-  if (threadIdx.x == 0) sq_out[t.slot] = s_red[0];  // one piece per slot per rank
+  if (threadIdx.x == 0 && DZ_STORE_OK(sq_out + t.slot, 4)) sq_out[t.slot] = s_red[0];  // one piece per slot per rank
 }
 
 // gamma search bookkeeping on the device (one thread per constraint).
@@ -377,6 +382,7 @@ static int launch_sweep(const ZoSweepArgs& a, cudaStream_t stream) {
 }  // namespace dz
 
 using namespace dz;
+DZ_DEBUG_TU(zo)
 
 extern "C" int dz_zo_chunk() { return ZO_CHUNK; }
 extern "C" int dz_zo_tensor_struct_bytes() { return (int)sizeof(ZoTensor); }
@@ -475,7 +481,8 @@ __global__ void zo_fill_z_kernel(float* out, long long numel, long long elem_bas
   if (e0 >= numel) return;
   float z[8];
   gauss8<2>(reinterpret_cast<const char*>(tab), seed, tensor_id, (uint32_t)((elem_base + e0) >> 3), 0u, z);
-  for (int j = 0; j < 8 && e0 + j < numel; ++j) out[e0 + j] = z[j];
+  for (int j = 0; j < 8 && e0 + j < numel; ++j)
+    if (DZ_STORE_OK(out + e0 + j, 4)) out[e0 + j] = z[j];
 }
 extern "C" int dz_zo_fill_z(float* out, long long numel, long long elem_base,
                             unsigned long long seed, int tensor_id, const void* gauss_table,

@@ -89,7 +89,8 @@ class FusedComm:
         total = 2 * ag_bytes + 2 * rs_bytes + 2 * w_bytes + 64 * 1024 + 8 * norm_slots * (self.world + 1)
         self.region = SymmRegion(total + 16 * 4096, self.group, device)
         self.device = self.region.device
-        self.n_push = n_push          # kept for callers; the push now rides in every CTA (see comm_gemm.cu)
+        # > 0 fixes the number of pushing CTAs of every launch (measurements); 0 = planned per launch
+        self.n_push_override = 0
         self.ag = [_Channel(self.region, ag_bytes) for _ in range(2)] if ag_bytes else []
         self.rs = [_Channel(self.region, rs_bytes) for _ in range(2)] if rs_bytes else []
         self.wst = [_Channel(self.region, w_bytes) for _ in range(2)] if w_bytes else []
@@ -106,22 +107,59 @@ class FusedComm:
         self._push_total = 0
         self._gemm_total = 0
         self._calls = {"ag": 0, "rs": 0, "w": 0}
+        self._dbg_out = None
 
     # ------------------------------------------------------------------ helpers
-    def _launch(self, d: _Desc, push: bool, M: int, N: int) -> None:
+    def _push_plan(self, d: _Desc, M: int, N: int, consumer_waits: bool) -> tuple[int, int]:
+        """(CTAs that push, tiles left to them).  Posted stores from every SM saturate NVLink in a fraction of
+        the launch and the back-pressure then stalls the operand loads of all GEMM tiles, so the number of
+        pushing CTAs follows the rate the transfer needs: the bytes this rank sends, over the part of the
+        GEMM's duration it may take (a third when the same launch multiplies what arrives, most of it when
+        the push is a prefetch for the next launch), at about 12 GB/s per pushing CTA.  Those CTAs get a
+        reduced share of the output tiles (60 % of the others'), at the end of the tile order."""
+        import math
+        L = _lib.lib()
+        if self.n_push_override:
+            n = int(self.n_push_override)
+        elif M <= 0:
+            n = 96                                                          # push only: as fast as NVLink takes it
+        else:
+            out_bytes = d.push_nseg * d.push_rows * d.push_cols * 2 * (self.world - 1 + int(bool(d.push_to_self)))
+            t_gemm = max(2.0 * M * N * d.K / 1.2e15, 30e-6)
+            window = (0.35 if consumer_waits else 0.8) * t_gemm
+            rate = min(out_bytes / window, 700e9)
+            n = int(math.ceil(rate / (8e9 if d.push_perturb else 12e9)))
+        grid0 = L.dz_comm_gemm_grid(M, N, 0) if M > 0 else _SM_COUNT
+        n = max(8, min(n, _SM_COUNT))
+        if M <= 0:
+            return n, 0
+        n = min(n, max(grid0, 8))
+        tiles = L.dz_comm_gemm_tiles(M, N)
+        g = grid0 - n
+        if g <= 0 or tiles <= grid0:
+            return n, 0
+        f = 0.6
+        join = int(tiles * n * f / (g + n * f))
+        return n, max(0, min(join, tiles - 1))
+
+    def _launch(self, d: _Desc, push: bool, M: int, N: int, consumer_waits: bool = True) -> None:
         L = _lib.lib()
         assert ctypes.sizeof(_Desc) == L.dz_comm_gemm_desc_bytes(), "launch descriptor out of step with the library"
         d.rank, d.world = self.rank, self.world
         d.counters = self.counters.data_ptr()
-        # every CTA of a pushing launch carries a slice of the push (four extra warps beside its GEMM
-        # warps), and every CTA of any launch reports its completion: the counters advance by the grid size
-        grid = L.dz_comm_gemm_grid(M, N, int(push))
-        d.n_push = 1 if push else 0
+        # the first n_push CTAs carry a slice of the push (four extra warps beside their GEMM warps); every CTA
+        # of any launch reports its completion: the counters advance by the pushing CTAs / the grid size
+        n_push, join = self._push_plan(d, M, N, consumer_waits) if push else (0, 0)
+        grid = L.dz_comm_gemm_grid(M, N, n_push)
+        d.n_push, d.join_tiles = n_push, join
         if push:
-            self._push_total += grid
+            self._push_total += n_push
             d.push_target = self._push_total & 0xFFFFFFFF
         self._gemm_total += grid
         d.gemm_target = self._gemm_total & 0xFFFFFFFF
+        if _lib.DEBUG_BOUNDS and self._dbg_out is not None:
+            _lib.note(self._dbg_out)              # the local output of this launch
+            self._dbg_out = None
         rc = L.dz_comm_gemm(ctypes.byref(d), _lib.ptr(_lib.err_word(self.device)), _lib.stream_ptr())
         _lib.check(rc, "dz_comm_gemm")
 
@@ -158,6 +196,7 @@ class FusedComm:
         d = _Desc()
         d.A, d.lda, d.W, d.ldw = x_full.data_ptr(), x_full.stride(0), w.data_ptr(), w.stride(0)
         d.out, d.ldo = out.data_ptr(), out.stride(0)
+        self._dbg_out = out
         d.bias = bias.data_ptr() if bias is not None else None
         d.M, d.N, d.K, d.act, d.out_scale = M, N, K, ACT[act], 1.0
         d.gather, d.rows_per_src, d.wait_self = 1, rows, 0
@@ -277,6 +316,7 @@ class FusedComm:
                 out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
             d.A, d.lda, d.W, d.ldw = x.data_ptr(), x.stride(0), w_full.data_ptr(), K
             d.out, d.ldo = out.data_ptr(), out.stride(0)
+            self._dbg_out = out
             bias, residual = gemm.get("bias"), gemm.get("residual")
             d.bias = bias.data_ptr() if bias is not None else None
             if residual is not None:
@@ -288,12 +328,42 @@ class FusedComm:
             # acks count consumptions of the slot: the next pusher into it waits for this one
             ch.ack_epoch += 1
             d.ack_ptrs, d.ack_epoch = ch.ack_ptrs.data_ptr(), ch.ack_epoch
-        self._launch(d, push is not None, M, Ng)
+        same = push is not None and gemm is not None and gemm["slot"] == slot
+        self._launch(d, push is not None, M, Ng, consumer_waits=same)
         return slot, out
 
     def fsdp_weight(self, slot: int, N: int, K: int) -> torch.Tensor:
         """The staging copy of a gathered weight (valid after its consumers' flags are up)."""
         return self.wst[slot].view[:N * K * 2].view(torch.bfloat16).view(N, K)
+
+    # ------------------------------------------------------------------ flag protocol check
+    def protocol_report(self) -> list[str]:
+        """Host-side check of the flag protocol, to be called when every rank is idle (after a
+        synchronise and a barrier): for every staging buffer, each source rank's ready word must equal
+        the number of pushes issued into the buffer, the partial-sum words of a reduce-scatter buffer
+        the number of GEMMs that filled it, and no ack may run ahead of the consumptions announced.
+        Returns the mismatches (empty = consistent)."""
+        torch.cuda.synchronize(self.device)
+        bad = []
+        for kind, chans in (("ag", self.ag), ("w", self.wst)):
+            for i, ch in enumerate(chans):
+                ready = ch.ready.view(self.world, MAX_CHUNKS)[:, 0].tolist()
+                acks = ch.ack.tolist()
+                for src in range(self.world):
+                    if kind == "ag" and src == self.rank:
+                        continue                      # own rows are written in place, never flagged
+                    if ready[src] != ch.epoch:
+                        bad.append(f"{kind}[{i}] ready[{src}] = {ready[src]}, pushes issued {ch.epoch}")
+                want_ack = ch.epoch if kind == "ag" else ch.ack_epoch
+                for src in range(self.world):
+                    if acks[src] > want_ack:
+                        bad.append(f"{kind}[{i}] ack[{src}] = {acks[src]} ahead of {want_ack}")
+        for i, ch in enumerate(self.rs):
+            flags = ch.ready.view(-1)[:self.world].tolist()
+            for src in range(self.world):
+                if flags[src] != ch.epoch:
+                    bad.append(f"rs[{i}] partials[{src}] = {flags[src]}, GEMMs issued {ch.epoch}")
+        return bad
 
     # ------------------------------------------------------------------ DiZO norms
     def norm_allreduce_gamma(self, partial_sq: torch.Tensor, gs, reinit: bool, use_multimem: bool = False):

@@ -1,7 +1,7 @@
 """Timing of the fused compute+collective kernels against the NCCL + GEMM composition.
 
     python -m torch.distributed.run --nproc-per-node N -m dizo_b200.parallel.microbench \
-        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas 16]
+        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas N]
 
 For every path, device time (CUDA events, max over ranks) of the fused launch and of the
 composition it replaces (NCCL all-gather or reduce-scatter plus the framework's own GEMM), and
@@ -47,7 +47,8 @@ def main():
     ap.add_argument("--hidden", dest="d", type=int, default=9216)
     ap.add_argument("--ffn-dim", dest="ffn", type=int, default=36864)
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--push-ctas", dest="n_push", type=int, default=16)
+    ap.add_argument("--push-ctas", dest="n_push", type=int, default=0,
+                    help="fix the number of pushing CTAs of every launch (0 = planned per launch from the bytes to move)")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -57,7 +58,8 @@ def main():
     peaks = _peaks()
     M, d, F = a.m, a.d, a.ffn
     Fl, rows = F // world, M // world
-    fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2, n_push=a.n_push)
+    fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2)
+    fc.n_push_override = a.n_push
     g = torch.Generator(device=dev).manual_seed(1)
     x_local = torch.randn(rows, d, device=dev, generator=g).bfloat16()
     w1 = (torch.randn(Fl, d, device=dev, generator=g) * 0.02).bfloat16()

@@ -29,6 +29,9 @@ class SymmRegion:
             self.multicast_ptr = int(self.handle.multicast_ptr)
         except Exception:
             self.multicast_ptr = 0
+        from ..ops import _lib
+        for p in self.ptrs:                       # checked-store build: the peers' regions are writable
+            _lib.note_range(p, nbytes)
         self.buf.zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)

@@ -7,8 +7,16 @@ import pytest
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def pytest_addoption(parser):
+    parser.addoption("--debug-bounds", action="store_true", default=False,
+                     help="run against the checked-store build of the kernel library (every global store is "
+                          "checked against the registered tensors; built on demand)")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    if config.getoption("--debug-bounds"):
+        os.environ["DIZO_DEBUG_BOUNDS"] = "1"       # read when dizo_b200.ops._lib is first imported
 
 
 def pytest_collection_modifyitems(config, items):

@@ -105,6 +105,8 @@ def main():
     torch.cuda.synchronize()
     _lib.check_device_errors()
     dist.barrier()
+    report = fs.comm.protocol_report()            # every ready / ack / partial-sum word agrees with the launches issued
+    assert not report, report
     if rank == 0:
         print("FSDP_OK world", world)
     dist.destroy_process_group()

@@ -565,7 +565,11 @@ class OPTModel:
         return gemm.linear(h, get(stem + "2.weight"), get(stem + "2.bias"))
 
     # ------------------------------------------------------------------ forward
-    def _layer_forward(self, h: torch.Tensor, w: SimpleNamespace, batch: Batch) -> torch.Tensor:
+    def _layer_forward(self, h: torch.Tensor, w: SimpleNamespace, batch: Batch,
+                       rows: torch.Tensor | None = None) -> torch.Tensor:
+        """One block.  With ``rows`` (the last block of a loss forward) everything after the attention
+        runs on those token rows only and [R, d] is returned: the other rows of the last block's
+        out_proj / FFN feed nothing, which saves three quarters of that block's GEMM work."""
         cfg = self.config
         B, L, d = h.shape
         pre = cfg.do_layer_norm_before
@@ -575,6 +579,9 @@ class OPTModel:
             self.kv_capture.append(qkv)
         ctx = attn_ops.attention(qkv.view(B, L, 3 * d), cfg.num_attention_heads, batch.pad_left,
                                  w.prefix_k, w.prefix_v)
+        if rows is not None:
+            ctx = norm.gather_rows(ctx.reshape(-1, d), rows)
+            h = norm.gather_rows(h.reshape(-1, d), rows)
         h = gemm.linear(ctx, w.out_w, w.out_b, residual=h)
         if not pre:
             h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
@@ -586,8 +593,10 @@ class OPTModel:
         return h
 
     @torch.no_grad()
-    def hidden_states(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
-        """Decoder output before the final LayerNorm / project_out: [B, L, d]."""
+    def hidden_states(self, batch: Batch, transform: Transform | None = None,
+                      rows: torch.Tensor | None = None) -> torch.Tensor:
+        """Decoder output before the final LayerNorm / project_out: [B, L, d], or - with ``rows`` - only
+        those (sequence * L + position) rows of it, [R, d] (see :meth:`_layer_forward`)."""
         cfg = self.config
         nl = cfg.num_hidden_layers
         use_t = transform is not None and len(self.arena.pieces) > 0
@@ -650,21 +659,32 @@ class OPTModel:
             if use_t and i + 1 < nl and has_group.get(i + 1):
                 pending = launch_transform(i + 1)
             w = self._layer_weights(i, self._resolver(i, transform, staged, shift))
-            h = self._layer_forward(h, w, batch)
+            only = rows if (i == nl - 1 and self.kv_capture is None) else None
+            h = self._layer_forward(h, w, batch, only)
             if overlap and has_group.get(i):
                 ev = torch.cuda.Event()
                 ev.record(main)
                 free[i % 2] = ev
         if overlap:
             main.wait_stream(self._side)
+        if rows is not None and nl == 0:
+            h = norm.gather_rows(h.reshape(-1, cfg.hidden_size), rows)
         return h
 
+    def _selected(self, batch: Batch, transform: Transform | None) -> torch.Tensor:
+        """Final-normalised hidden rows ``batch.rows``.  The replicated model restricts its last block to
+        them; sharded layouts (own ``hidden_states``) compute every row and pick afterwards."""
+        if type(self).hidden_states is OPTModel.hidden_states:
+            return self.final_rows(self.hidden_states(batch, transform, rows=batch.rows), None)
+        return self.final_rows(self.hidden_states(batch, transform), batch.rows)
+
     @torch.no_grad()
-    def final_rows(self, h: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-        """Final LayerNorm (+ project_out) applied to the selected rows of h only."""
+    def final_rows(self, h: torch.Tensor, rows: torch.Tensor | None) -> torch.Tensor:
+        """Final LayerNorm (+ project_out) applied to the selected rows of h only (``rows`` None: h
+        already holds just those rows)."""
         cfg = self.config
         d = cfg.hidden_size
-        x = norm.gather_rows(h.reshape(-1, d), rows)
+        x = h if rows is None else norm.gather_rows(h.reshape(-1, d), rows)
         gget = self._gget
         if cfg.do_layer_norm_before:
             x = norm.layernorm(x, gget(_P + "final_layer_norm.weight"),
@@ -679,8 +699,7 @@ class OPTModel:
     @torch.no_grad()
     def loss(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
         """One fp32 loss (1-element tensor on the device) for the batch."""
-        h = self.hidden_states(batch, transform)
-        x = self.final_rows(h, batch.rows)
+        x = self._selected(batch, transform)
         table = self.lm_head_weight()
         if batch.cand_ids is not None:
             _, loss = loss_ops.verbalizer_ce(x, table, batch.cand_ids, batch.labels)
@@ -691,8 +710,7 @@ class OPTModel:
     @torch.no_grad()
     def row_logprobs(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
         """log p(target) for every (row, target) pair of the batch (evaluation path)."""
-        h = self.hidden_states(batch, transform)
-        x = self.final_rows(h, batch.rows)
+        x = self._selected(batch, transform)
         return loss_ops.token_logprobs(x, self.lm_head_weight(), batch.targets)
 
     @torch.no_grad()

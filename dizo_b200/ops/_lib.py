@@ -157,7 +157,11 @@ def note(t: torch.Tensor) -> torch.Tensor:
 def forget(t: torch.Tensor) -> None:
     """Drop ``t``'s storage from the table (tests: the next store into it must be reported)."""
     if DEBUG_BOUNDS:
-        _dbg_ranges.pop(t.untyped_storage().data_ptr(), None)
+        st = t.untyped_storage()
+        lo, hi = st.data_ptr(), st.data_ptr() + st.nbytes()
+        # ranges of freed tensors linger (the allocator reuses their memory): drop every overlap
+        for k in [k for k, v in _dbg_ranges.items() if k < hi and v > lo]:
+            _dbg_ranges.pop(k)
         _dbg_push()
 
 

@@ -14,8 +14,8 @@
 //     CTAs push is the host's choice per launch, from the bytes to move and the time the GEMM
 //     gives them: posted stores from all 148 SMs saturate NVLink within a fraction of the launch
 //     and the back-pressure then stalls the TMA loads of every GEMM (measured on 8 GPUs), so the
-//     rate is held near what the transfer needs, and the pushing CTAs take a smaller share of the
-//     tiles (`join_tiles`, at the end of the tile order).  When a CTA has pushed its slice it
+//     host limits the pushing CTAs and gives them a smaller share of the tiles, or none
+//     (`join_tiles`; their tiles sit at the end of the tile order).  When a CTA has pushed its slice it
 //     fences at system scope; the last one raises the `ready` flag of this rank at every peer.
 //   * GATHERED OPERAND: rows of A (tensor parallel: sequence-sharded activations) or of W
 //     (FSDP: row-sharded weights) arrive from peers in this rank's staging buffer; the TMA
@@ -80,7 +80,7 @@ struct CommGemmArgs {
                                  // (fused q|k|v: d); 0 = no repetition
   int wait_self;                 // own rows are also produced by this launch's push role
   int chunk_tiles;               // gather 1: row tiles per progress chunk of a source (0 = one chunk)
-  int join_tiles;                // tiles at the end of the order that the pushing CTAs multiply
+  int join_tiles;                // tiles at the end of the order that the pushing CTAs multiply (< 0: none)
   const uint32_t* ready_flags;   // local [world][CG_MAXC]: flag[s][c] >= ready_epoch once rank s has
                                  // pushed chunk c of its rows (unchunked pushes use c = 0 only)
   uint32_t ready_epoch;
@@ -355,8 +355,9 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_kb = (p.K + CG_BK - 1) / CG_BK;
   // CTAs that also push take the last join_tiles tiles of the order, the others the rest
   const bool pusher = (int)blockIdx.x < p.n_push;
-  const bool split = p.n_push > 0 && p.n_push < (int)gridDim.x && p.join_tiles > 0;
-  const int reg_tiles = split ? num_tiles - p.join_tiles : num_tiles;
+  // (join_tiles < 0: the pushing CTAs multiply nothing)
+  const bool split = p.n_push > 0 && p.n_push < (int)gridDim.x && p.join_tiles != 0;
+  const int reg_tiles = (split && p.join_tiles > 0) ? num_tiles - p.join_tiles : num_tiles;
   const int cta = !split ? (int)blockIdx.x : (pusher ? reg_tiles + (int)blockIdx.x : (int)blockIdx.x - p.n_push);
   const int n_cta = !split ? (int)gridDim.x : (pusher ? p.n_push : (int)gridDim.x - p.n_push);
   const int tile_end = (split && !pusher) ? reg_tiles : num_tiles;
@@ -764,8 +765,9 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   // one CTA per SM at most: every CTA must be resident at once (the roles wait on one another through flags)
   const int grid = dz_comm_gemm_grid(has_gemm ? d->M : 0, has_gemm ? d->N : 0, a.n_push);
   if (grid < 1 || grid > sm_count() || a.n_push > grid) return DZ_ERR_TOO_LARGE;
-  if (has_gemm && a.n_push > 0 && a.n_push < grid && d->join_tiles > 0) {
-    // without a split (join_tiles 0) when the pushing CTAs are left no tile, every CTA strides over all tiles
+  if (has_gemm && a.n_push > 0 && a.n_push < grid && d->join_tiles != 0) {
+    // join_tiles 0: every CTA strides over all tiles; > 0: the pushing CTAs take that many tiles at the end of
+    // the order; < 0: the pushing CTAs multiply nothing
     if (d->join_tiles >= a.num_m * a.num_n) return DZ_ERR_ARG;
     a.join_tiles = d->join_tiles;
   }

@@ -89,8 +89,8 @@ class FusedComm:
         total = 2 * ag_bytes + 2 * rs_bytes + 2 * w_bytes + 64 * 1024 + 8 * norm_slots * (self.world + 1)
         self.region = SymmRegion(total + 16 * 4096, self.group, device)
         self.device = self.region.device
-        # > 0 fixes the number of pushing CTAs of every launch (measurements); 0 = planned per launch
-        self.n_push_override = 0
+        self.push_ctas = 0            # pushing CTAs per launch; 0 = by the number of ranks (see _push_plan)
+        self.push_share = 0.0         # their share of a normal CTA's output tiles (0 = they only push)
         self.ag = [_Channel(self.region, ag_bytes) for _ in range(2)] if ag_bytes else []
         self.rs = [_Channel(self.region, rs_bytes) for _ in range(2)] if rs_bytes else []
         self.wst = [_Channel(self.region, w_bytes) for _ in range(2)] if w_bytes else []
@@ -111,36 +111,28 @@ class FusedComm:
 
     # ------------------------------------------------------------------ helpers
     def _push_plan(self, d: _Desc, M: int, N: int, consumer_waits: bool) -> tuple[int, int]:
-        """(CTAs that push, tiles left to them).  Posted stores from every SM saturate NVLink in a fraction of
-        the launch and the back-pressure then stalls the operand loads of all GEMM tiles, so the number of
-        pushing CTAs follows the rate the transfer needs: the bytes this rank sends, over the part of the
-        GEMM's duration it may take (a third when the same launch multiplies what arrives, most of it when
-        the push is a prefetch for the next launch), at about 12 GB/s per pushing CTA.  Those CTAs get a
-        reduced share of the output tiles (60 % of the others'), at the end of the tile order."""
-        import math
+        """(CTAs that push, ``join_tiles``: tiles left to them; -1 = none, 0 = a full share).
+
+        Measured policy.  Two ranks: every CTA pushes (one destination, half of the bytes stay local; the
+        transfer rides along at no visible cost).  More ranks: posted stores from all 148 SMs to seven
+        destinations slowed every GEMM tile (8 GPUs: all-gather -> GEMM 0.61 -> 0.71 ms, FSDP 4.45 -> 5.49 ms
+        at OPT-66B shapes), so ``push_ctas`` CTAs push and take ``push_share`` of a normal CTA's tiles."""
         L = _lib.lib()
-        if self.n_push_override:
-            n = int(self.n_push_override)
-        elif M <= 0:
-            n = 96                                                          # push only: as fast as NVLink takes it
-        else:
-            out_bytes = d.push_nseg * d.push_rows * d.push_cols * 2 * (self.world - 1 + int(bool(d.push_to_self)))
-            t_gemm = max(2.0 * M * N * d.K / 1.2e15, 30e-6)
-            window = (0.35 if consumer_waits else 0.8) * t_gemm
-            rate = min(out_bytes / window, 700e9)
-            n = int(math.ceil(rate / (8e9 if d.push_perturb else 12e9)))
-        grid0 = L.dz_comm_gemm_grid(M, N, 0) if M > 0 else _SM_COUNT
-        n = max(8, min(n, _SM_COUNT))
         if M <= 0:
+            return min(_SM_COUNT, 96), 0                                    # push only
+        grid0 = L.dz_comm_gemm_grid(M, N, 0)
+        n = self.push_ctas if self.push_ctas > 0 else (grid0 if self.world <= 2 else 16)
+        n = max(1, min(n, _SM_COUNT))
+        if n >= grid0:
             return n, 0
-        n = min(n, max(grid0, 8))
         tiles = L.dz_comm_gemm_tiles(M, N)
+        f = self.push_share
+        if f <= 0.0:
+            return n, -1
         g = grid0 - n
-        if g <= 0 or tiles <= grid0:
+        if f >= 1.0 or tiles <= grid0:
             return n, 0
-        f = 0.6
-        join = int(tiles * n * f / (g + n * f))
-        return n, max(0, min(join, tiles - 1))
+        return n, max(1, min(int(tiles * n * f / (g + n * f)), tiles - 1))
 
     def _launch(self, d: _Desc, push: bool, M: int, N: int, consumer_waits: bool = True) -> None:
         L = _lib.lib()

@@ -1,7 +1,7 @@
 """Timing of the fused compute+collective kernels against the NCCL + GEMM composition.
 
     python -m torch.distributed.run --nproc-per-node N -m dizo_b200.parallel.microbench \
-        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas N]
+        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas N --push-share F]
 
 For every path, device time (CUDA events, max over ranks) of the fused launch and of the
 composition it replaces (NCCL all-gather or reduce-scatter plus the framework's own GEMM), and
@@ -48,7 +48,9 @@ def main():
     ap.add_argument("--ffn-dim", dest="ffn", type=int, default=36864)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--push-ctas", dest="n_push", type=int, default=0,
-                    help="fix the number of pushing CTAs of every launch (0 = planned per launch from the bytes to move)")
+                    help="CTAs whose push warps are active (0 = the default policy for this number of ranks)")
+    ap.add_argument("--push-share", type=float, default=0.0,
+                    help="output tiles of a pushing CTA relative to the others (0 = it only pushes)")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -59,7 +61,7 @@ def main():
     M, d, F = a.m, a.d, a.ffn
     Fl, rows = F // world, M // world
     fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2)
-    fc.n_push_override = a.n_push
+    fc.push_ctas, fc.push_share = a.n_push, a.push_share
     g = torch.Generator(device=dev).manual_seed(1)
     x_local = torch.randn(rows, d, device=dev, generator=g).bfloat16()
     w1 = (torch.randn(Fl, d, device=dev, generator=g) * 0.02).bfloat16()
@@ -76,7 +78,8 @@ def main():
         out.append({"path": name, "world": world, "fused_ms": fused_ms, "nccl_composition_ms": base_ms,
                     "speedup": base_ms / fused_ms, "roofline_ms": floor_ms,
                     "fraction_of_roofline": floor_ms / fused_ms,
-                    "tflops_per_gpu": flops / fused_ms / 1e9})
+                    "tflops_per_gpu": flops / fused_ms / 1e9, "hidden": d,
+                    "push_ctas": a.n_push or ("all" if world <= 2 else 16), "push_share": a.push_share})
 
     # ---- TP: all-gather -> GEMM (fc1 shape)
     def fused_ag():

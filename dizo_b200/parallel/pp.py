@@ -10,8 +10,9 @@ stage already works on the next micro-batch.  There is no backward, so there are
 the fill and drain of one forward, and nothing is stashed.
 
 Perturbation needs no communication: every stage regenerates z for its own tensors from the
-shared step seed (z depends only on seed, tensor id and element index), so a pipeline step is
-bit-identical to the single-device step in fp32.  The stage's transformed weights
+shared step seed (z depends only on seed, tensor id and element index), so a pipeline step applies
+the same perturbation and update as the single-device step (equal up to the summation order of the
+last block's small GEMMs, which run per micro-batch here).  The stage's transformed weights
 (theta + eps z, or the DiZO blend) are staged once per forward - all owned blocks, not one layer
 at a time - because every micro-batch passes through all of them.  The loss is computed on the last
 stage and broadcast (one scalar); activations travel by ``torch.distributed`` send / recv (NCCL on
@@ -117,8 +118,10 @@ class PPOPTModel(OPTModel):
         return [(a, min(B, a + step)) for a in range(0, B, step)]
 
     @torch.no_grad()
-    def hidden_states(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor | None:
-        """The last stage returns the final residual stream [B, L, d]; the others return None."""
+    def hidden_states(self, batch: Batch, transform: Transform | None = None,
+                      rows: torch.Tensor | None = None) -> torch.Tensor | None:
+        """The last stage returns the final residual stream [B, L, d] (with ``rows``: only those token rows,
+        [R, d], the last block running on them alone as in the single-device model); the others None."""
         cfg = self.config
         d = cfg.hidden_size
         B, L = batch.input_ids.shape
@@ -138,8 +141,12 @@ class PPOPTModel(OPTModel):
             else:
                 h = torch.empty((b - a, L, d), dtype=self.dtype, device=self.device)
                 dist.recv(h, src=prev_r, group=self.group)
-            for w in weights:
-                h = self._layer_forward(h, w, mb)
+            for j, w in enumerate(weights):
+                only = None
+                if last and rows is not None and j == len(weights) - 1:
+                    keep = (rows >= a * L) & (rows < b * L)          # this micro-batch's loss rows
+                    only = (rows[keep] - a * L).to(torch.int32)
+                h = self._layer_forward(h, w, mb, only)
             if last:
                 outs.append(h)
             else:
@@ -158,10 +165,10 @@ class PPOPTModel(OPTModel):
 
     @torch.no_grad()
     def loss(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
-        h = self.hidden_states(batch, transform)
+        h = self.hidden_states(batch, transform, rows=batch.rows)
 
         def tail():
-            x = self.final_rows(h, batch.rows)
+            x = self.final_rows(h, None)
             table = self.lm_head_weight()
             if batch.cand_ids is not None:
                 return loss_ops.verbalizer_ce(x, table, batch.cand_ids, batch.labels)[1]
@@ -171,8 +178,8 @@ class PPOPTModel(OPTModel):
 
     @torch.no_grad()
     def row_logprobs(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
-        h = self.hidden_states(batch, transform)
-        return self._from_last(lambda: loss_ops.token_logprobs(self.final_rows(h, batch.rows),
+        h = self.hidden_states(batch, transform, rows=batch.rows)
+        return self._from_last(lambda: loss_ops.token_logprobs(self.final_rows(h, None),
                                                                self.lm_head_weight(), batch.targets),
                                (batch.targets.numel(),))
 

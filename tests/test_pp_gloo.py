@@ -23,18 +23,20 @@ PP_SCRIPT = textwrap.dedent('''
     from dizo_b200.models.opt import Transform
     for tr in (None, Transform(seed=5, coef=1e-2)):
         a, b = solo.loss(batch(0, 3), tr), pp.loss(batch(0, 3), tr)
-        assert torch.equal(a.reshape(1), b.reshape(1)), (a, b)
+        # fp32 on both sides; the last block runs on the loss rows only, per micro-batch in the pipeline and
+        # for the whole batch in the single process, so the BLAS sums may differ in the last bits
+        assert torch.allclose(a.reshape(1), b.reshape(1), rtol=1e-5, atol=1e-6), (a, b)
     # ZO steps + a gamma search: identical trajectories, no parameter ever communicated
     e1, e2 = ZOEngine(solo, eps=1e-3, dp_group=False), ZOEngine(pp, eps=1e-3, dp_group=False)
     for step in range(4):
         l1 = e1.step(batch(step), 1e-3, seed=100 + step)
         l2 = e2.step(batch(step), 1e-3, seed=100 + step)
-        assert float(l1) == float(l2), (step, l1, l2)
+        assert abs(float(l1) - float(l2)) < 1e-5, (step, l1, l2)
     full = pp.gather_state_dict()
     ref = solo.state_dict()
     assert set(full) == set(ref)
     for k in ref:
-        assert torch.equal(full[k], ref[k]), k
+        assert torch.allclose(full[k], ref[k], rtol=0, atol=1e-5), k
     p2 = DiZOProjector(pp, max_iters=2, dp_group=False)
     it = iter(range(100))
     p2.search_zo(lambda: batch(50 + next(it)), seed=9)

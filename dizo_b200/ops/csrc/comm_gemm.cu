@@ -33,6 +33,7 @@
 // always arrives by the peer's stores into local memory, then is read with local TMA loads.
 // All waits are bounded and report through the error word.
 #include "common.cuh"
+#include "cluster2sm.cuh"
 #include "host_util.h"
 #include "philox.cuh"
 
@@ -153,14 +154,15 @@ __device__ __forceinline__ bool cg_wait_flag(const uint32_t* p, uint32_t epoch, 
 }
 
 // Tiles are visited source by source, own rows first.
-__device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, int& mb, int& nb) {
+// (`bm`: rows of a tile - 128 for the one-SM kernel, 256 for the two-SM kernel)
+__device__ __forceinline__ void cg_tile_coords(int tile, const CommGemmArgs& p, const int bm, int& mb, int& nb) {
   if (p.gather == 1) {
     // own rows first; then chunk by chunk (every source pushes its chunk c to all ranks before chunk
     // c+1, so this is the order in which the rows arrive).  Inside the own block and inside a chunk
     // the walk is column-major - all row tiles of the group for one 256-column block of W, then the
     // next block - so the CTAs in flight share a few W tiles and the group's A rows instead of
     // streaming the whole of W (which exceeds L2 at small world sizes) once per row tile.
-    const int mbs = p.rows_per_src / CG_BM;          // row tiles per source
+    const int mbs = p.rows_per_src / bm;             // row tiles per source
     const int per_src = mbs * p.num_n;
     if (tile < per_src) {
       mb = p.rank * mbs + tile % mbs;
@@ -336,6 +338,127 @@ __device__ __forceinline__ void cg_push_role(const CommGemmArgs& p, uint8_t* tab
   }
 }
 
+// Drain one accumulator of this warp's 32 rows x 256 columns: bias, scale, activation, residual, then the
+// store - to the local output, or (push epilogue) staged through shared memory and sent as full-width rows
+// to the rank that owns them.  `row` is this lane's output row, `warp_row0` the first row of the warp,
+// `t_row` the TMEM address of the warp's lane quadrant in the accumulator.
+__device__ __forceinline__ void cg_drain_tile(const CommGemmArgs& p, const uint32_t t_row, const long long row,
+                                              const long long warp_row0, const int nb, const int quad,
+                                              const int lane, const uint32_t out_stage) {
+  const bool row_ok = row < p.M;
+  // destination of this row
+  __nv_bfloat16* orow_bf = nullptr;
+  float* orow_f32 = nullptr;
+  if (row_ok) {
+    if (p.push_out) {
+      int owner = (int)(row / p.rows_per_owner);
+      long long lr = row - (long long)owner * p.rows_per_owner;
+      orow_bf = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
+                (long long)p.rank * p.out_slot_stride + lr * p.ldo;
+    } else if (p.out_fp32) {
+      orow_f32 = reinterpret_cast<float*>(p.out) + row * p.ldo;
+    } else {
+      orow_bf = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo;
+    }
+  }
+#pragma unroll 1
+  for (int c = 0; c < CG_BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = nb * CG_BN + c * 32;
+    if (col0 < p.N) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    const bool full_chunk = (col0 + 32 <= p.N);
+    if (p.bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+    }
+    if (p.out_scale != 1.0f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
+    }
+    if (p.act == 1) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    } else if (p.act == 2) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+    }
+    if (row_ok) {
+      if (p.residual) {
+        const __nv_bfloat16* rp = p.residual + row * p.ldr + col0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+      }
+      if (orow_f32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if ((full_chunk || col0 + j < p.N) && DZ_STORE_OK(orow_f32 + col0 + j, 4)) orow_f32[col0 + j] = v[j];
+      } else if (p.push_out) {
+        // stage this warp's 32 rows x 128 columns (one half of the tile's width) in its own
+        // shared-memory block, 16-byte units XOR-swizzled by the row against bank conflicts
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t unit = (uint32_t)((c & 3) * 4 + q) ^ (uint32_t)(lane & 15);
+          const uint32_t addr = out_stage + quad * 8192 + lane * 256 + unit * 16;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                       "r"(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1])), "r"(pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3])),
+                       "r"(pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5])), "r"(pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]))
+                       : "memory");
+        }
+      } else if (full_chunk) {
+        uint4* op4 = reinterpret_cast<uint4*>(orow_bf + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+          o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+          o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+          o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N && DZ_STORE_OK(orow_bf + col0 + j, 2)) orow_bf[col0 + j] = __float2bfloat16(v[j]);
+      }
+    }
+    }
+    if (p.push_out && (c & 3) == 3) {
+      // drain one half of the width: the warp sends its 32 rows, two per store instruction
+      // (256 contiguous bytes each) to the rank that owns them, so the NVLink writes are
+      // full-width instead of 16-byte fragments.  Only this warp touches the block.
+      __syncwarp();
+      const int half = c >> 2;
+      const long long row0 = warp_row0;
+      const int owner = (int)(row0 / p.rows_per_owner);
+      __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
+                             (long long)p.rank * p.out_slot_stride +
+                             (row0 - (long long)owner * p.rows_per_owner) * p.ldo +
+                             (long long)nb * CG_BN + half * 128;
+      const int unit = lane & 15;
+      const int colu = nb * CG_BN + half * 128 + unit * 8;
+#pragma unroll 4
+      for (int rr = lane >> 4; rr < 32; rr += 2) {
+        if (row0 + rr < p.M && colu < p.N) {
+          const uint32_t addr = out_stage + quad * 8192 + rr * 256 + (((uint32_t)unit ^ (uint32_t)(rr & 15)) * 16);
+          uint4 o;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(addr) : "memory");
+          if (DZ_STORE_OK(obase + (long long)rr * p.ldo + unit * 8, 16))
+            *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + unit * 8) = o;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
 template <int CG_STAGES>
 __global__ void __launch_bounds__(CG_THREADS, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -400,7 +523,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t seen = 0;      // bit s set: source s is known to have arrived
       for (int tile = cta; tile < tile_end && ok; tile += n_cta) {
         int mb, nb;
-        cg_tile_coords(tile, p, mb, nb);
+        cg_tile_coords(tile, p, CG_BM, mb, nb);
         if (p.gather) {
           // every source rank that owns a row of this tile's gathered operand must have arrived
           long long r0 = p.gather == 1 ? (long long)mb * CG_BM : (long long)nb * CG_BN;
@@ -487,124 +610,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     for (int tile = cta; tile < tile_end; tile += n_cta) {
       int mb, nb;
-      cg_tile_coords(tile, p, mb, nb);
+      cg_tile_coords(tile, p, CG_BM, mb, nb);
       if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &s_abort, p.err, ERR_WAIT_TMEM_FULL))
         break;
       tc_fence_after();
       const long long row = (long long)mb * CG_BM + row_in_tile;
-      const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + acc * CG_BN + (static_cast<uint32_t>(quad * 32) << 16);
-      // destination of this row
-      __nv_bfloat16* orow_bf = nullptr;
-      float* orow_f32 = nullptr;
-      if (row_ok) {
-        if (p.push_out) {
-          int owner = (int)(row / p.rows_per_owner);
-          long long lr = row - (long long)owner * p.rows_per_owner;
-          orow_bf = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
-                    (long long)p.rank * p.out_slot_stride + lr * p.ldo;
-        } else if (p.out_fp32) {
-          orow_f32 = reinterpret_cast<float*>(p.out) + row * p.ldo;
-        } else {
-          orow_bf = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo;
-        }
-      }
-#pragma unroll 1
-      for (int c = 0; c < CG_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = nb * CG_BN + c * 32;
-        if (col0 < p.N) {
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        const bool full_chunk = (col0 + 32 <= p.N);
-        if (p.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-        }
-        if (p.out_scale != 1.0f) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
-        }
-        if (p.act == 1) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-        } else if (p.act == 2) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-        }
-        if (row_ok) {
-          if (p.residual) {
-            const __nv_bfloat16* rp = p.residual + row * p.ldr + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
-          }
-          if (orow_f32) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if ((full_chunk || col0 + j < p.N) && DZ_STORE_OK(orow_f32 + col0 + j, 4)) orow_f32[col0 + j] = v[j];
-          } else if (p.push_out) {
-            // stage this warp's 32 rows x 128 columns (one half of the tile's width) in its own
-            // shared-memory block, 16-byte units XOR-swizzled by the row against bank conflicts
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t unit = (uint32_t)((c & 3) * 4 + q) ^ (uint32_t)(lane & 15);
-              const uint32_t addr = out_stage + quad * 8192 + lane * 256 + unit * 16;
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                           "r"(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1])), "r"(pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3])),
-                           "r"(pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5])), "r"(pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]))
-                           : "memory");
-            }
-          } else if (full_chunk) {
-            uint4* op4 = reinterpret_cast<uint4*>(orow_bf + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N && DZ_STORE_OK(orow_bf + col0 + j, 2)) orow_bf[col0 + j] = __float2bfloat16(v[j]);
-          }
-        }
-        }
-        if (p.push_out && (c & 3) == 3) {
-          // drain one half of the width: the warp sends its 32 rows, two per store instruction
-          // (256 contiguous bytes each) to the rank that owns them, so the NVLink writes are
-          // full-width instead of 16-byte fragments.  Only this warp touches the block.
-          __syncwarp();
-          const int half = c >> 2;
-          const long long row0 = (long long)mb * CG_BM + quad * 32;
-          const int owner = (int)(row0 / p.rows_per_owner);
-          __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[owner]) +
-                                 (long long)p.rank * p.out_slot_stride +
-                                 (row0 - (long long)owner * p.rows_per_owner) * p.ldo +
-                                 (long long)nb * CG_BN + half * 128;
-          const int unit = lane & 15;
-          const int colu = nb * CG_BN + half * 128 + unit * 8;
-#pragma unroll 4
-          for (int rr = lane >> 4; rr < 32; rr += 2) {
-            if (row0 + rr < p.M && colu < p.N) {
-              const uint32_t addr = out_stage + quad * 8192 + rr * 256 + (((uint32_t)unit ^ (uint32_t)(rr & 15)) * 16);
-              uint4 o;
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(addr) : "memory");
-              if (DZ_STORE_OK(obase + (long long)rr * p.ldo + unit * 8, 16))
-                *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldo + unit * 8) = o;
-            }
-          }
-          __syncwarp();
-        }
-      }
+      cg_drain_tile(p, t_row, row, (long long)mb * CG_BM + quad * 32, nb, quad, lane, out_stage);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
@@ -639,6 +651,223 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Two-SM variant: a cluster of two CTAs computes one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2 (the tile engine of gemm2_sm100.cu: CTA r of the pair stages rows
+// [128 r, 128 r + 128) of the A tile and of the W tile, the leader issues the MMAs, each CTA drains
+// its own 128 accumulator rows), with the same communication roles as the one-SM kernel above: push
+// warps in the pushing CTAs, per-source waits before the first load of gathered rows (each CTA for
+// the rows it loads itself), the reduce-scatter epilogue, acks.  Row extents that change owner must
+// be multiples of 256 (all-gather) / 128 (reduce-scatter); the host falls back to the one-SM kernel
+// otherwise.  chunk_tiles counts 256-row tiles here.
+constexpr int C2_BM = 256;
+constexpr int C2_STAGES_PLAIN = 6;
+constexpr int C2_STAGES_PUSH = 5;                    // one stage makes room for the row staging
+constexpr int C2_A_BYTES = 128 * CG_BK * 2;
+constexpr int C2_B_BYTES = 128 * CG_BK * 2;
+constexpr int C2_STAGE_BYTES = C2_A_BYTES + C2_B_BYTES;
+constexpr int C2_SMEM_PLAIN = C2_STAGES_PLAIN * C2_STAGE_BYTES + CG_TABLE_BYTES + 1024;
+constexpr int C2_SMEM_PUSH = C2_STAGES_PUSH * C2_STAGE_BYTES + CG_OUT_STAGE_BYTES + 1024;
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CG_THREADS, 1)
+comm_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const CommGemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[STAGES];      // used in the leader only
+  __shared__ __align__(8) uint64_t bar_empty[STAGES];     // one per CTA
+  __shared__ __align__(8) uint64_t bar_acc_full[2];       // one per CTA
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];      // used in the leader only
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();
+  const bool leader = crank == 0;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int num_tiles = p.num_m * p.num_n;
+  const int num_kb = (p.K + CG_BK - 1) / CG_BK;
+  // tile shares in units of clusters (n_push is even: both CTAs of a pair push or neither does)
+  const int cluster_id = (int)blockIdx.x >> 1;
+  const int num_clusters = (int)gridDim.x >> 1;
+  const int push_clusters = p.n_push >> 1;
+  const bool pusher = (int)blockIdx.x < p.n_push;
+  const bool split = push_clusters > 0 && push_clusters < num_clusters && p.join_tiles != 0;
+  const int reg_tiles = (split && p.join_tiles > 0) ? num_tiles - p.join_tiles : num_tiles;
+  const int cta = !split ? cluster_id : (pusher ? reg_tiles + cluster_id : cluster_id - push_clusters);
+  const int n_cta = !split ? num_clusters : (pusher ? push_clusters : num_clusters - push_clusters);
+  const int tile_end = (split && !pusher) ? reg_tiles : num_tiles;
+  uint8_t* table_smem = smem_raw + ((smem_base - smem_u32(smem_raw)) + STAGES * C2_STAGE_BYTES);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 8);      // 4 epilogue warps x 2 CTAs
+    }
+    fence_mbar_init();
+    if (num_tiles > 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(smem_u32(&s_tmem_base), CG_TMEM_COLS);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp >= CG_GEMM_THREADS / 32) {
+    // ------------------------------------------------------------ push warps
+    if (pusher) cg_push_role(p, table_smem, (int)threadIdx.x - CG_GEMM_THREADS);
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (each CTA)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t seen = 0;
+      for (int tile = cta; tile < tile_end && ok; tile += n_cta) {
+        int mb, nb;
+        cg_tile_coords(tile, p, C2_BM, mb, nb);
+        if (p.gather) {
+          // the source ranks that own the 128 gathered rows THIS CTA loads must have arrived
+          long long r0 = (p.gather == 1 ? (long long)mb * C2_BM : (long long)nb * CG_BN) + (long long)crank * 128;
+          long long r1 = min(r0 + 128, (long long)(p.gather == 1 ? p.M : p.N));
+          bool fenced = true;
+          for (long long rr = r0; rr < r1 && ok;) {
+            long long q = p.src_period ? rr % p.src_period : rr;
+            int src = (int)(q / p.rows_per_src);
+            if (src >= p.world) src = p.world - 1;
+            const bool chunked = p.gather == 1 && p.chunk_tiles > 0;
+            const int chunk = chunked ? (int)((q % p.rows_per_src) / C2_BM) / p.chunk_tiles : 0;
+            if ((src != p.rank || p.wait_self) && (chunked || !(seen & (1u << src)))) {
+              if (!cg_wait_flag(p.ready_flags + src * CG_MAXC + chunk, p.ready_epoch, &s_abort, p.err)) {
+                ok = false;
+                break;
+              }
+              if (!chunked) seen |= 1u << src;
+              fenced = false;
+            }
+            rr += p.rows_per_src - (q % p.rows_per_src);
+          }
+          if (!ok) break;
+          if (!fenced) asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &s_abort, p.err, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = smem_u32(&bar_full[stage]);
+          const uint32_t full_leader = map_to_cta(full_local, 0);
+          const uint32_t a_dst = smem_base + stage * C2_STAGE_BYTES;
+          const uint32_t b_dst = a_dst + C2_A_BYTES;
+          if (leader) mbar_arrive_expect_tx(full_local, 2 * C2_STAGE_BYTES);   // both CTAs' bytes
+          tma_load_2d_2sm(a_dst, &tmA, full_leader, kb * CG_BK, mb * C2_BM + (int)crank * 128);
+          tma_load_2d_2sm(b_dst, &tmB, full_leader, kb * CG_BK, nb * CG_BN + (int)crank * 128);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA)
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(C2_BM, CG_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < tile_end && ok; tile += n_cta) {
+        if (!mbar_wait_cluster(smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1, &s_abort, p.err,
+                               ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * CG_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &s_abort, p.err, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * C2_STAGE_BYTES;
+          const uint32_t b_src = a_src + C2_A_BYTES;
+          const uint64_t a_desc = umma_desc_k_sw128(a_src);
+          const uint64_t b_desc = umma_desc_k_sw128(b_src);
+#pragma unroll
+          for (int k = 0; k < CG_BK / 16; ++k)
+            umma_bf16_ss_2sm(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_2sm(smem_u32(&bar_empty[stage]), 3);      // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_2sm(smem_u32(&bar_acc_full[acc]), 3);       // wakes both epilogues
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (each CTA: its 128 rows)
+    const int quad = warp & 3;
+    const uint32_t out_stage = smem_base + STAGES * C2_STAGE_BYTES;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cta; tile < tile_end; tile += n_cta) {
+      int mb, nb;
+      cg_tile_coords(tile, p, C2_BM, mb, nb);
+      if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_phase, &s_abort, p.err, ERR_WAIT_TMEM_FULL))
+        break;
+      tc_fence_after();
+      const long long warp_row0 = (long long)mb * C2_BM + (long long)crank * 128 + quad * 32;
+      const uint32_t t_row = tmem_base + acc * CG_BN + (static_cast<uint32_t>(quad * 32) << 16);
+      cg_drain_tile(p, t_row, warp_row0 + lane, warp_row0, nb, quad, lane, out_stage);
+      // this CTA's half of the accumulator is drained: tell the leader's MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (p.push_out) __threadfence_system();
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    unsigned int old = atomicAdd(p.counters + 1, 1u);
+    if (old + 1u == p.gemm_target && !s_abort) {
+      __threadfence_system();
+      if (p.push_out)
+        for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.rs_flag_ptrs[d] + p.rank, p.rs_epoch);
+      if (p.gather && p.ack_ptrs)
+        for (int d = 0; d < p.world; ++d) cg_st_release_sys(p.ack_ptrs[d] + p.rank, p.ack_epoch);
+    }
+    if (s_abort) {
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+  }
+  cluster_sync_all();          // neither CTA leaves while the other may still read its shared memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, CG_TMEM_COLS);
+  }
+}
+
 }  // namespace dz
 
 using namespace dz;
@@ -665,29 +894,46 @@ struct DzCommGemmDesc {
   long long push_elem_base[3]; const void* gauss_table;
   // bookkeeping
   int rank, world; void* counters; unsigned int push_target, gemm_target;
-  int gemm_ctas;                 // (unused)
+  int two_sm;                    // 1: run the two-SM kernel (the caller asked dz_comm_gemm_two_sm first)
   int chunk_rows;                // all-gather -> GEMM: rows per progress chunk of a source (0 = one chunk)
   int join_tiles;                // tiles at the end of the order left to the pushing CTAs (0 = no split)
 };
 
 extern "C" int dz_comm_gemm_desc_bytes() { return (int)sizeof(DzCommGemmDesc); }
 
-// CTAs of a launch of this shape with n_push pushing CTAs: one per output tile up to the SM count, and
-// at least the pushing ones.  The host keeps its completion counters in step with it.
-extern "C" int dz_comm_gemm_grid(int M, int N, int n_push) {
-  const int sms = sm_count();
-  const long long tiles = (long long)((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
-  long long g = tiles < sms ? tiles : sms;
-  if (n_push > g) g = n_push < sms ? n_push : sms;
-  return (int)g;
+// Whether a launch of this shape runs the two-SM kernel: enough 256 x 256 tiles for one wave of CTA pairs,
+// and - when rows of A arrive from peers - ownership and progress chunks in whole 256-row tiles.
+extern "C" int dz_comm_gemm_two_sm(int M, int N, int gather, int rows_per_src, int chunk_rows) {
+  if (M <= 0 || N <= 0) return 0;
+  const long long tiles = (long long)((M + C2_BM - 1) / C2_BM) * ((N + CG_BN - 1) / CG_BN);
+  if (tiles < sm_count() / 2) return 0;
+  if (gather == 1 && ((rows_per_src % C2_BM) || (chunk_rows % C2_BM))) return 0;
+  return 1;
 }
-extern "C" int dz_comm_gemm_tiles(int M, int N) {
-  return ((M + CG_BM - 1) / CG_BM) * ((N + CG_BN - 1) / CG_BN);
+extern "C" int dz_comm_gemm_tiles(int M, int N, int two_sm) {
+  const int bm = two_sm ? C2_BM : CG_BM;
+  return ((M + bm - 1) / bm) * ((N + CG_BN - 1) / CG_BN);
+}
+// CTAs of a launch of this shape with n_push pushing CTAs: one per output tile (two per 256 x 256 tile of the
+// two-SM kernel) up to the SM count, and at least the pushing ones.  The host keeps its completion counters
+// in step with it.
+extern "C" int dz_comm_gemm_grid(int M, int N, int n_push, int two_sm) {
+  const int sms = sm_count() & ~1;
+  const long long tiles = (M > 0 && N > 0) ? dz_comm_gemm_tiles(M, N, two_sm) : 0;
+  long long g = two_sm ? 2 * tiles : tiles;
+  if (g > sms) g = sms;
+  if (n_push > g) g = n_push < sms ? n_push : sms;
+  if (two_sm) g = (g + 1) & ~1ll;
+  return (int)g;
 }
 
 extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t stream) {
   if (!d) return DZ_ERR_ARG;
   const bool has_gemm = d->M > 0 && d->N > 0 && d->K > 0;
+  const bool two = has_gemm && d->two_sm &&
+                   dz_comm_gemm_two_sm(d->M, d->N, d->gather, d->rows_per_src, d->chunk_rows);
+  if (d->two_sm && !two) return DZ_ERR_ARG;
+  const int BM = two ? C2_BM : CG_BM;
   if (!has_gemm && d->n_push <= 0) return DZ_ERR_ARG;
   if (d->world <= 0 || d->world > CG_MAX_WORLD || d->rank < 0 || d->rank >= d->world) return DZ_ERR_ARG;
   CommGemmArgs a{};
@@ -696,18 +942,18 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
     if (!d->A || !d->W) return DZ_ERR_ARG;
     if ((d->K & 7) || (d->lda & 7) || (d->ldw & 7) || (d->ldo & 7)) return DZ_ERR_ALIGN;
     if (d->gather && (d->rows_per_src <= 0 || !d->ready_flags)) return DZ_ERR_ARG;
-    if (d->gather == 1 && (d->rows_per_src % CG_BM)) return DZ_ERR_ALIGN;
+    if (d->gather == 1 && (d->rows_per_src % (two ? C2_BM : CG_BM))) return DZ_ERR_ALIGN;
     if (d->push_out && (!d->out_ptrs || !d->rs_flag_ptrs || d->rows_per_owner <= 0 ||
                         (d->rows_per_owner % CG_BM) || d->out_fp32))
       return DZ_ERR_ARG;
     if (!d->push_out && !d->out) return DZ_ERR_ARG;
     if (d->push_out && (d->N & 7)) return DZ_ERR_ALIGN;
-    int rc = make_tmap_bf16_2d(&tmA, d->A, d->M, d->K, d->lda, CG_BM, CG_BK, true);
+    int rc = make_tmap_bf16_2d(&tmA, d->A, d->M, d->K, d->lda, 128, CG_BK, true);
     if (rc) return rc;
-    rc = make_tmap_bf16_2d(&tmB, d->W, d->N, d->K, d->ldw, CG_BN, CG_BK, true);
+    rc = make_tmap_bf16_2d(&tmB, d->W, d->N, d->K, d->ldw, two ? 128 : CG_BN, CG_BK, true);
     if (rc) return rc;
     a.M = d->M; a.N = d->N; a.K = d->K;
-    a.num_m = (d->M + CG_BM - 1) / CG_BM;
+    a.num_m = (d->M + BM - 1) / BM;
     a.num_n = (d->N + CG_BN - 1) / CG_BN;
   }
   if (d->n_push > 0) {
@@ -745,13 +991,13 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.push_to_self = d->push_to_self;
   if (d->chunk_rows > 0) {
     // chunks are whole row tiles, at most CG_MAXC of them per source
-    if (d->chunk_rows % CG_BM || d->push_perturb) return DZ_ERR_ARG;
+    if (d->chunk_rows % BM || d->push_perturb) return DZ_ERR_ARG;
     if (d->n_push > 0 && (d->push_rows + d->chunk_rows - 1) / d->chunk_rows > CG_MAXC) return DZ_ERR_ARG;
     if (has_gemm && d->gather == 1 &&
         (d->rows_per_src % d->chunk_rows || d->rows_per_src / d->chunk_rows > CG_MAXC))
       return DZ_ERR_ARG;
     a.push_chunk_rows = d->chunk_rows;
-    a.chunk_tiles = d->chunk_rows / CG_BM;
+    a.chunk_tiles = d->chunk_rows / BM;
   }
   a.push_flag_ptrs = (uint32_t* const*)d->push_flag_ptrs; a.push_epoch = d->push_epoch;
   a.push_wait_acks = (const uint32_t*)d->push_wait_acks; a.push_wait_epoch = d->push_wait_epoch;
@@ -760,10 +1006,13 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.rank = d->rank; a.world = d->world; a.counters = (unsigned int*)d->counters;
   a.push_target = d->push_target; a.gemm_target = d->gemm_target; a.err = err;
   if (!a.counters) return DZ_ERR_ARG;
-  static PerDeviceFlag configured;
+  static PerDeviceFlag configured, configured2p, configured2;
   if (int rc_cfg = ensure_dyn_smem(configured, comm_gemm_kernel<CG_STAGES_PUSH>, CG_SMEM_PUSH)) return rc_cfg;
+  if (int rc_cfg = ensure_dyn_smem(configured2p, comm_gemm2_kernel<C2_STAGES_PUSH>, C2_SMEM_PUSH)) return rc_cfg;
+  if (int rc_cfg = ensure_dyn_smem(configured2, comm_gemm2_kernel<C2_STAGES_PLAIN>, C2_SMEM_PLAIN)) return rc_cfg;
+  if (two) a.n_push = (a.n_push + 1) & ~1;          // both CTAs of a pair push, or neither
   // one CTA per SM at most: every CTA must be resident at once (the roles wait on one another through flags)
-  const int grid = dz_comm_gemm_grid(has_gemm ? d->M : 0, has_gemm ? d->N : 0, a.n_push);
+  const int grid = dz_comm_gemm_grid(has_gemm ? d->M : 0, has_gemm ? d->N : 0, a.n_push, two);
   if (grid < 1 || grid > sm_count() || a.n_push > grid) return DZ_ERR_TOO_LARGE;
   if (has_gemm && a.n_push > 0 && a.n_push < grid && d->join_tiles != 0) {
     // join_tiles 0: every CTA strides over all tiles; > 0: the pushing CTAs take that many tiles at the end of
@@ -771,7 +1020,11 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
     if (d->join_tiles >= a.num_m * a.num_n) return DZ_ERR_ARG;
     a.join_tiles = d->join_tiles;
   }
-  if (a.push_out)
+  if (two && a.push_out)
+    comm_gemm2_kernel<C2_STAGES_PUSH><<<grid, CG_THREADS, C2_SMEM_PUSH, stream>>>(tmA, tmB, a);
+  else if (two)
+    comm_gemm2_kernel<C2_STAGES_PLAIN><<<grid, CG_THREADS, C2_SMEM_PLAIN, stream>>>(tmA, tmB, a);
+  else if (a.push_out)
     comm_gemm_kernel<CG_STAGES_PUSH><<<grid, CG_THREADS, CG_SMEM_PUSH, stream>>>(tmA, tmB, a);
   else
     comm_gemm_kernel<CG_STAGES_PLAIN><<<grid, CG_THREADS, CG_SMEM_PLAIN, stream>>>(tmA, tmB, a);

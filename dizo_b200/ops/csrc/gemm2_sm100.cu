@@ -18,6 +18,7 @@
 // Every wait is bounded (see common.cuh); both CTAs meet at a cluster barrier before TMEM is
 // released, so neither exits while the other may still read its shared memory.
 #include "common.cuh"
+#include "cluster2sm.cuh"
 #include "host_util.h"
 
 namespace dz {
@@ -46,102 +47,6 @@ struct Gemm2Args {
   float out_scale;
   uint32_t* err;
 };
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address of the same shared-memory location in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred P1;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P1, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, P1;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag, uint32_t* err_word,
-                                                  uint32_t code) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  uint32_t spins = 0;
-  uint64_t t0 = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
-      if (*abort_flag) return false;
-      uint64_t now = global_timer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > DZ_WAIT_TIMEOUT_NS) {
-        *abort_flag = 1;
-        if (err_word) atomicCAS(err_word, 0u, code | (blockIdx.x << 8));
-        return false;
-      }
-    }
-  }
-  return true;
-}
-// 2-D tiled load into this CTA's shared memory whose completion bytes are credited to an
-// mbarrier that may live in the peer CTA (cluster address).  Not a multicast.
-__device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap* m,
-                                                uint32_t bar_cluster_addr, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_2sm(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_2sm() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16_ss_2sm(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                                 uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrive on the barrier at the same offset in every CTA of `mask` once the MMAs issued so
-// far have completed.
-__device__ __forceinline__ void umma_commit_2sm(uint32_t bar, uint16_t mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-      "[%0], %1;"
-      ::"r"(bar), "h"(mask)
-      : "memory");
-}
 
 __device__ __forceinline__ void tile_coords2(int tile, const Gemm2Args& p, int& mb, int& nb) {
   int tiles_per_group = p.group_m * p.num_n;

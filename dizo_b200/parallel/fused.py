@@ -57,7 +57,7 @@ class _Desc(ctypes.Structure):
         ("push_perturb", c_int), ("push_seed", ctypes.c_ulonglong), ("push_coef", c_float),
         ("push_tensor_id", c_int * 3), ("push_elem_base", c_ll * 3), ("gauss_table", c_void),
         ("rank", c_int), ("world", c_int), ("counters", c_void), ("push_target", c_uint),
-        ("gemm_target", c_uint), ("gemm_ctas", c_int), ("chunk_rows", c_int), ("join_tiles", c_int),
+        ("gemm_target", c_uint), ("two_sm", c_int), ("chunk_rows", c_int), ("join_tiles", c_int),
     ]
 
 
@@ -89,6 +89,7 @@ class FusedComm:
         total = 2 * ag_bytes + 2 * rs_bytes + 2 * w_bytes + 64 * 1024 + 8 * norm_slots * (self.world + 1)
         self.region = SymmRegion(total + 16 * 4096, self.group, device)
         self.device = self.region.device
+        self.two_sm = True            # use the two-SM (256 x 256 tile) kernel where the shape allows it
         self.push_ctas = 0            # pushing CTAs per launch; 0 = by the number of ranks (see _push_plan)
         self.push_share = 0.0         # their share of a normal CTA's output tiles (0 = they only push)
         self.ag = [_Channel(self.region, ag_bytes) for _ in range(2)] if ag_bytes else []
@@ -110,7 +111,7 @@ class FusedComm:
         self._dbg_out = None
 
     # ------------------------------------------------------------------ helpers
-    def _push_plan(self, d: _Desc, M: int, N: int, consumer_waits: bool) -> tuple[int, int]:
+    def _push_plan(self, d: _Desc, M: int, N: int, consumer_waits: bool, two: int = 0) -> tuple[int, int]:
         """(CTAs that push, ``join_tiles``: tiles left to them; -1 = none, 0 = a full share).
 
         Measured policy.  Two ranks: every CTA pushes (one destination, half of the bytes stay local; the
@@ -120,19 +121,22 @@ class FusedComm:
         L = _lib.lib()
         if M <= 0:
             return min(_SM_COUNT, 96), 0                                    # push only
-        grid0 = L.dz_comm_gemm_grid(M, N, 0)
+        grid0 = L.dz_comm_gemm_grid(M, N, 0, two)
         n = self.push_ctas if self.push_ctas > 0 else (grid0 if self.world <= 2 else 16)
         n = max(1, min(n, _SM_COUNT))
+        if two:
+            n = min((n + 1) & ~1, _SM_COUNT & ~1)      # CTA pairs push together
         if n >= grid0:
             return n, 0
-        tiles = L.dz_comm_gemm_tiles(M, N)
+        tiles = L.dz_comm_gemm_tiles(M, N, two)
+        units, push_units = (grid0 // 2, n // 2) if two else (grid0, n)     # CTAs or CTA pairs that take tiles
         f = self.push_share
         if f <= 0.0:
             return n, -1
-        g = grid0 - n
-        if f >= 1.0 or tiles <= grid0:
+        g = units - push_units
+        if f >= 1.0 or tiles <= units:
             return n, 0
-        return n, max(1, min(int(tiles * n * f / (g + n * f)), tiles - 1))
+        return n, max(1, min(int(tiles * push_units * f / (g + push_units * f)), tiles - 1))
 
     def _launch(self, d: _Desc, push: bool, M: int, N: int, consumer_waits: bool = True) -> None:
         L = _lib.lib()
@@ -141,9 +145,11 @@ class FusedComm:
         d.counters = self.counters.data_ptr()
         # the first n_push CTAs carry a slice of the push (four extra warps beside their GEMM warps); every CTA
         # of any launch reports its completion: the counters advance by the pushing CTAs / the grid size
-        n_push, join = self._push_plan(d, M, N, consumer_waits) if push else (0, 0)
-        grid = L.dz_comm_gemm_grid(M, N, n_push)
-        d.n_push, d.join_tiles = n_push, join
+        two = int(self.two_sm and M > 0 and
+                  L.dz_comm_gemm_two_sm(M, N, d.gather, d.rows_per_src, d.chunk_rows))
+        n_push, join = self._push_plan(d, M, N, consumer_waits, two) if push else (0, 0)
+        grid = L.dz_comm_gemm_grid(M, N, n_push, two)
+        d.n_push, d.join_tiles, d.two_sm = n_push, join, two
         if push:
             self._push_total += n_push
             d.push_target = self._push_total & 0xFFFFFFFF
@@ -201,10 +207,12 @@ class FusedComm:
         d.push_dst_row0[0] = self.rank * rows
         d.push_flag_ptrs, d.push_epoch = ch.ready_ptrs.data_ptr(), ch.epoch
         d.push_wait_acks, d.push_wait_epoch = ch.ack.data_ptr(), prev
-        # progress chunks: whole 128-row tiles, as fine as the flag words allow
-        tiles = rows // 128
+        # progress chunks: whole row tiles (256 rows where the two-SM kernel can run, else 128), as fine as
+        # the flag words allow
+        unit = 256 if (self.two_sm and rows % 256 == 0) else 128
+        tiles = rows // unit
         ct = next(c for c in range(1, tiles + 1) if tiles % c == 0 and tiles // c <= MAX_CHUNKS)
-        d.chunk_rows = ct * 128 if self.world > 2 and tiles > 1 else 0
+        d.chunk_rows = ct * unit if self.world > 2 and tiles > 1 else 0
         self._launch(d, True, M, N)
         return out
 

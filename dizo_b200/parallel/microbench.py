@@ -49,6 +49,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--push-ctas", dest="n_push", type=int, default=0,
                     help="CTAs whose push warps are active (0 = the default policy for this number of ranks)")
+    ap.add_argument("--one-sm", action="store_true", help="keep the fused launches on the one-SM tile kernel")
     ap.add_argument("--push-share", type=float, default=0.0,
                     help="output tiles of a pushing CTA relative to the others (0 = it only pushes)")
     a = ap.parse_args()
@@ -61,7 +62,7 @@ def main():
     M, d, F = a.m, a.d, a.ffn
     Fl, rows = F // world, M // world
     fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2)
-    fc.push_ctas, fc.push_share = a.n_push, a.push_share
+    fc.push_ctas, fc.push_share, fc.two_sm = a.n_push, a.push_share, not a.one_sm
     g = torch.Generator(device=dev).manual_seed(1)
     x_local = torch.randn(rows, d, device=dev, generator=g).bfloat16()
     w1 = (torch.randn(Fl, d, device=dev, generator=g) * 0.02).bfloat16()
@@ -79,7 +80,8 @@ def main():
                     "speedup": base_ms / fused_ms, "roofline_ms": floor_ms,
                     "fraction_of_roofline": floor_ms / fused_ms,
                     "tflops_per_gpu": flops / fused_ms / 1e9, "hidden": d,
-                    "push_ctas": a.n_push or ("all" if world <= 2 else 16), "push_share": a.push_share})
+                    "push_ctas": a.n_push or ("all" if world <= 2 else 16), "push_share": a.push_share,
+                    "tile_kernel": "one-SM" if a.one_sm else "two-SM"})
 
     # ---- TP: all-gather -> GEMM (fc1 shape)
     def fused_ag():

@@ -24,10 +24,12 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
-    M, d, F = 256 * world, 1024, 2048
-    fc = FusedComm(ag_bytes=M * d * 2, rs_bytes=M * d * 2, w_bytes=F * d * 2, n_push=8)
+    # two shape sets: a small one (one-SM tile kernel) and one with enough 256 x 256 tiles and 256-row ownership
+    # blocks for the two-SM kernel (cta_group::2) to take every fused launch
+    cases = [(256 * world, 1024, 2048, 384, 640), (1024 * world, 2560, 2560 * world, 1024, 2560)]
+    Mx, dx, Fx = cases[-1][:3]
+    fc = FusedComm(ag_bytes=Mx * dx * 2, rs_bytes=Mx * dx * 2, w_bytes=max(Fx, 3 * cases[-1][4]) * dx * 2, n_push=8)
     g = torch.Generator(device=dev).manual_seed(1234)          # same stream on every rank
-    rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
 
     # ---- barrier + norm all-reduce fused with the gamma arithmetic
     fc.barrier()
@@ -42,6 +44,25 @@ def main():
         assert torch.allclose(gs.ts, want.sqrt()) and torch.allclose(gs.gamma, want.sqrt())
         assert torch.allclose(gs.alpha, torch.ones_like(gs.alpha), atol=1e-6)
 
+    L = _lib.lib()
+    for case, (M, d, F, xs_rows, dq) in enumerate(cases):
+        two = [L.dz_comm_gemm_two_sm(M, F // world, 1, M // world, 0), L.dz_comm_gemm_two_sm(M, d, 0, 0, 0),
+               L.dz_comm_gemm_two_sm(xs_rows, F, 2, F // world, 0)]
+        assert two == ([0, 0, 0] if case == 0 else [1, 1, 1]), (case, two)
+        run_case(fc, g, dev, rank, world, M, d, F, xs_rows, dq)
+
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    dist.barrier()
+    report = fc.protocol_report()            # every ready / ack / partial-sum word agrees with the launches issued
+    assert not report, report
+    if rank == 0:
+        print("FUSED_OK world", world)
+    dist.destroy_process_group()
+
+
+def run_case(fc, g, dev, rank, world, M, d, F, xs_rows, dq):
+    rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
     # ---- tensor parallel: all-gather -> GEMM, GEMM -> reduce-scatter (+ residual + LayerNorm)
     x_all = torch.randn(M, d, device=dev, generator=g).bfloat16()
     w1 = (torch.randn(F, d, device=dev, generator=g) * 0.03).bfloat16()      # fc1, rows sharded
@@ -73,7 +94,7 @@ def main():
         assert rel(z, z_ref) < 1e-2, ("rs_ln", rep, rel(z, z_ref))
 
     # ---- FSDP: shard push fused with the perturbation and the consuming GEMM
-    xs = torch.randn(384, d, device=dev, generator=g).bfloat16()
+    xs = torch.randn(xs_rows, d, device=dev, generator=g).bfloat16()
     shard = w1[rank * Fl:(rank + 1) * Fl].contiguous()
     z_full = torch.from_numpy(philox.gaussian(77, 9, F * d)).view(F, d).to(dev)
     w_pert = perturb_reference(w1, 1e-2, z_full)
@@ -93,9 +114,8 @@ def main():
         # the pushed shard is the packed bf16 fma of the staging sweep: equal to the host statement bit for bit
         assert torch.equal(got, w_pert), ("fsdp gather+perturb", rep)
         assert rel(out, ref) < 1e-3, ("fsdp_gemm", rep, rel(out, ref))
-    # fused q|k|v: three segments in one push, ownership repeating every d rows, tiles that
-    # straddle two owners (rows_per_src = d / world is not a multiple of the 256-row tile)
-    dq = 640
+    # fused q|k|v: three segments in one push, ownership repeating every dq rows, tiles that
+    # straddle two owners (rows_per_src = dq / world need not be a multiple of the 256-row tile)
     wq = [(torch.randn(dq, d, device=dev, generator=g) * 0.03).bfloat16() for _ in range(3)]
     rq = dq // world
     segs = [dict(w_shard=wq[j][rank * rq:(rank + 1) * rq].contiguous(), dst_row0=j * dq + rank * rq,
@@ -108,15 +128,6 @@ def main():
     w_qkv = torch.cat([perturb_reference(wq[j], -1e-2, zq[j]) for j in range(3)])
     assert torch.equal(fc.fsdp_weight(slot, 3 * dq, d), w_qkv)
     assert rel(out, linear(xs, w_qkv)) < 2e-3, rel(out, linear(xs, w_qkv))
-
-    torch.cuda.synchronize()
-    _lib.check_device_errors()
-    dist.barrier()
-    report = fc.protocol_report()            # every ready / ack / partial-sum word agrees with the launches issued
-    assert not report, report
-    if rank == 0:
-        print("FUSED_OK world", world)
-    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

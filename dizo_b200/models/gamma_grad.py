@@ -22,11 +22,13 @@ is computed without autograd and without a weight gradient:
   data-gradient GEMMs read the same staging slot after a peer barrier (second gather, in reverse
   layer order), and ``theta - theta_0`` of the k / v shards travels the same way.
 
-Covered: full-parameter and LoRA modes of every OPT size (pre- and post-LayerNorm, with or without
-``project_in/out``, ReLU), replicated or FSDP-sharded (full-parameter).  Prefix rows in the attention
-backward are not covered (LoRA + prefix uses the autograd statement in
-:mod:`dizo_b200.models.opt_autograd`).  CPU tensors run the same orchestration over the PyTorch
-statements of the ops, which is how the CPU suite checks it against autograd.
+* prefix rows (LoRA + prefix; the prefix tensors themselves are never constrained) enter as extra key
+  columns of the attention backward: the tiled kernel differentiates the sequence keys with the forward's
+  log-sum-exp, which already covers the prefix columns, and a small kernel adds their share of dQ.
+
+Covered: full-parameter, LoRA and LoRA + prefix modes of every OPT size (pre- and post-LayerNorm, with or
+without ``project_in/out``, ReLU), replicated or FSDP-sharded (full-parameter).  CPU tensors run the same
+orchestration over the PyTorch statements of the ops, which is how the CPU suite checks it against autograd.
 """
 from __future__ import annotations
 
@@ -50,7 +52,7 @@ def supported(model: OPTModel) -> bool:
         return False
     if _is_fsdp(model):
         return model.mode == "full"
-    return model.mode in ("full", "lora") and type(model).hidden_states is OPTModel.hidden_states
+    return model.mode in ("full", "lora", "lora+prefix") and type(model).hidden_states is OPTModel.hidden_states
 
 
 # ---------------------------------------------------------------------------------- weight access
@@ -154,14 +156,15 @@ class GammaGrad:
         self.prov = _FSDP(model) if _is_fsdp(model) else _Replicated(model)
 
     # ------------------------------------------------------------------ helpers
-    def _attention(self, qkv, B, L, pad_left):
+    def _attention(self, qkv, B, L, pad_left, w):
         """context and the saved statistic (None on CPU: the CPU backward uses autograd)."""
         H = self.model.config.num_attention_heads
+        pk, pv = getattr(w, "prefix_k", None), getattr(w, "prefix_v", None)
         if qkv.is_cuda:
             lse = torch.empty((B, H, L), dtype=torch.float32, device=qkv.device)
-            ctx = attn_ops.attention(qkv.view(B, L, -1), H, pad_left, lse=lse)
+            ctx = attn_ops.attention(qkv.view(B, L, -1), H, pad_left, pk, pv, lse=lse)
             return ctx, lse
-        return attn_ops.attention(qkv.view(B, L, -1), H, pad_left), None
+        return attn_ops.attention(qkv.view(B, L, -1), H, pad_left, pk, pv), None
 
     # ------------------------------------------------------------------ loss tail
     def _tail(self, h2: torch.Tensor, batch: Batch, gget):
@@ -269,7 +272,7 @@ class GammaGrad:
             w = P.stage(i, tr, 0)
             x1 = norm.layernorm(h, w.ln1_w, w.ln1_b, eps) if pre else h
             qkv = P.linear(w, "qkv", x1)
-            ctx, lse = self._attention(qkv, B, L, batch.pad_left)
+            ctx, lse = self._attention(qkv, B, L, batch.pad_left, w)
             r1 = P.linear(w, "out", ctx.view(M, d), residual=h)
             h_mid = r1 if pre else norm.layernorm(r1, w.ln1_w, w.ln1_b, eps)
             x2 = norm.layernorm(h_mid, w.ln2_w, w.ln2_b, eps) if pre else h_mid
@@ -300,12 +303,13 @@ class GammaGrad:
                 del df
                 dr1 = bw.layernorm_backward(dh_mid, r1, w.ln1_w, eps)
             dctx = P.dgrad(w, "out", dr1)
+            pk, pv = getattr(w, "prefix_k", None), getattr(w, "prefix_v", None)
             if qkv.is_cuda:
                 dqkv = attn_ops.attention_backward(qkv.view(B, L, 3 * d), ctx.view(B, L, d), dctx.view(B, L, d),
-                                                   lse, H, batch.pad_left).view(M, 3 * d)
+                                                   lse, H, batch.pad_left, prefix_k=pk, prefix_v=pv).view(M, 3 * d)
             else:
                 dqkv = attn_ops.attention_backward_reference(qkv.view(B, L, 3 * d), dctx.view(B, L, d), H,
-                                                             batch.pad_left).view(M, 3 * d)
+                                                             batch.pad_left, prefix_k=pk, prefix_v=pv).view(M, 3 * d)
             self._alpha_grads(w, x1, dqkv, grad)
             if i > 0:                     # nothing below the first block depends on a constrained tensor
                 if pre:

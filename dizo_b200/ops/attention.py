@@ -92,26 +92,42 @@ def attention(qkv: torch.Tensor, n_heads: int, pad_left: torch.Tensor | None = N
 
 
 def attention_backward_reference(qkv: torch.Tensor, dout: torch.Tensor, n_heads: int,
-                                 pad_left: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
-    """d loss / d qkv for d loss / d context = ``dout``: autograd through the fp32 statement."""
+                                 pad_left: torch.Tensor | None = None, scale: float | None = None,
+                                 prefix_k: torch.Tensor | None = None, prefix_v: torch.Tensor | None = None,
+                                 d_prefix: tuple | None = None) -> torch.Tensor:
+    """d loss / d qkv for d loss / d context = ``dout``: autograd through the fp32 statement.  ``d_prefix``:
+    optional pair of fp32 [P, d] tensors that receive the gradients of the prefix keys / values."""
     with torch.enable_grad():
         x = qkv.detach().float().requires_grad_(True)
-        o = attention_reference(x, n_heads, pad_left, None, None, scale)
-        (g,) = torch.autograd.grad(o, x, dout.float())
-    return g.to(qkv.dtype)
+        leaves = [x]
+        pk = pv = None
+        if prefix_k is not None:
+            pk, pv = prefix_k.detach().float().requires_grad_(True), prefix_v.detach().float().requires_grad_(True)
+            leaves += [pk, pv]
+        o = attention_reference(x, n_heads, pad_left, pk, pv, scale)
+        grads = torch.autograd.grad(o, leaves, dout.float())
+    if d_prefix is not None:
+        d_prefix[0].copy_(grads[1])
+        d_prefix[1].copy_(grads[2])
+    return grads[0].to(qkv.dtype)
 
 
 def attention_backward(qkv: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor,
                        n_heads: int, pad_left: torch.Tensor | None = None, scale: float | None = None,
-                       dqkv: torch.Tensor | None = None) -> torch.Tensor:
-    """Gradient of :func:`attention` (no prefix rows): qkv [B, L, 3d], its context ``out`` and
-    ``dout`` [B, L, d] (bf16), ``lse`` from the forward -> dqkv [B, L, 3d] bf16 (dQ | dK | dV).
+                       dqkv: torch.Tensor | None = None, prefix_k: torch.Tensor | None = None,
+                       prefix_v: torch.Tensor | None = None, d_prefix: tuple | None = None) -> torch.Tensor:
+    """Gradient of :func:`attention`: qkv [B, L, 3d], its context ``out`` and ``dout`` [B, L, d] (bf16),
+    ``lse`` from the forward -> dqkv [B, L, 3d] bf16 (dQ | dK | dV).  With prefix rows (``prefix_k/v``
+    [P, d], the ones the forward saw) their share of dQ is added, and ``d_prefix`` - a pair of zeroed fp32
+    [P, d] tensors - receives the gradients of the prefix keys and values when given.
 
-    CUDA: the two tcgen05 passes of ``csrc/attn_bwd_sm100.cu``.  Replaces the autograd pass over
-    the reference's eager attention (large_models/ht_opt.py:209-272) in the first-order gamma
-    search (large_models/trainer.py:714-741)."""
+    CUDA: the two tcgen05 passes of ``csrc/attn_bwd_sm100.cu`` over the sequence keys; because the
+    forward's log-sum-exp and D = rowsum(dO * O) cover the prefix columns too, those separate exactly and a
+    small kernel (``attn_prefix_bwd_kernel``) handles them.  Replaces the autograd pass over the
+    reference's eager attention (large_models/ht_opt.py:209-272) in the first-order gamma search
+    (large_models/trainer.py:714-741)."""
     if not qkv.is_cuda:
-        return attention_backward_reference(qkv, dout, n_heads, pad_left, scale)
+        return attention_backward_reference(qkv, dout, n_heads, pad_left, scale, prefix_k, prefix_v, d_prefix)
     B, L, d3 = qkv.shape
     d = d3 // 3
     hd = d // n_heads
@@ -124,12 +140,26 @@ def attention_backward(qkv: torch.Tensor, out: torch.Tensor, dout: torch.Tensor,
         dqkv = torch.empty((B, L, 3 * d), dtype=torch.bfloat16, device=qkv.device)
     assert dqkv.stride(-1) == 1 and dqkv.stride(0) == L * dqkv.stride(1)
     dsum = torch.empty((B, n_heads, L), dtype=torch.float32, device=qkv.device)
+    ll = ctypes.c_longlong
     rc = _lib.lib().dz_attn_bwd(
-        _lib.ptr(qkv), ctypes.c_longlong(qkv.stride(1)), 0, d, 2 * d,
-        _lib.ptr(out), _lib.ptr(dout), ctypes.c_longlong(d), _lib.ptr(lse), _lib.ptr(dsum),
-        _lib.ptr(dqkv), ctypes.c_longlong(dqkv.stride(1)), _lib.ptr(pad_left),
+        _lib.ptr(qkv), ll(qkv.stride(1)), 0, d, 2 * d,
+        _lib.ptr(out), _lib.ptr(dout), ll(d), _lib.ptr(lse), _lib.ptr(dsum),
+        _lib.ptr(dqkv), ll(dqkv.stride(1)), _lib.ptr(pad_left),
         B, L, n_heads, hd, ctypes.c_float(scale), _lib.ptr(_lib.err_word(qkv.device)), _lib.stream_ptr())
     _lib.check(rc, "dz_attn_bwd")
+    if prefix_k is not None:
+        assert prefix_k.dtype == torch.bfloat16 and prefix_k.stride(-1) == 1 and prefix_v.stride(0) == prefix_k.stride(0)
+        dpk = dpv = None
+        if d_prefix is not None:
+            dpk, dpv = d_prefix
+            assert dpk.dtype == torch.float32 and dpk.is_contiguous() and dpk.shape == (prefix_k.shape[0], d)
+            assert dpv.dtype == torch.float32 and dpv.is_contiguous() and dpv.shape == dpk.shape
+        rc = _lib.lib().dz_attn_prefix_bwd(
+            _lib.ptr(qkv), ll(qkv.stride(1)), _lib.ptr(dout), ll(d), _lib.ptr(prefix_k), _lib.ptr(prefix_v),
+            ll(prefix_k.stride(0)), prefix_k.shape[0], _lib.ptr(lse), _lib.ptr(dsum), _lib.ptr(dqkv),
+            ll(dqkv.stride(1)), _lib.ptr(dpk), _lib.ptr(dpv), ll(d), B, L, n_heads, hd, ctypes.c_float(scale),
+            _lib.stream_ptr())
+        _lib.check(rc, "dz_attn_prefix_bwd")
     return dqkv
 
 

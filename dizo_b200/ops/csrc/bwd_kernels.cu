@@ -180,6 +180,69 @@ __global__ void diff_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bflo
   }
 }
 
+// Prefix rows of the attention backward.  The prefix keys / values are extra key columns that every query sees
+// (no mask).  With the forward's log-sum-exp (which covers them) and D = rowsum(dO * O) of the full context,
+// their part of the gradient separates from the tiled kernel's:  p = exp2(c q.k_p - lse),  ds = p (dO.v_p - D),
+// dQ += scale ds k_p,  dK_p += scale ds q,  dV_p += p dO.  One warp per (batch row, query, head).
+__global__ void __launch_bounds__(128)
+attn_prefix_bwd_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __nv_bfloat16* __restrict__ dout,
+                       long long lddo, const __nv_bfloat16* __restrict__ pk, const __nv_bfloat16* __restrict__ pv,
+                       long long ldp, int npre, const float* __restrict__ lse, const float* __restrict__ dsum,
+                       __nv_bfloat16* __restrict__ dq, long long lddq, float* __restrict__ dpk,
+                       float* __restrict__ dpv, long long lddp, int B, int L, int H, int hd, float scale) {
+  const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)B * L * H) return;
+  const int h = (int)(wid % H);
+  const long long row = wid / H;                  // b * L + i
+  const long long b = row / L, i = row - b * L;
+  const float my_lse = lse[(b * H + h) * L + i], my_d = dsum[(b * H + h) * L + i];
+  const float c = scale * 1.4426950408889634f;
+  float qv[4], gv[4], acc[4];                     // head sizes up to 128: four elements per lane
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int e = lane + 32 * t;
+    qv[t] = e < hd ? __bfloat162float(q[row * ldq + h * hd + e]) : 0.f;
+    gv[t] = e < hd ? __bfloat162float(dout[row * lddo + h * hd + e]) : 0.f;
+    acc[t] = 0.f;
+  }
+  for (int p = 0; p < npre; ++p) {
+    float kv[4], vv[4], s = 0.f, dp = 0.f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int e = lane + 32 * t;
+      kv[t] = e < hd ? __bfloat162float(pk[p * ldp + h * hd + e]) : 0.f;
+      vv[t] = e < hd ? __bfloat162float(pv[p * ldp + h * hd + e]) : 0.f;
+      s += qv[t] * kv[t];
+      dp += gv[t] * vv[t];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      dp += __shfl_xor_sync(0xffffffffu, dp, o);
+    }
+    const float prob = exp2f(s * c - my_lse);
+    const float ds = prob * (dp - my_d) * scale;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int e = lane + 32 * t;
+      acc[t] += ds * kv[t];
+      if (dpk && e < hd) {
+        atomicAdd(dpk + p * lddp + h * hd + e, ds * qv[t]);
+        atomicAdd(dpv + p * lddp + h * hd + e, prob * gv[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int e = lane + 32 * t;
+    if (e < hd) {
+      __nv_bfloat16* o = dq + row * lddq + h * hd + e;
+      if (DZ_STORE_OK(o, 2)) *o = __float2bfloat16(__bfloat162float(*o) + acc[t]);
+    }
+  }
+}
+
 static inline bool bk_al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace dz
@@ -247,5 +310,23 @@ extern "C" int dz_diff_bf16(const void* a, const void* b, void* out, long long n
   if (blocks > 148 * 8) blocks = 148 * 8;
   diff_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                                     (__nv_bfloat16*)out, nvec);
+  return cuda_rc(cudaGetLastError());
+}
+
+// Adds the prefix rows' part of the attention gradient to dq (bf16 [B*L, lddq], the dQ block that dz_attn_bwd
+// wrote) and, when dpk / dpv are given (fp32 [npre, lddp], zeroed by the caller; atomics), accumulates the
+// prefix rows' own gradients.  q / dout: bf16 [B*L, ld]; pk / pv: bf16 [npre, ldp]; lse and dsum as dz_attn_bwd.
+extern "C" int dz_attn_prefix_bwd(const void* q, long long ldq, const void* dout, long long lddo, const void* pk,
+                                  const void* pv, long long ldp, int npre, const float* lse, const float* dsum,
+                                  void* dq, long long lddq, float* dpk, float* dpv, long long lddp, int B, int L,
+                                  int H, int hd, float scale, cudaStream_t stream) {
+  if (!q || !dout || !pk || !pv || !lse || !dsum || !dq || B <= 0 || L <= 0 || H <= 0 || npre <= 0)
+    return DZ_ERR_ARG;
+  if (hd <= 0 || hd > 128 || (dpk == nullptr) != (dpv == nullptr)) return DZ_ERR_ARG;
+  const long long warps = (long long)B * L * H;
+  if ((warps + 3) / 4 > 0x7fffffffLL) return DZ_ERR_TOO_LARGE;
+  attn_prefix_bwd_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(
+      (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)dout, lddo, (const __nv_bfloat16*)pk,
+      (const __nv_bfloat16*)pv, ldp, npre, lse, dsum, (__nv_bfloat16*)dq, lddq, dpk, dpv, lddp, B, L, H, hd, scale);
   return cuda_rc(cudaGetLastError());
 }

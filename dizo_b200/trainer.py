@@ -345,7 +345,7 @@ class OurTrainer:
         if a.enhanced == "fo":
             from .models import gamma_grad
             if not gamma_grad.supported(self.model):
-                # configurations the kernel backward does not cover (prefix rows): autograd statement
+                # configurations the kernel backward does not cover (GELU blocks, sharded LoRA): autograd statement
                 from .models.opt_autograd import make_fo_loss
                 fo_loss = make_fo_loss(self.model)
         self._dizo_seed_rng = np.random.RandomState(a.seed + 7919)

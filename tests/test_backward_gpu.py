@@ -87,6 +87,33 @@ def test_attention_backward_left_pad(hd):
     assert _rel(dqkv, ref) < 2e-2
 
 
+@pytest.mark.parametrize("hd", [64, 80, 128])
+def test_attention_backward_prefix_rows(hd):
+    """Prefix keys / values as extra, unmasked key columns: dQ | dK | dV and the prefix rows' own gradients."""
+    B, L, H, P = 2, 200, 4, 5
+    d = H * hd
+    g = torch.Generator(device=DEV).manual_seed(100 + hd)
+    qkv = torch.randn(B, L, 3 * d, device=DEV, generator=g).bfloat16()
+    pk = torch.randn(P, d, device=DEV, generator=g).bfloat16()
+    pv = torch.randn(P, d, device=DEV, generator=g).bfloat16()
+    pad = torch.tensor([0, 33], dtype=torch.int32, device=DEV)
+    dout = torch.randn(B, L, d, device=DEV, generator=g).bfloat16()
+    dout[1, :33] = 0
+    lse = torch.empty(B, H, L, dtype=torch.float32, device=DEV)
+    out = attention(qkv, H, pad_left=pad, prefix_k=pk, prefix_v=pv, lse=lse)
+    dp = (torch.zeros(P, d, device=DEV), torch.zeros(P, d, device=DEV))
+    dqkv = attention_backward(qkv, out, dout, lse, H, pad_left=pad, prefix_k=pk, prefix_v=pv, d_prefix=dp)
+    _sync_ok()
+    rp = (torch.zeros(P, d, device=DEV), torch.zeros(P, d, device=DEV))
+    ref = attention_backward_reference(qkv, dout, H, pad_left=pad, prefix_k=pk, prefix_v=pv, d_prefix=rp)
+    for name, sl in (("dq", slice(0, d)), ("dk", slice(d, 2 * d)), ("dv", slice(2 * d, 3 * d))):
+        assert _rel(dqkv[..., sl], ref[..., sl]) < 2e-2, (name, _rel(dqkv[..., sl], ref[..., sl]))
+    assert _rel(dp[0], rp[0]) < 2e-2 and _rel(dp[1], rp[1]) < 2e-2, (_rel(dp[0], rp[0]), _rel(dp[1], rp[1]))
+    # the prefix rows matter: leaving them out of the backward must show
+    no_prefix = attention_backward(qkv, out, dout, lse, H, pad_left=pad)
+    assert _rel(no_prefix[..., :d], ref[..., :d]) > 5e-2
+
+
 @pytest.mark.parametrize("rows,d", [(7, 768), (300, 2560), (64, 5120), (5, 9216)])
 def test_layernorm_backward(rows, d):
     g = torch.Generator(device=DEV).manual_seed(d)
@@ -183,7 +210,7 @@ def test_gamma_grad_kernel_backward_matches_autograd(kind):
     assert _rel(grad, a.grad) < 0.2
 
 
-@pytest.mark.parametrize("variant", ["lora", "post_ln"])
+@pytest.mark.parametrize("variant", ["lora", "lora+prefix", "post_ln"])
 def test_gamma_grad_kernel_backward_other_layouts(variant):
     """The kernel backward for LoRA (the adapter factors are the constrained tensors: rank-8 GEMMs)
     and for the post-LayerNorm layout with project_in / project_out (opt-350m), against autograd."""
@@ -193,9 +220,9 @@ def test_gamma_grad_kernel_backward_other_layouts(variant):
     from dizo_b200.models.opt import OPTModel, preset
     from dizo_b200.models.opt_autograd import make_fo_loss
 
-    if variant == "lora":
+    if variant.startswith("lora"):
         cfg = preset("opt-125m", num_hidden_layers=4)
-        m = OPTModel(cfg, DEV, torch.bfloat16, mode="lora").init_random_fast(seed=0)
+        m = OPTModel(cfg, DEV, torch.bfloat16, mode=variant).init_random_fast(seed=0)
         scale = 0.05
     else:
         cfg = preset("opt-350m", num_hidden_layers=4)

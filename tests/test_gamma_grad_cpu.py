@@ -45,8 +45,8 @@ def test_supported_flags():
     cfg, m, _ = _model()
     assert supported(m)
     assert supported(OPTModel(cfg, "cpu", torch.float32, mode="lora"))
-    # prefix rows are not covered by the attention backward; GELU has no fused backward mask
-    assert not supported(OPTModel(cfg, "cpu", torch.float32, mode="lora+prefix"))
+    assert supported(OPTModel(cfg, "cpu", torch.float32, mode="lora+prefix"))
+    # GELU has no fused backward mask
     assert not supported(OPTModel(preset("opt-tiny", activation_function="gelu"), "cpu", torch.float32))
 
 
@@ -75,6 +75,21 @@ def test_lora_factors_gamma_grad_matches_autograd():
     g = torch.Generator().manual_seed(3)
     for n in m.arena.slot_names:                       # A and B leave their anchors (B_0 = 0)
         m.param(n).add_(torch.randn(m.param(n).shape, generator=g) * 0.05)
+    _check_against_autograd(m, proj, cfg)
+
+
+def test_lora_with_prefix_rows_gamma_grad_matches_autograd():
+    """LoRA + prefix: the prefix rows are extra key columns of the attention and of its backward."""
+    cfg = preset("opt-tiny")
+    m = OPTModel(cfg, "cpu", torch.float32, mode="lora+prefix", lora_r=8, num_prefix=3).init_random(seed=0, std=0.05)
+    proj = DiZOProjector(m)
+    assert proj.n == 4 * cfg.num_hidden_layers and supported(m)
+    g = torch.Generator().manual_seed(3)
+    for n in m.arena.slot_names:
+        m.param(n).add_(torch.randn(m.param(n).shape, generator=g) * 0.05)
+    for n in m.trainable_names:
+        if "prefix_" in n:
+            m.param(n).copy_(torch.randn(m.param(n).shape, generator=g) * 0.3)
     _check_against_autograd(m, proj, cfg)
 
 

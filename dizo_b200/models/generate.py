@@ -84,50 +84,21 @@ class _Decoder:
 
     def step(self, tokens: torch.Tensor, positions: torch.Tensor, pad_left: torch.Tensor) -> torch.Tensor:
         """tokens, positions: int32 [B]; returns the next-token logits [B, V] (fp32)."""
-        m, cfg = self.m, self.m.config
-        d = cfg.hidden_size
-        get = m._resolver(-1, None, None, 0)
-        tok, pos = get(_P + "embed_tokens.weight"), get(_P + "embed_positions.weight")
-        if cfg.word_embed_proj_dim != d:
-            e = norm.embed(tokens.view(-1, 1), None, tok, None).view(-1, cfg.word_embed_proj_dim)
-            h = norm.add_rows(gemm.linear(e, get(_P + "project_in.weight")), positions, pos)
-        else:
-            h = norm.embed(tokens.view(-1, 1), positions.view(-1, 1), tok, pos).view(-1, d)
+        m = self.m
         t = self.len
-        pre = cfg.do_layer_norm_before
-        for i in range(cfg.num_hidden_layers):
+        h = m.decode_embed(tokens, positions, m._resolver(-1, None, None, 0))
+        for i in range(m.config.num_hidden_layers):
             w = m._layer_weights(i, m._resolver(i, None, None, 0))
-            x = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps) if pre else h
-            qkv = gemm.linear(x, w.qkv_w, w.qkv_b)
-            self.k[i][:, t].copy_(qkv[:, d:2 * d])
-            self.v[i][:, t].copy_(qkv[:, 2 * d:])
-            ctx = decode_ops.decode_attention(qkv[:, :d], self.k[i], self.v[i], t + 1,
-                                              cfg.num_attention_heads, pad_left, w.prefix_k, w.prefix_v)
-            h = gemm.linear(ctx.contiguous(), w.out_w, w.out_b, residual=h)
-            if not pre:
-                h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
-            x = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps) if pre else h
-            f = gemm.linear(x, w.fc1_w, w.fc1_b, act=cfg.activation_function)
-            h = gemm.linear(f, w.fc2_w, w.fc2_b, residual=h)
-            if not pre:
-                h = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
+            h = m.decode_block(h, w, self.k[i], self.v[i], t, pad_left)
         self.len = t + 1
         return _head_logits(m, h)
 
 
 def _head_logits(model: OPTModel, h_last: torch.Tensor) -> torch.Tensor:
-    cfg = model.config
     get = model._resolver(-1, None, None, 0)
-    x = h_last
-    if cfg.do_layer_norm_before:
-        x = norm.layernorm(x, get(_P + "final_layer_norm.weight"), get(_P + "final_layer_norm.bias"),
-                           cfg.layer_norm_eps)
-    if cfg.word_embed_proj_dim != cfg.hidden_size:
-        x = gemm.linear(x, get(_P + "project_out.weight"))
-    table = get("lm_head.weight") if model.untied else get(_P + "embed_tokens.weight")
+    x = model._final_norm(h_last, get)
+    table = get("lm_head.weight") if model.untied else get(model.EMBED)
     return gemm.linear(x.contiguous(), table, out_dtype=torch.float32).float()
-
-
 
 
 def _bias_residual(part: torch.Tensor, bias: torch.Tensor, res: torch.Tensor) -> torch.Tensor:

@@ -129,13 +129,15 @@ def base_param_specs(cfg: OPTConfig) -> list[tuple[str, tuple, int]]:
     return specs
 
 
-def adapter_param_specs(cfg: OPTConfig, lora_r: int, num_prefix: int, reparam: bool = False,
-                        embed_dim: int = 512, mid_dim: int = 512) -> list[tuple[str, tuple, int]]:
+def adapter_param_specs(cfg, lora_r: int, num_prefix: int, reparam: bool = False,
+                        embed_dim: int = 512, mid_dim: int = 512, layer_prefix=None,
+                        kv_dim: int | None = None) -> list[tuple[str, tuple, int]]:
     """LoRA factors and prefix tensors.  With ``reparam`` the prefix rows are not parameters but the
     output of a per-layer two-layer MLP over shared input embeddings (large_models/prefix.py:177-197):
     ``prefix_input_embeds`` [P, embed_dim] lives with layer 0, every layer owns ``prefix_mlp_keys`` and
     ``prefix_mlp_values`` (Linear(embed, mid) - tanh - Linear(mid, d), names as ``nn.Sequential`` gives)."""
     d = cfg.hidden_size
+    layer_prefix = layer_prefix or globals()["layer_prefix"]
     specs = []
     for i in range(cfg.num_hidden_layers):
         lp = layer_prefix(i)
@@ -171,11 +173,11 @@ _LAYER_ORDER = ["self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn
                 for wb in ("weight", "bias")]
 
 
-def _arena_sort_key(name: str, group: int):
+def _arena_sort_key(name: str, group: int, order=None):
     if group < 0:
         return (group, 0, name)
     suffix = name.split(f"layers.{group}.", 1)[1]
-    return (group, _LAYER_ORDER.index(suffix), name)
+    return (group, (order or _LAYER_ORDER).index(suffix), name)
 
 
 @dataclass
@@ -248,17 +250,17 @@ class OPTModel:
         self.untied = untie_emb or mode == "head" or not config.tie_word_embeddings
         self.overlap_transform = overlap_transform and self.device.type == "cuda"
 
-        base = base_param_specs(config)
+        base = self._base_specs()
         extra = []
         if self.untied:
             extra.append(("lm_head.weight", (config.vocab_size, config.word_embed_proj_dim), -1))
-        adapters = adapter_param_specs(config, self.lora_r, self.num_prefix, self.prefix_reparam,
+        adapters = self._adapter_specs(self.lora_r, self.num_prefix, self.prefix_reparam,
                                        prefix_embed_dim, prefix_mid_dim)
         # canonical RNG stream ids: independent of mode, sharding and arena order (new kinds of tensors
         # are appended, so the ids of the existing ones never move)
         canon = [n for n, _, _ in base] + ["lm_head.weight"] + \
-                [n for n, _, _ in adapter_param_specs(config, 8, 5)] + \
-                [n for n, _, _ in adapter_param_specs(config, 0, 5, True)]
+                [n for n, _, _ in self._adapter_specs(8, 5)] + \
+                [n for n, _, _ in self._adapter_specs(0, 5, True)]
         self.tensor_ids = {n: i for i, n in enumerate(canon)}
         self.all_specs = [sp for sp in base + extra + adapters if self.owns(sp[0])]
         self.hf_order = [n for n, _, _ in self.all_specs]
@@ -270,7 +272,7 @@ class OPTModel:
             for n, s, g in specs:
                 ls, kw = self.shard_of(n, tuple(s))
                 ps.append(Piece(n, ls, self.tensor_ids[n], g, **kw))
-            ps.sort(key=lambda p: _arena_sort_key(p.name, p.group))
+            ps.sort(key=lambda p: self._sort_key(p.name, p.group))
             return ps
 
         self.arena = ParamArena(mk([s for s in self.all_specs if s[0] in tset]), self.device, dtype)
@@ -283,6 +285,24 @@ class OPTModel:
         # LoRA: k_proj.weight is frozen, so its copy inside a layer's merged QKV operand stays valid
         self._k_frozen = self.use_lora
         self.kv_capture: list | None = None      # set to [] to record per-layer qkv (generation)
+
+    # ------------------------------------------------------------------ architecture hooks
+    EMBED = _P + "embed_tokens.weight"          # the token table (tied LM head)
+    layer_prefix = staticmethod(layer_prefix)
+
+    def _base_specs(self) -> list[tuple[str, tuple, int]]:
+        return base_param_specs(self.config)
+
+    def _adapter_specs(self, lora_r: int, num_prefix: int, reparam: bool = False, embed_dim: int = 512,
+                       mid_dim: int = 512) -> list[tuple[str, tuple, int]]:
+        return adapter_param_specs(self.config, lora_r, num_prefix, reparam, embed_dim, mid_dim)
+
+    def _sort_key(self, name: str, group: int):
+        return _arena_sort_key(name, group)
+
+    @staticmethod
+    def _is_norm_weight(name: str) -> bool:
+        return "layer_norm.weight" in name
 
     # ------------------------------------------------------------------ sharding hooks
     def owns(self, name: str) -> bool:
@@ -303,7 +323,7 @@ class OPTModel:
     def _select_trainable(self) -> list[str]:
         names = self.hf_order
         if self.mode == "full":
-            out = [n for n in names if n != _P + "embed_tokens.weight"]
+            out = [n for n in names if n != self.EMBED]
         elif self.mode == "head":
             out = ["lm_head.weight"]
         else:
@@ -349,18 +369,17 @@ class OPTModel:
                 v = (torch.rand(shape, generator=g) * 2 - 1) * (1.0 / fan_in) ** 0.5     # nn.Linear's default
             elif "prefix_" in n:
                 v = torch.randn(shape, generator=g)
-            elif "layer_norm.weight" in n:
+            elif self._is_norm_weight(n):
                 v = torch.ones(shape)
             elif n.endswith(".bias"):
                 v = torch.zeros(shape)
             else:
                 v = torch.randn(shape, generator=g) * std
-                if n == _P + "embed_tokens.weight" or n == _P + "embed_positions.weight":
-                    if n == _P + "embed_tokens.weight":
-                        v[self.config.pad_token_id].zero_()
+                if n == self.EMBED and self.config.pad_token_id is not None:
+                    v[self.config.pad_token_id].zero_()
             t.copy_(self.local_slice(n, v).to(self.dtype))
-        if self.untied and "lm_head.weight" in self._where:
-            self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
+        if self.untied and self.config.tie_word_embeddings and "lm_head.weight" in self._where:
+            self.param("lm_head.weight").copy_(self.param(self.EMBED))       # an untied copy of a tied model
         self._merge_buf = {}                     # cached merged operands hold copies of frozen weights
         return self
 
@@ -376,7 +395,7 @@ class OPTModel:
                          (1.0 / fan_in) ** 0.5).to(self.dtype))
             elif "lora_B" in n or n.endswith(".bias"):
                 t.zero_()
-            elif "layer_norm.weight" in n:
+            elif self._is_norm_weight(n):
                 t.fill_(1.0)
             elif "lora_A" in n:
                 t.copy_(((torch.rand(shape, generator=g, device=self.device) * 2 - 1) *
@@ -390,8 +409,8 @@ class OPTModel:
                 for s in range(0, flat.numel(), step):
                     e = min(s + step, flat.numel())
                     flat[s:e].copy_((torch.randn(e - s, generator=g, device=self.device) * std).to(self.dtype))
-        if self.untied and "lm_head.weight" in self._where:
-            self.param("lm_head.weight").copy_(self.param(_P + "embed_tokens.weight"))
+        if self.untied and self.config.tie_word_embeddings and "lm_head.weight" in self._where:
+            self.param("lm_head.weight").copy_(self.param(self.EMBED))       # an untied copy of a tied model
         self._merge_buf = {}                     # cached merged operands hold copies of frozen weights
         return self
 
@@ -402,7 +421,7 @@ class OPTModel:
         """Hugging Face OPT names (plus ``lora_A/B`` and ``prefix_keys/values``)."""
         sd = {n: self.param(n).detach().clone() for n in self.hf_order}
         if not self.untied:
-            sd["lm_head.weight"] = sd[_P + "embed_tokens.weight"]
+            sd["lm_head.weight"] = sd[self.EMBED]
         return sd
 
     @torch.no_grad()
@@ -413,8 +432,8 @@ class OPTModel:
             if src is None and n.startswith("model."):
                 src = sd.get(n[len("model."):])          # OPTModel-prefixed checkpoints
             if src is None:
-                if n == "lm_head.weight" and (_P + "embed_tokens.weight") in sd:
-                    src = sd[_P + "embed_tokens.weight"]
+                if n == "lm_head.weight" and self.EMBED in sd:
+                    src = sd[self.EMBED]
                 elif "lora_" in n or "prefix_" in n:
                     missing.append(n)
                     continue
@@ -611,15 +630,7 @@ class OPTModel:
             g_shift = self._sweep_group(-1, transform, g_staged)
         self._gget = self._resolver(-1, transform, g_staged, g_shift)
         gget = self._gget
-        positions = batch.positions
-        tok = gget(_P + "embed_tokens.weight")
-        pos = gget(_P + "embed_positions.weight")
-        if cfg.word_embed_proj_dim != cfg.hidden_size:
-            e = norm.embed(batch.input_ids, None, tok, None)
-            e = gemm.linear(e, gget(_P + "project_in.weight"))
-            h = norm.add_rows(e, positions.reshape(-1), pos)
-        else:
-            h = norm.embed(batch.input_ids, positions, tok, pos)
+        h = self._embed(batch.input_ids, batch.positions, gget)
         # ---- layers, with the transform of layer i+1 running beside the GEMMs of layer i
         main = torch.cuda.current_stream(self.device) if overlap else None
         ready = [None, None]
@@ -671,6 +682,56 @@ class OPTModel:
             h = norm.gather_rows(h.reshape(-1, cfg.hidden_size), rows)
         return h
 
+    def _embed(self, ids: torch.Tensor, positions: torch.Tensor, gget) -> torch.Tensor:
+        """Token (+ learned position) embedding of ids / positions [B, L] -> [B, L, d]."""
+        cfg = self.config
+        tok = gget(self.EMBED)
+        pos = gget(_P + "embed_positions.weight")
+        if cfg.word_embed_proj_dim != cfg.hidden_size:
+            e = norm.embed(ids, None, tok, None)
+            e = gemm.linear(e, gget(_P + "project_in.weight"))
+            return norm.add_rows(e, positions.reshape(-1), pos)
+        return norm.embed(ids, positions, tok, pos)
+
+    def _final_norm(self, x: torch.Tensor, gget) -> torch.Tensor:
+        """What sits between the last block and the LM head: final LayerNorm, project_out."""
+        cfg = self.config
+        if cfg.do_layer_norm_before:
+            x = norm.layernorm(x, gget(_P + "final_layer_norm.weight"),
+                               gget(_P + "final_layer_norm.bias"), cfg.layer_norm_eps)
+        if cfg.word_embed_proj_dim != cfg.hidden_size:
+            x = gemm.linear(x, gget(_P + "project_out.weight"))
+        return x
+
+    # ------------------------------------------------------------------ one-token decoding (generation)
+    def decode_embed(self, tokens: torch.Tensor, positions: torch.Tensor, get) -> torch.Tensor:
+        """tokens, positions: int32 [B] -> [B, d]."""
+        return self._embed(tokens.view(-1, 1), positions.view(-1, 1), get).view(-1, self.config.hidden_size)
+
+    def decode_block(self, h: torch.Tensor, w: SimpleNamespace, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     t: int, pad_left: torch.Tensor) -> torch.Tensor:
+        """One block on a [B, d] activation: writes this token's K / V at cache column ``t`` and attends to
+        columns [0, t]."""
+        from ..ops import decode as decode_ops
+        cfg = self.config
+        d = cfg.hidden_size
+        pre = cfg.do_layer_norm_before
+        x = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps) if pre else h
+        qkv = gemm.linear(x, w.qkv_w, w.qkv_b)
+        k_cache[:, t].copy_(qkv[:, d:2 * d])
+        v_cache[:, t].copy_(qkv[:, 2 * d:])
+        ctx = decode_ops.decode_attention(qkv[:, :d], k_cache, v_cache, t + 1, cfg.num_attention_heads, pad_left,
+                                          w.prefix_k, w.prefix_v)
+        h = gemm.linear(ctx.contiguous(), w.out_w, w.out_b, residual=h)
+        if not pre:
+            h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
+        x = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps) if pre else h
+        f = gemm.linear(x, w.fc1_w, w.fc1_b, act=cfg.activation_function)
+        h = gemm.linear(f, w.fc2_w, w.fc2_b, residual=h)
+        if not pre:
+            h = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
+        return h
+
     def _selected(self, batch: Batch, transform: Transform | None) -> torch.Tensor:
         """Final-normalised hidden rows ``batch.rows``.  The replicated model restricts its last block to
         them; sharded layouts (own ``hidden_states``) compute every row and pick afterwards."""
@@ -685,16 +746,10 @@ class OPTModel:
         cfg = self.config
         d = cfg.hidden_size
         x = h if rows is None else norm.gather_rows(h.reshape(-1, d), rows)
-        gget = self._gget
-        if cfg.do_layer_norm_before:
-            x = norm.layernorm(x, gget(_P + "final_layer_norm.weight"),
-                               gget(_P + "final_layer_norm.bias"), cfg.layer_norm_eps)
-        if cfg.word_embed_proj_dim != d:
-            x = gemm.linear(x, gget(_P + "project_out.weight"))
-        return x
+        return self._final_norm(x, self._gget)
 
     def lm_head_weight(self) -> torch.Tensor:
-        return self._gget("lm_head.weight") if self.untied else self._gget(_P + "embed_tokens.weight")
+        return self._gget("lm_head.weight") if self.untied else self._gget(self.EMBED)
 
     @torch.no_grad()
     def loss(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import torch
 
-from .opt import OPTModel, layer_prefix, make_batch
+from .opt import OPTModel, make_batch
 
 
 class LoRA:
@@ -118,5 +118,5 @@ def init_prefix_by_real_activations(model: OPTModel, seed: int = 0) -> None:
         model.use_prefix, model.kv_capture = True, None
     for i, qkv in enumerate(cap):
         q3 = qkv.reshape(P, 3 * d)
-        model.param(layer_prefix(i) + "self_attn.prefix_keys").copy_(q3[:, d:2 * d])
-        model.param(layer_prefix(i) + "self_attn.prefix_values").copy_(q3[:, 2 * d:])
+        model.param(model.layer_prefix(i) + "self_attn.prefix_keys").copy_(q3[:, d:2 * d])
+        model.param(model.layer_prefix(i) + "self_attn.prefix_values").copy_(q3[:, 2 * d:])

@@ -14,7 +14,6 @@ import logging
 import numpy as np
 import torch
 
-from .opt import _P
 
 logger = logging.getLogger(__name__)
 
@@ -56,7 +55,7 @@ def linear_probe(trainer):
     if coef.shape[0] == 1:                      # two classes: one weight vector
         assert len(reg.classes_) == 2
         coef = torch.cat([-coef / 2, coef / 2], dim=0)
-    name = "lm_head.weight" if model.untied else _P + "embed_tokens.weight"
+    name = "lm_head.weight" if model.untied else model.EMBED
     head = model.param(name)
     logger.info("Assigning weights to model")
     for i, token_id in enumerate(reg.classes_):

@@ -119,7 +119,7 @@ def check_device_errors(device: torch.device | int | None = None) -> None:
 # when the table changes.  ``debug_check`` (called by ``check_device_errors``) raises if a kernel
 # recorded a skipped store.  Stands in for compute-sanitizer where that tool is closed.
 _DBG_MAX = 256
-_DBG_TUS = ("zo", "norm", "lmhead", "bwd", "peft", "gemm1", "gemm2", "commgemm")
+_DBG_TUS = ("zo", "norm", "lmhead", "bwd", "peft", "gemm1", "gemm2", "commgemm", "llama")
 
 
 class _DbgState(ctypes.Structure):

@@ -105,10 +105,16 @@ class Framework:
             path = self.resolve_model_dir(a.model_name)
             if path is not None:
                 with open(os.path.join(path, "config.json")) as f:
-                    cfg = OPTConfig.from_hf(json.load(f))
-                if cfg.model_type != "opt":
-                    raise NotImplementedError(f"{a.model_name}: model_type {cfg.model_type!r}; the kernels "
-                                              "implement the OPT decoder family")
+                    raw = json.load(f)
+                mtype = raw.get("model_type", "opt")
+                if mtype == "opt":
+                    cfg = OPTConfig.from_hf(raw)
+                elif mtype in ("llama", "mistral"):
+                    from .models.llama import LlamaConfig
+                    cfg = LlamaConfig.from_hf(raw)
+                else:
+                    raise NotImplementedError(f"{a.model_name}: model_type {mtype!r}; the kernels implement the "
+                                              "OPT and LLaMA (llama, mistral) decoder families")
                 if not a.random_init:
                     state = load_weights(path, lazy=True)   # one tensor at a time: every rank keeps its slice
             else:
@@ -119,9 +125,14 @@ class Framework:
                         f"--model_name {a.model_name!r} is neither a checkpoint directory nor a model in the "
                         "local Hugging Face cache (nothing is downloaded). Pass --random_init to build a "
                         "randomly initialised model of that shape on purpose.")
-                if key not in PRESETS:
-                    raise KeyError(f"--random_init needs a known shape; {key!r} is not one of {sorted(PRESETS)}")
-                cfg = preset(key)
+                from .models import llama as llama_models
+                if key in PRESETS:
+                    cfg = preset(key)
+                elif key in llama_models.PRESETS:
+                    cfg = llama_models.preset(key)
+                else:
+                    raise KeyError(f"--random_init needs a known shape; {key!r} is not one of "
+                                   f"{sorted(PRESETS) + sorted(llama_models.PRESETS)}")
                 logger.info("--random_init: %s with random weights", key)
             mode = "full"
             if a.head_tuning:
@@ -134,7 +145,14 @@ class Framework:
                 mode = "prefix"
             world = torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
             self.dp_group = None                      # None: the default group, when there is one
-            if a.pp > 1:
+            if cfg.model_type != "opt":
+                if a.pp > 1 or a.tp > 1 or a.fsdp_shard:
+                    raise NotImplementedError("--pp / --tp / --fsdp_shard shard the OPT family; LLaMA-family "
+                                              "models run replicated (data parallel)")
+                from .models.llama import LlamaModel
+                model = LlamaModel(cfg, self.device, self._dtype(), mode=mode, num_prefix=a.num_prefix,
+                                   prefix_reparam=not a.no_reparam)
+            elif a.pp > 1:
                 # consecutive blocks on consecutive ranks; every rank sees the same batch
                 assert a.pp == world, "--pp must equal the number of ranks (one pipeline)"
                 assert a.enhanced != "fo", "the first-order gamma search is not staged over a pipeline"
@@ -198,6 +216,8 @@ class Framework:
             tok.pad_token_id = 0
         if cfg.model_type == "opt":
             tok.bos_token_id = 0 if not isinstance(tok, StubTokenizer) else tok.bos_token_id
+        elif not isinstance(tok, StubTokenizer):
+            tok.pad_token_id = 0                     # the llama fix-up of large_models/run.py:229-231
         tok.padding_side = "left"
         return tok
 

@@ -161,18 +161,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         ok = mbar_wait(smem_u32(&bar_y_full[st]), ph, &s_abort, p.err, ERR_WAIT_FULL);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t x1 = smem_base + S::OFF_X1, x2 = smem_base + S::OFF_X2;
+        // One thread issues every MMA and a 128 x 128 x 16 product lasts 64 cycles, so the descriptors are
+        // built once per iteration and each MMA only adds a constant to their address field.
+        const uint64_t x1d = umma_desc_k_sw128(smem_base + S::OFF_X1), x2d = umma_desc_k_sw128(smem_base + S::OFF_X2);
         const uint32_t y1 = smem_base + S::OFF_Y1 + st * S::TILE, y2 = smem_base + S::OFF_Y2 + st * S::TILE;
+        const uint64_t y1d = umma_desc_k_sw128(y1), y2d = umma_desc_k_sw128(y2);
+        const uint64_t y1m = umma_desc_mn_sw128(y1, AB_T * 128, 1024), y2m = umma_desc_mn_sw128(y2, AB_T * 128, 1024);
         // S (or S^T) = X1 Y1^T,  dP (or dP^T) = X2 Y2^T : contraction over the head dimension.
         // Tensor-core operations of one thread execute in issue order, so these overwrite the
         // S / dP columns only after the previous iteration's accumulations have read them.
-        for (int kk = 0; kk < k_steps; ++kk) {
-          const uint32_t off = (kk >> 2) * (AB_T * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tm_s, umma_desc_k_sw128(x1 + off), umma_desc_k_sw128(y1 + off), idesc_s, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+          if (kk < k_steps) {
+            const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (AB_T * 128) + (kk & 3) * 32) >> 4);
+            umma_bf16_ss(tm_s, x1d + off, y1d + off, idesc_s, kk != 0);
+          }
         }
-        for (int kk = 0; kk < k_steps; ++kk) {
-          const uint32_t off = (kk >> 2) * (AB_T * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tm_dp, umma_desc_k_sw128(x2 + off), umma_desc_k_sw128(y2 + off), idesc_s, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+          if (kk < k_steps) {
+            const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (AB_T * 128) + (kk & 3) * 32) >> 4);
+            umma_bf16_ss(tm_dp, x2d + off, y2d + off, idesc_s, kk != 0);
+          }
         }
         umma_commit(smem_u32(&bar_s));
         ok = mbar_wait(smem_u32(&bar_ds), it & 1, &s_abort, p.err, ERR_WAIT_MISC);
@@ -181,18 +191,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
         // contraction over the 128 streamed rows: 16 rows = 8 packed TMEM columns of the A operand
         // (rows 0-63 packed at columns [0,32), rows 64-127 at [64,96)) and two 8-row groups
         // (1024 bytes each) of the MN-major B operand
-        for (int kk = 0; kk < AB_T / 16; ++kk) {
-          if (!DQ) {
-            // dV_j += P^T dO_i
-            umma_bf16_ts(tm_acc1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8,
-                         umma_desc_mn_sw128(y2 + kk * 2048, AB_T * 128, 1024), idesc_acc, (it | kk) != 0);
-          }
+        if (!DQ) {
+#pragma unroll
+          for (int kk = 0; kk < AB_T / 16; ++kk)      // dV_j += P^T dO_i
+            umma_bf16_ts(tm_acc1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8, y2m + static_cast<uint64_t>(kk * (2048 >> 4)),
+                         idesc_acc, (it | kk) != 0);
         }
-        for (int kk = 0; kk < AB_T / 16; ++kk) {
-          // dK_j += dS^T Q_i   |   dQ_i += dS K_j
+#pragma unroll
+        for (int kk = 0; kk < AB_T / 16; ++kk)        // dK_j += dS^T Q_i   |   dQ_i += dS K_j
           umma_bf16_ts(DQ ? tm_acc1 : tm_acc2, tm_dp + (kk >> 2) * 64 + (kk & 3) * 8,
-                       umma_desc_mn_sw128(y1 + kk * 2048, AB_T * 128, 1024), idesc_acc, (it | kk) != 0);
-        }
+                       y1m + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_acc, (it | kk) != 0);
         umma_commit(smem_u32(&bar_y_empty[st]));
       }
       if (ok) umma_commit(smem_u32(&bar_acc));

@@ -165,26 +165,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_s = umma_idesc_bf16(A_BQ, A_BKV, 0, 0);
       const uint32_t idesc_o = umma_idesc_bf16(A_BQ, (hd + 15) & ~15, 0, 1);  // V is MN-major
       const int k_steps = (hd + 15) / 16;
+      // One thread issues every MMA, and a 128 x 128 x 16 product occupies the tensor pipe for only 64 cycles:
+      // the descriptors are built once and each MMA adds a constant to their address field, so that issuing
+      // stays cheaper than executing (building them per MMA took about 90 cycles each).
+      const uint64_t q_desc0 = umma_desc_k_sw128(smem_base + S::OFF_Q);
+      const uint64_t q_desc1 = umma_desc_k_sw128(smem_base + S::OFF_Q + S::Q_TILE);
+      const uint64_t k_desc0 = umma_desc_k_sw128(smem_base + S::OFF_K);
+      const uint64_t k_desc1 = umma_desc_k_sw128(smem_base + S::OFF_K + S::KV_TILE);
+      const uint64_t v_desc0 = umma_desc_mn_sw128(smem_base + S::OFF_V, A_BKV * 128, 1024);
+      const uint64_t v_desc1 = umma_desc_mn_sw128(smem_base + S::OFF_V + S::KV_TILE, A_BKV * 128, 1024);
+      static_assert(A_KV_STAGES == 2 && A_BQ == A_BKV, "descriptor selection below assumes two stages");
       auto issue_s = [&](int t, int vb) {
-        int st = vb % A_KV_STAGES;
-        uint32_t qa = smem_base + S::OFF_Q + t * S::Q_TILE;
-        uint32_t ka = smem_base + S::OFF_K + st * S::KV_TILE;
-        for (int kk = 0; kk < k_steps; ++kk) {
-          uint64_t ad = umma_desc_k_sw128(qa + (kk >> 2) * (A_BQ * 128) + (kk & 3) * 32);
-          uint64_t bd = umma_desc_k_sw128(ka + (kk >> 2) * (A_BKV * 128) + (kk & 3) * 32);
-          umma_bf16_ss(tm_s[t], ad, bd, idesc_s, kk != 0);
+        const uint64_t qd = t ? q_desc1 : q_desc0;
+        const uint64_t kd = (vb & 1) ? k_desc1 : k_desc0;
+        const uint32_t ds = tm_s[t];
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+          if (kk < k_steps) {
+            // 64-column blocks of the head are A_BQ * 128 bytes apart, 16 columns are 32 bytes
+            const uint64_t off = static_cast<uint64_t>(((kk >> 2) * (A_BQ * 128) + (kk & 3) * 32) >> 4);
+            umma_bf16_ss(ds, qd + off, kd + off, idesc_s, kk != 0);
+          }
         }
         umma_commit(smem_u32(&bar_s[t]));
       };
       auto issue_pv = [&](int t, int vb) {
-        int st = vb % A_KV_STAGES;
-        uint32_t va = smem_base + S::OFF_V + st * S::KV_TILE;
-        for (int kk = 0; kk < A_BKV / 16; ++kk) {
-          // A = P from TMEM: 16 keys = 8 packed 32-bit columns.  B = V, MN-major: 16 keys = two
-          // 8-row groups of 1024 bytes; 64-column blocks of the head are A_BKV*128 bytes apart.
-          uint64_t bd = umma_desc_mn_sw128(va + kk * 2048, A_BKV * 128, 1024);
-          umma_bf16_ts(tm_o[t], tm_s[t] + kk * 8, bd, idesc_o, (vb | kk) != 0);
-        }
+        // A = P from TMEM: 16 keys = 8 packed 32-bit columns.  B = V, MN-major: 16 keys = two
+        // 8-row groups of 1024 bytes; 64-column blocks of the head are A_BKV*128 bytes apart.
+        const uint64_t vd = (vb & 1) ? v_desc1 : v_desc0;
+        const uint32_t dso = tm_o[t], pa = tm_s[t];
+#pragma unroll
+        for (int kk = 0; kk < A_BKV / 16; ++kk)
+          umma_bf16_ts(dso, pa + kk * 8, vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_o, (vb | kk) != 0);
         umma_commit(smem_u32(&bar_pv[t]));
       };
       ok = mbar_wait(smem_u32(&bar_q), 0, &s_abort, p.err, ERR_WAIT_FULL);
@@ -269,10 +281,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (bmax > m_used + A_RESCALE_THRESHOLD || m_used == -INFINITY) m_new = fmaxf(m_used, bmax);
       const bool changed = (m_new != m_used);
       if (vb > 0) {
-        // PV of the previous block must be complete before O is touched or P overwritten
-        ok = mbar_wait(smem_u32(&bar_pv[t]), (vb - 1) & 1, &s_abort, p.err, ERR_WAIT_MISC);
-        if (!ok) break;
-        tc_fence_after();
+        // PV of the previous block is complete here - O may be touched and P overwritten: it was issued before
+        // this block's score product by the same thread, and the commit that signalled bar_s covers every
+        // tensor-core operation issued before it
         if (__any_sync(0xffffffffu, changed && m_used != -INFINITY)) {
           const float f = (changed && m_used != -INFINITY) ? exp2f(m_used - m_new) : 1.0f;
           for (int c0 = 0; c0 < hd; c0 += 16) {

@@ -13,7 +13,8 @@ are summed with one small all-reduce each.  FSDP: every matrix is sharded by out
 computes its slice of each projection from the replicated [batch, d] activation and the slices are
 all-gathered (a few KB per token); attention runs on the full heads on every rank.  All ranks of the
 group must call :func:`generate` together (same batch size); the stop test is agreed by all-reduce.
-Pipeline-parallel models are not decoded (candidate scoring and training cover them).
+Pipeline parallel: every stage caches the K / V of its own blocks, a token's activation is sent stage to stage
+and the last stage's logits are broadcast.
 """
 from __future__ import annotations
 
@@ -222,6 +223,62 @@ class _FSDPDecoder(_Decoder):
         return bool(flag.item())
 
 
+class _PPDecoder(_Decoder):
+    """Pipeline parallel: every stage keeps the K / V cache of its own blocks; a token's [B, d] activation
+    travels stage to stage and the last stage's logits are broadcast (every rank decodes the same batch)."""
+
+    def __init__(self, model, B: int, max_len: int):
+        self.m = model
+        cfg = model.config
+        d = cfg.hidden_size
+        dev, dt = model.device, model.dtype
+        self.layers = list(range(model.lo, model.hi))
+        self.k = [torch.zeros(B, max_len, d, dtype=dt, device=dev) for _ in self.layers]
+        self.v = [torch.zeros(B, max_len, d, dtype=dt, device=dev) for _ in self.layers]
+        self.len = 0
+        self.B = B
+
+    def prefill(self, batch: Batch) -> torch.Tensor:
+        m = self.m
+        d = m.config.hidden_size
+        B, L = batch.input_ids.shape
+        m.kv_capture = []
+        try:
+            h = m.hidden_states(batch)                         # micro-batches through this stage's blocks
+        finally:
+            cap, m.kv_capture = m.kv_capture, None
+        n_own = len(self.layers)
+        row0 = 0
+        for j0 in range(0, len(cap), max(n_own, 1)):           # captured per micro-batch, then per block
+            rows = cap[j0].numel() // (3 * d * L)
+            for j in range(n_own):
+                q3 = cap[j0 + j].reshape(rows, L, 3 * d)
+                self.k[j][row0:row0 + rows, :L].copy_(q3[:, :, d:2 * d])
+                self.v[j][row0:row0 + rows, :L].copy_(q3[:, :, 2 * d:])
+            row0 += rows
+        self.len = L
+        V = m.config.vocab_size
+        return m._from_last(lambda: _head_logits(m, h[:, -1, :]), (B, V))
+
+    def step(self, tokens, positions, pad_left) -> torch.Tensor:
+        m, cfg = self.m, self.m.config
+        d = cfg.hidden_size
+        first, last = m.stage == 0, m.stage == m.n - 1
+        t = self.len
+        if first:
+            h = m.decode_embed(tokens, positions, m._resolver(-1, None, None, 0))
+        else:
+            h = torch.empty((self.B, d), dtype=m.dtype, device=m.device)
+            dist.recv(h, src=m._rank_of(m.stage - 1), group=m.group)
+        for j, i in enumerate(self.layers):
+            w = m._layer_weights(i, m._resolver(i, None, None, 0))
+            h = m.decode_block(h, w, self.k[j], self.v[j], t, pad_left)
+        if not last:
+            dist.send(h.contiguous(), dst=m._rank_of(m.stage + 1), group=m.group)
+        self.len = t + 1
+        return m._from_last(lambda: _head_logits(m, h), (self.B, cfg.vocab_size))
+
+
 def _make_decoder(model, B: int, max_len: int) -> _Decoder:
     kind = type(model).__name__
     if type(model).hidden_states is OPTModel.hidden_states:
@@ -230,8 +287,9 @@ def _make_decoder(model, B: int, max_len: int) -> _Decoder:
         return _TPDecoder(model, B, max_len)
     if kind in ("FSDPOPTModel", "FSDPCompositionModel"):
         return _FSDPDecoder(model, B, max_len)
-    raise NotImplementedError("autoregressive decoding covers replicated, tensor-parallel and FSDP models; "
-                              "pipeline-parallel models are scored and trained only")
+    if kind == "PPOPTModel":
+        return _PPDecoder(model, B, max_len)
+    raise NotImplementedError(f"autoregressive decoding is not built for {kind}")
 
 
 @torch.no_grad()

@@ -43,6 +43,17 @@ PP_SCRIPT = textwrap.dedent('''
     lp = pp.row_logprobs(__import__("dizo_b200.data.batching", fromlist=["x"]).batch_from_inputs(
         dict(input_ids=batch(0).input_ids, labels=batch(0).input_ids.clone(), option_len=[3] * 5), pad_token_id=1))
     assert lp.numel() == 15 and torch.isfinite(lp).all()
+    # decoding over the pipeline (every stage caches its own blocks): same tokens as the single process,
+    # greedy with left padding and beams
+    from dizo_b200.models.generate import generate
+    solo2 = OPTModel(cfg, "cpu", torch.float32)
+    solo2.load_state_dict(pp.gather_state_dict())
+    ids = batch(7).input_ids[:, :9].long()
+    mask = torch.ones_like(ids); mask[1, :3] = 0; ids[1, :3] = 1
+    for kw in (dict(), dict(num_beams=2)):
+        want = generate(solo2, ids, mask, max_new_tokens=5, **kw)
+        got = generate(pp, ids, mask, max_new_tokens=5, **kw)
+        assert want == got, (kw, want, got)
     print("PP_OK", rank)
 ''')
 

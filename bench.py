@@ -148,8 +148,12 @@ def run_ours(a, world, rank, local):
     from dizo_b200.ops import _lib
 
     dev = torch.device("cuda", local)
-    cfg = preset(a.model)
+    from dizo_b200.models import llama as llama_models
+    is_llama = a.model.lower() in llama_models.PRESETS
+    cfg = llama_models.preset(a.model) if is_llama else preset(a.model)
     par = a.parallelism if world > 1 else "dp"
+    if is_llama and (par != "dp" or a.enhanced == "fo"):
+        raise SystemExit("LLaMA-family models run replicated (--parallelism dp) with --enhanced zo | none")
     if par in ("tp", "pp") and a.enhanced == "fo":
         raise SystemExit("--enhanced fo runs on replicated or FSDP-sharded parameters (--parallelism dp | fsdp)")
     if par == "fsdp":
@@ -161,6 +165,8 @@ def run_ours(a, world, rank, local):
     elif par == "pp":
         from dizo_b200.parallel.pp import PPOPTModel
         model = PPOPTModel(cfg, dev)
+    elif is_llama:
+        model = llama_models.LlamaModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=a.overlap)
     else:
         model = OPTModel(cfg, dev, torch.bfloat16, mode=a.mode, overlap_transform=a.overlap)
     model.init_random_fast(seed=0)

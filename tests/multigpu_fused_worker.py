@@ -50,6 +50,13 @@ def main():
                L.dz_comm_gemm_two_sm(xs_rows, F, 2, F // world, 0)]
         assert two == ([0, 0, 0] if case == 0 else [1, 1, 1]), (case, two)
         run_case(fc, g, dev, rank, world, M, d, F, xs_rows, dq)
+    # the policies used with more than two ranks, on both tile kernels: sixteen CTAs that only push, and CTAs
+    # that push and keep a part of a normal CTA's tiles
+    for ctas, share in ((16, 0.0), (32, 0.5)):
+        fc.push_ctas, fc.push_share = ctas, share
+        for M, d, F, xs_rows, dq in cases:
+            run_case(fc, g, dev, rank, world, M, d, F, xs_rows, dq)
+    fc.push_ctas, fc.push_share = 0, 0.0
 
     torch.cuda.synchronize()
     _lib.check_device_errors()

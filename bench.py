@@ -64,6 +64,7 @@ def dist_setup():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        quiet_nccl()
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
@@ -141,6 +142,12 @@ def physical_gpu_index(local: int) -> int:
 
 
 # ------------------------------------------------------------------------------- ours
+def quiet_nccl():
+    """NCCL prints its version banner to stdout under NCCL_DEBUG=VERSION; the bench prints one JSON line."""
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
+
+
 def run_ours(a, world, rank, local):
     from dizo_b200.data.synthetic import synthetic_batch
     from dizo_b200.engine import DiZOProjector, ZOEngine
@@ -590,6 +597,21 @@ def run_reference(a):
 
 def main():
     a = parse()
+    # Libraries write banners to stdout (NCCL prints its version there); the contract is ONE JSON line.  File
+    # descriptor 1 points at stderr while the benchmark runs and is restored for the result line.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(*args, **kw):
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        _print(*args, **kw)
+        sys.stdout.flush()
+        os.dup2(2, 1)
+    import builtins
+    _print = builtins.print
+    globals()["print"] = emit           # every print of this module is a result line
     if a.impl == "reference":
         return run_reference(a)
     world, rank, local = dist_setup()

@@ -111,18 +111,42 @@ class FusedComm:
         self._dbg_out = None
 
     # ------------------------------------------------------------------ helpers
+    # what one pushing CTA moves (measured: 8.3 GB/s per CTA with 4 ranks, 13.7 GB/s with 8) and what the tile
+    # kernels sustain; both only rank the alternatives of _push_plan
+    _PUSH_GBS_PER_CTA = 10.0
+    _GEMM_TFLOPS = 1300.0
+
     def _push_plan(self, d: _Desc, M: int, N: int, consumer_waits: bool, two: int = 0) -> tuple[int, int]:
         """(CTAs that push, ``join_tiles``: tiles left to them; -1 = none, 0 = a full share).
 
         Measured policy.  Two ranks: every CTA pushes (one destination, half of the bytes stay local; the
         transfer rides along at no visible cost).  More ranks: posted stores from all 148 SMs to seven
         destinations slowed every GEMM tile (8 GPUs: all-gather -> GEMM 0.61 -> 0.71 ms, FSDP 4.45 -> 5.49 ms
-        at OPT-66B shapes), so ``push_ctas`` CTAs push and take ``push_share`` of a normal CTA's tiles."""
+        at OPT-66B shapes), so sixteen CTAs only push - as long as sixteen can move the launch's bytes within the
+        time of its GEMM.  A launch whose push outweighs its GEMM (the out_proj GEMM beside the fc1 shard push of
+        an FSDP block; all-gather -> GEMM at OPT-13B width) is bound by the transfer: with up to four ranks every
+        CTA then pushes again (4 GPUs, OPT-13B all-gather -> GEMM: 0.47 ms with sixteen pushers, 0.36 ms with all,
+        0.40 ms NCCL + GEMM); with more ranks the number of pushing-only CTAs is the one that balances the
+        transfer against the GEMM on the remaining SMs.  ``push_ctas`` / ``push_share`` override the choice."""
         L = _lib.lib()
         if M <= 0:
             return min(_SM_COUNT, 96), 0                                    # push only
         grid0 = L.dz_comm_gemm_grid(M, N, 0, two)
-        n = self.push_ctas if self.push_ctas > 0 else (grid0 if self.world <= 2 else 16)
+        if self.push_ctas > 0:
+            n = self.push_ctas
+        elif self.world <= 2:
+            n = grid0
+        else:
+            nbytes = 2.0 * max(int(d.push_nseg), 1) * int(d.push_rows) * int(d.push_cols) * (self.world - 1)
+            t_gemm = 2.0 * M * N * int(d.K) / (self._GEMM_TFLOPS * 1e12)
+            rate = self._PUSH_GBS_PER_CTA * 1e9
+            if nbytes <= 16 * rate * t_gemm:
+                n = 16
+            elif self.world <= 4:
+                n = grid0
+            else:
+                cost = lambda k: max(nbytes / (k * rate), t_gemm * _SM_COUNT / (_SM_COUNT - k))
+                n = min(range(16, 66, 8), key=cost)
         n = max(1, min(n, _SM_COUNT))
         if two:
             n = min((n + 1) & ~1, _SM_COUNT & ~1)      # CTA pairs push together

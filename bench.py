@@ -20,7 +20,6 @@ import os
 import statistics
 import subprocess
 import sys
-import time
 
 import torch
 

@@ -23,8 +23,7 @@ theta <- theta_0 + gamma / ||theta - theta_0|| * (theta - theta_0).  The search 
 from __future__ import annotations
 
 import logging
-from dataclasses import dataclass
-from typing import Callable, Iterator
+from typing import Callable
 
 import torch
 import torch.distributed as dist

@@ -18,7 +18,7 @@ import torch
 
 from .data.batching import batch_from_inputs
 from .metrics import calculate_metric
-from .models.opt import OPTModel, make_batch
+from .models.opt import OPTModel
 from .utils import Prediction, encode_prompt, pad_sequences
 
 logger = logging.getLogger(__name__)

@@ -38,7 +38,7 @@ import torch
 
 from ..ops import attention as attn_ops
 from ..ops import backward as bw
-from ..ops import gemm, loss as loss_ops, norm
+from ..ops import gemm, norm
 from .opt import _P, Batch, OPTModel, Transform, layer_prefix
 
 

@@ -23,7 +23,6 @@ from typing import List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from ..ops import attention as attn_ops
 from ..ops import decode as decode_ops
 from ..ops import gemm, norm
 from .opt import _P, Batch, OPTModel, layer_prefix, make_batch

@@ -21,7 +21,7 @@ and PyTorch statements of the same ops for CPU tensors (fp32 oracle).
 """
 from __future__ import annotations
 
-from dataclasses import asdict, dataclass, field
+from dataclasses import asdict, dataclass
 from types import SimpleNamespace
 from typing import Callable, Iterable
 
@@ -29,7 +29,7 @@ import torch
 
 from ..ops import attention as attn_ops
 from ..ops import gemm, loss as loss_ops, norm, peft as peft_ops
-from ..ops.zo import CHUNK, ParamArena, Piece
+from ..ops.zo import ParamArena, Piece
 
 
 @dataclass

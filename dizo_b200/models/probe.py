@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import logging
 
-import numpy as np
 import torch
 
 

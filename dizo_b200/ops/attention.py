@@ -8,8 +8,6 @@ reference's eager OPT attention with its additive causal + padding mask
 from __future__ import annotations
 
 import ctypes
-import math
-import os
 
 import torch
 

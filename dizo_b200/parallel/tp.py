@@ -25,9 +25,9 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from ..models.opt import _P, Batch, OPTConfig, OPTModel, Transform, layer_prefix
+from ..models.opt import _P, Batch, OPTConfig, OPTModel, Transform
 from ..ops import attention as attn_ops
-from ..ops import gemm, loss as loss_ops, norm
+from ..ops import norm
 from .fused import FusedComm
 
 _ROW = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight", "fc1.weight")

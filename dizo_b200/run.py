@@ -15,15 +15,13 @@ import json
 import logging
 import os
 import random
-import time
-from typing import List, Optional
+from typing import Optional
 
 import numpy as np
 import torch
 
 from .args import OurArguments, parse_args
 from .evaluation import Evaluator
-from .metrics import calculate_metric
 from .models import peft as peft_wiring
 from .models.opt import OPTConfig, OPTModel, PRESETS, preset
 from .tasks import get_task

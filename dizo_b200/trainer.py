@@ -29,7 +29,7 @@ import torch.distributed as dist
 from .args import OurArguments
 from .data.batching import batch_from_inputs
 from .engine import DiZOProjector, ZOEngine
-from .metrics import calculate_metric, f1
+from .metrics import f1
 from .models.opt import Batch, OPTModel, Transform
 from .utils import TrainerCallback, TrainerControl
 from .utils.checkpoint import load_checkpoint, save_checkpoint

@@ -70,6 +70,18 @@ class ZOEngine:
     def forward(self, batch: Batch, transform: Transform | None = None) -> torch.Tensor:
         return self.model.loss(batch, transform)
 
+    def forward_pair(self, batch: Batch, seed: int, seed_dev: torch.Tensor | None = None,
+                     loss_fn: Callable[[Batch, Transform | None], torch.Tensor] | None = None):
+        """(L(theta + eps z), L(theta - eps z)) with in-flight perturbation: block by block with one draw of z per
+        block where the model supports it (``OPTModel.loss_pair``), else two separate forwards."""
+        eps = self.eps
+        m = self.model
+        if loss_fn is None and getattr(m, "pair_supported", None) is not None and m.pair_supported():
+            return m.loss_pair(batch, seed, eps, seed_dev=seed_dev)
+        fwd = loss_fn or self.forward
+        return (fwd(batch, Transform(seed=seed, coef=eps, seed_dev=seed_dev)),
+                fwd(batch, Transform(seed=seed, coef=-eps, seed_dev=seed_dev)))
+
     def reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
         """Mean over the data-parallel group of a 1-element device tensor (NCCL / gloo)."""
         if self.dp_group is not False and _dist_on(self.dp_group):
@@ -90,8 +102,7 @@ class ZOEngine:
         fwd = loss_fn or self.forward
         eps = self.eps
         if self.mode == "inflight":
-            l1 = fwd(batch, Transform(seed=seed, coef=eps))
-            l2 = fwd(batch, Transform(seed=seed, coef=-eps))
+            l1, l2 = self.forward_pair(batch, seed, loss_fn=loss_fn)
         else:
             self.perturb(seed, 1.0)
             l1 = fwd(batch, None)
@@ -151,8 +162,7 @@ class GraphedZOStep:
 
     def _body(self) -> torch.Tensor:
         e, eps = self.engine, self.engine.eps
-        l1 = e.forward(self.batch, Transform(coef=eps, seed_dev=self.seed))
-        l2 = e.forward(self.batch, Transform(coef=-eps, seed_dev=self.seed))
+        l1, l2 = e.forward_pair(self.batch, 0, seed_dev=self.seed)
         e.loss1.copy_(l1.reshape(1))
         e.loss2.copy_(l2.reshape(1))
         scalar_diff(e.loss1, e.loss2, 1.0 / (2.0 * e.eps_fd), e.projected_grad)

@@ -507,7 +507,8 @@ class OPTModel:
             return ar.view(name)
         return get
 
-    def _sweep_group(self, group: int, transform: Transform, dst: torch.Tensor, small: bool = False) -> int:
+    def _sweep_group(self, group: int, transform: Transform, dst: torch.Tensor, small: bool = False,
+                     dst2: torch.Tensor | None = None) -> int:
         lo, hi = self.arena.group_range(group)
         r = self._blend_range(group, transform)
         if r is not None:
@@ -516,7 +517,7 @@ class OPTModel:
                 return 0
         self.arena.sweep(t_begin=lo, t_end=hi, dst=dst, seed1=transform.seed, c1=transform.coef,
                          c1_dev=transform.coef_dev, seed1_dev=transform.seed_dev, alpha=transform.alpha,
-                         small=small)
+                         small=small, dst2=dst2)
         return self.arena.span(lo, hi)[0]
 
     def _lora_qkv_buffer(self, i: int) -> tuple[torch.Tensor, bool]:
@@ -747,6 +748,61 @@ class OPTModel:
         d = cfg.hidden_size
         x = h if rows is None else norm.gather_rows(h.reshape(-1, d), rows)
         return self._final_norm(x, self._gget)
+
+    # ------------------------------------------------------------------ both sides of the two-point estimate
+    def pair_supported(self) -> bool:
+        """Whether :meth:`loss_pair` applies: the unsharded forward, sweeps on the main stream, prefix rows (if
+        any) held as parameters."""
+        return (type(self).hidden_states is OPTModel.hidden_states and not self.overlap_transform
+                and not self.prefix_reparam and len(self.arena.pieces) > 0)
+
+    @torch.no_grad()
+    def loss_pair(self, batch: Batch, seed: int, eps: float, seed_dev: torch.Tensor | None = None):
+        """(L(theta + eps z), L(theta - eps z)) for z = z(seed).  The two forwards advance block by block: one
+        sweep per block draws z once and stages theta + eps z and theta - eps z side by side
+        (``ParamArena.sweep(dst2=...)``), then the block runs on each activation stream with its copy.  The staged
+        values, the kernels and therefore both losses are the same bit for bit as two separate forwards with
+        ``Transform(coef=+eps)`` and ``Transform(coef=-eps)`` (large_models/trainer.py:1570-1595 perturbs, runs a
+        forward, perturbs twice the other way, runs the second); what is saved is one of the two draws of z per
+        step - a third of the sweep time, which the generator bounds."""
+        cfg = self.config
+        nl = cfg.num_hidden_layers
+        tr = Transform(seed=seed, coef=eps, seed_dev=seed_dev)
+        groups = set(self.arena.groups())
+        ggets = [self._resolver(-1, None, None, 0)] * 2
+        if -1 in groups:
+            n = self.arena.group_numel(-1)
+            g1, g2 = self._staging_for("globals", n), self._staging_for("globals-", n)
+            shift = self._sweep_group(-1, tr, g1, dst2=g2)
+            ggets = [self._resolver(-1, tr, g1, shift), self._resolver(-1, tr, g2, shift)]
+        hs = [self._embed(batch.input_ids, batch.positions, g) for g in ggets]
+        layer_numel = max((self.arena.group_numel(g) for g in groups if g >= 0), default=0)
+        for i in range(nl):
+            if i in groups:
+                b1 = self._staging_for(("layer", i % 2), layer_numel)
+                b2 = self._staging_for(("layer-", i % 2), layer_numel)
+                shift = self._sweep_group(i, tr, b1, dst2=b2)
+                gets = [self._resolver(i, tr, b1, shift), self._resolver(i, tr, b2, shift)]
+            else:
+                gets = [self._resolver(i, None, None, 0)] * 2
+            only = batch.rows if i == nl - 1 else None
+            for s in range(2):
+                hs[s] = self._layer_forward(hs[s], self._layer_weights(i, gets[s]), batch, only)
+        losses = []
+        for s in range(2):
+            self._gget = ggets[s]
+            h = hs[s]
+            if nl == 0:
+                h = norm.gather_rows(h.reshape(-1, cfg.hidden_size), batch.rows)
+            x = self.final_rows(h, None)
+            table = self.lm_head_weight()
+            if batch.cand_ids is not None:
+                losses.append(loss_ops.verbalizer_ce(x, table, batch.cand_ids, batch.labels)[1])
+            else:
+                lp = loss_ops.token_logprobs(x, table, batch.targets)
+                losses.append(loss_ops.option_ce(lp, batch.seq_start, batch.ex_start, batch.labels,
+                                                 batch.classification))
+        return losses[0], losses[1]
 
     def lm_head_weight(self) -> torch.Tensor:
         return self._gget("lm_head.weight") if self.untied else self._gget(self.EMBED)

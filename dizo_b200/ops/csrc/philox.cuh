@@ -146,6 +146,24 @@ __device__ __forceinline__ uint4 perturb8_packed(const char* base, uint64_t seed
   return make_uint4(v[0], v[1], v[2], v[3]);
 }
 
+// Both signs of the same perturbation from one draw of z: theta + c z and theta - c z (bf16x2, one rounding each).
+template <int SHIFT>
+__device__ __forceinline__ void perturb8_packed_dual(const char* base, uint64_t seed, uint32_t tid, uint32_t grp,
+                                                     uint32_t c2, uint4 raw, uint4& plus, uint4& minus) {
+  uint32_t zp[4];
+  gauss8_packed<SHIFT>(base, seed, tid, grp, 0u, zp);
+  const uint32_t v[4] = {raw.x, raw.y, raw.z, raw.w};
+  const uint32_t nc2 = c2 ^ 0x80008000u;          // -c in both halves
+  uint32_t a[4], b[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(a[j]) : "r"(c2), "r"(zp[j]), "r"(v[j]));
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(b[j]) : "r"(nc2), "r"(zp[j]), "r"(v[j]));
+  }
+  plus = make_uint4(a[0], a[1], a[2], a[3]);
+  minus = make_uint4(b[0], b[1], b[2], b[3]);
+}
+
 // A coefficient rounded to bf16 and replicated into both halves of a bf16x2 register.
 __device__ __forceinline__ uint32_t bf16x2_splat(float c) {
   __nv_bfloat162 v = __float2bfloat162_rn(c);

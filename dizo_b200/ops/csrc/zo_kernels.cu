@@ -64,6 +64,7 @@ __device__ __forceinline__ uint32_t zo_group(const ZoTensor& t, long long e0) {
 struct ZoSweepArgs {
   const __nv_bfloat16* src;     // arena
   __nv_bfloat16* dst;           // arena (in place) or staging laid out like the arena range
+  __nv_bfloat16* dst2;          // optional second staging area: receives theta - c1 z while dst receives theta + c1 z
   long long dst_shift;          // dst element index = arena element index - dst_shift
   const __nv_bfloat16* anchor;  // anchor arena (theta_0 of the slotted tensors) or null
   const ZoTensor* table;
@@ -99,23 +100,33 @@ __device__ __forceinline__ void zo_chunk(const ZoSweepArgs& a, const ZoTensor& t
   constexpr bool PACKED = !Z2 && !BLEND && !NORM && !SR;
   if (PACKED) {
     if (e0 < t.numel) {
-      uint4 o = raw;
-      if (c1 != 0.f) o = perturb8_packed<TS>(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
+      uint4 o = raw, o2 = raw;
+      if (c1 != 0.f) {
+        if (a.dst2) perturb8_packed_dual<TS>(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw, o, o2);
+        else o = perturb8_packed<TS>(tab, a.seed1, t.tensor_id, zo_group(t, e0), c1_pair, raw);
+      }
       if (e0 + 8 > t.numel) {
         // ragged tail of a tensor: keep the padding elements as they were
         uint32_t ov[4] = {o.x, o.y, o.z, o.w};
+        uint32_t ov2[4] = {o2.x, o2.y, o2.z, o2.w};
         const uint32_t rawv[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (e0 + j >= t.numel) {
             const uint32_t m = (j & 1) ? 0xffff0000u : 0xffffu;
             ov[j >> 1] = (ov[j >> 1] & ~m) | (rawv[j >> 1] & m);
+            ov2[j >> 1] = (ov2[j >> 1] & ~m) | (rawv[j >> 1] & m);
           }
         }
         o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+        o2 = make_uint4(ov2[0], ov2[1], ov2[2], ov2[3]);
       }
       uint4* dp = reinterpret_cast<uint4*>(a.dst + (cpos + lane * 8 - a.dst_shift));
       if (DZ_STORE_OK(dp, 16)) *dp = o;
+      if (a.dst2) {
+        uint4* dp2 = reinterpret_cast<uint4*>(a.dst2 + (cpos + lane * 8 - a.dst_shift));
+        if (DZ_STORE_OK(dp2, 16)) *dp2 = o2;
+      }
     }
     return;
   }
@@ -445,6 +456,26 @@ extern "C" int dz_zo_sweep(const void* src, void* dst, long long dst_shift, cons
   return dz_zo_sweep_seeded(src, dst, dst_shift, anchor, table, t_begin, t_end, chunk_begin, chunk_end, seed1,
                             nullptr, c1, c1_ptr, seed2, c2, c2_ptr, alpha, chunk_sq, sr_seed, flags,
                             gauss_table, stream);
+}
+
+// The two-point estimate's two staged copies from one draw of z: dst_plus = theta + c1 z, dst_minus = theta - c1 z
+// (both laid out like the arena range, same dst_shift).  Plain perturbation only (the packed bf16 path).
+extern "C" int dz_zo_sweep_dual(const void* src, void* dst_plus, void* dst_minus, long long dst_shift,
+                                const void* table, int t_begin, int t_end, long long chunk_begin,
+                                long long chunk_end, unsigned long long seed1,
+                                const unsigned long long* seed1_dev, float c1, const float* c1_ptr, int small,
+                                const void* gauss_table, cudaStream_t stream) {
+  if (!src || !dst_plus || !dst_minus || !table || !gauss_table || t_end <= t_begin) return DZ_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(gauss_table) & 15) return DZ_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(dst_plus) & 15) || (reinterpret_cast<uintptr_t>(dst_minus) & 15)) return DZ_ERR_ALIGN;
+  ZoSweepArgs a{};
+  a.src = (const __nv_bfloat16*)src; a.dst = (__nv_bfloat16*)dst_plus; a.dst2 = (__nv_bfloat16*)dst_minus;
+  a.dst_shift = dst_shift; a.table = (const ZoTensor*)table;
+  a.t_begin = t_begin; a.t_end = t_end; a.chunk_begin = chunk_begin; a.chunk_end = chunk_end;
+  a.seed1 = seed1; a.seed1_dev = seed1_dev; a.c1 = c1; a.c1_ptr = c1_ptr;
+  a.gauss_table = (const uint32_t*)gauss_table;
+  if (small) return launch_sweep<false, false, false, false, true>(a, stream);
+  return launch_sweep<false, false, false, false>(a, stream);
 }
 
 extern "C" int dz_zo_reduce_chunks(const void* table, int num_tensors, const float* chunk_sq,

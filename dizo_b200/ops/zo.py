@@ -211,8 +211,13 @@ class ParamArena:
               seed1: int = 0, c1: float = 0.0, c1_dev: torch.Tensor | None = None,
               seed1_dev: torch.Tensor | None = None, seed2: int = 0, c2: float = 0.0, c2_dev: torch.Tensor | None = None,
               alpha: torch.Tensor | None = None, sq_out: torch.Tensor | None = None,
-              stochastic_round_seed: int | None = None, small: bool = False) -> None:
+              stochastic_round_seed: int | None = None, small: bool = False,
+              dst2: torch.Tensor | None = None) -> None:
         """dst[range] = round(blend(theta) + c1*z(seed1) + c2*z(seed2)); optional norms.
+
+        ``dst2`` (plain perturbation into staging buffers only): a second buffer that receives
+        ``theta - c1*z(seed1)`` from the same draw of z - the two forwards of the two-point estimate read the
+        two buffers, and z is generated once instead of twice.
 
         ``dst=None`` writes the arena in place; otherwise ``dst`` is a staging buffer whose
         element 0 corresponds to the first element of the range.  ``c?_dev`` (1-element fp32
@@ -235,6 +240,10 @@ class ParamArena:
         use_z2 = (c2 != 0.0) or (c2_dev is not None)
         blend = alpha is not None
         norm = sq_out is not None
+        if dst2 is not None:
+            assert dst is not None and dst2.numel() >= end - begin and dst2.dtype == self.dtype
+            assert not (use_z2 or blend or norm or stochastic_round_seed is not None), \
+                "the two-sided sweep is the plain perturbation"
         if (blend or norm) and self.anchor is None:
             raise ValueError("blend/norm need set_dizo() first")
         if self.device.type != "cuda":
@@ -244,6 +253,9 @@ class ParamArena:
                     stochastic_round_seed = sr_seed_for(seed1)
             self._sweep_cpu(t_begin, t_end, out, shift, seed1, c1, c1_dev, seed2, c2, c2_dev,
                             use_z2, alpha, sq_out, stochastic_round_seed)
+            if dst2 is not None:
+                self._sweep_cpu(t_begin, t_end, dst2, shift, seed1, -c1, c1_dev, seed2, c2, c2_dev,
+                                use_z2, alpha, sq_out, stochastic_round_seed)
             return
         assert self.dtype == torch.bfloat16, "the CUDA sweep is bf16"
         L = _lib.lib()
@@ -256,6 +268,15 @@ class ParamArena:
                                          device=self.device)
         if seed1_dev is not None:
             assert seed1_dev.dtype == torch.int64 and seed1_dev.is_cuda and seed1_dev.numel() == 1
+        if dst2 is not None:
+            rc = L.dz_zo_sweep_dual(
+                _lib.ptr(self.data), _lib.ptr(out), _lib.ptr(dst2), ctypes.c_longlong(shift),
+                _lib.ptr(self.table()), t_begin, t_end, ctypes.c_longlong(begin // CHUNK),
+                ctypes.c_longlong(end // CHUNK), ctypes.c_uint64(seed1 & (2 ** 64 - 1)), _lib.ptr(seed1_dev),
+                ctypes.c_float(c1), _lib.ptr(c1_dev), int(bool(small)), _lib.ptr(gauss_table_dev(self.device)),
+                _lib.stream_ptr())
+            _lib.check(rc, "dz_zo_sweep_dual")
+            return
         rc = L.dz_zo_sweep_seeded(
             _lib.ptr(self.data), _lib.ptr(out), ctypes.c_longlong(shift), _lib.ptr(self.anchor),
             _lib.ptr(self.table()), t_begin, t_end, ctypes.c_longlong(begin // CHUNK),

@@ -229,8 +229,7 @@ class OurTrainer:
             batch = self._to_batch(inputs)
         eps, seed = eng.eps, self.zo_random_seed
         if eng.mode == "inflight":
-            l1 = fwd(batch, Transform(seed=seed, coef=eps))
-            l2 = fwd(batch, Transform(seed=seed, coef=-eps))
+            l1, l2 = eng.forward_pair(batch, seed, loss_fn=fwd if self.args.non_diff else None)
         else:
             self.zo_perturb_parameters(scaling_factor=1)
             l1 = fwd(batch, None)

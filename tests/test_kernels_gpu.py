@@ -213,6 +213,32 @@ def test_small_footprint_sweep_equals_the_regular_one():
         assert torch.equal(a, b), kw
 
 
+def test_two_sided_sweep_equals_two_sweeps():
+    """theta + c z and theta - c z staged from one draw of z: the same bits as two sweeps with +c and -c, for
+    every group (ragged tensor tails included), in both kernel variants and with a device-side seed."""
+    ga = _arena(DEV)
+    seed_dev = torch.tensor([91], dtype=torch.int64, device=DEV)
+    for g in ga.groups():
+        lo, hi = ga.group_range(g)
+        n = ga.group_numel(g)
+        for kw in (dict(seed1=5, c1=1e-3), dict(seed1=5, c1=1e-3, small=True), dict(seed1_dev=seed_dev, c1=2e-3)):
+            plus = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+            minus = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+            a = torch.full((n,), 7.0, dtype=torch.bfloat16, device=DEV)
+            b = torch.full((n,), 7.0, dtype=torch.bfloat16, device=DEV)
+            ga.sweep(t_begin=lo, t_end=hi, dst=plus, **kw)
+            ga.sweep(t_begin=lo, t_end=hi, dst=minus, **{**kw, "c1": -kw["c1"]})
+            ga.sweep(t_begin=lo, t_end=hi, dst=a, dst2=b, **kw)
+            _sync_ok()
+            # compare what the sweeps write (the padding between pieces keeps the buffer's old content)
+            for i in range(lo, hi):
+                p_ = ga.pieces[i]
+                o = p_.offset - ga.span(lo, hi)[0]
+                assert torch.equal(a[o:o + p_.numel], plus[o:o + p_.numel]), (g, kw, p_.name)
+                assert torch.equal(b[o:o + p_.numel], minus[o:o + p_.numel]), (g, kw, p_.name)
+                assert not torch.equal(a[o:o + p_.numel], b[o:o + p_.numel])
+
+
 def test_perturb_restore_replay_and_update():
     a = _arena(DEV)
     ref = a.data.clone()

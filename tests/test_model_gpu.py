@@ -9,6 +9,8 @@ from dizo_b200.engine import DiZOProjector, ZOEngine
 from dizo_b200.models.opt import OPTModel, Transform, make_batch, preset
 from dizo_b200.ops import _lib
 
+DEV = "cuda"
+
 pytestmark = pytest.mark.gpu
 
 
@@ -71,6 +73,41 @@ def test_peft_forward_matches_cpu(mode):
     assert abs(out - ref) < 2e-2, (out, ref)
     t = Transform(seed=9, coef=1e-2)
     assert abs(gpu.loss(b.to("cuda"), t).item() - cpu.loss(b, t).item()) < 2e-2
+
+
+@pytest.mark.parametrize("family,mode", [("opt", "full"), ("opt", "lora+prefix"), ("llama", "full")])
+def test_loss_pair_equals_two_forwards(family, mode):
+    """Both sides of the two-point estimate block by block from one draw of z per block: the same two losses,
+    bit for bit, as two forwards with +eps and -eps; and a ZO step moves the parameters identically."""
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import ZOEngine
+    from dizo_b200.models.llama import LlamaModel, preset as llama_preset
+    from dizo_b200.models.opt import OPTModel, Transform, preset
+    if family == "opt":
+        cfg = preset("opt-125m", num_hidden_layers=3)
+        mk = lambda: OPTModel(cfg, DEV, torch.bfloat16, mode=mode).init_random_fast(seed=0)
+    else:
+        cfg = llama_preset("llama-tiny-gqa", hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+                           intermediate_size=704, vocab_size=2048, num_hidden_layers=3)
+        mk = lambda: LlamaModel(cfg, DEV, torch.bfloat16, mode=mode).init_random_fast(seed=0)
+    m = mk()
+    assert m.pair_supported()
+    b = synthetic_batch(0, 4, 96, cfg.vocab_size, seed=1, pad_left=7).to(DEV)
+    l1 = m.loss(b, Transform(seed=31, coef=1e-3)).clone()
+    l2 = m.loss(b, Transform(seed=31, coef=-1e-3)).clone()
+    p1, p2 = m.loss_pair(b, 31, 1e-3)
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    assert torch.equal(l1.reshape(1), p1.reshape(1)) and torch.equal(l2.reshape(1), p2.reshape(1)), (l1, p1, l2, p2)
+    # the engine's step through the pair path against a step that runs the two forwards separately
+    m2 = mk()
+    e1 = ZOEngine(m, eps=1e-3, dp_group=False)
+    e2 = ZOEngine(m2, eps=1e-3, dp_group=False)
+    e1.step(b, 1e-3, seed=5)
+    e2.step(b, 1e-3, seed=5, loss_fn=m2.loss)            # a loss function given: two separate forwards
+    torch.cuda.synchronize()
+    assert torch.equal(e1.projected_grad, e2.projected_grad)
+    assert torch.equal(m.arena.data, m2.arena.data)
 
 
 def test_zo_training_reduces_loss_and_dizo_bounds():

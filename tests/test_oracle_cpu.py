@@ -109,3 +109,26 @@ def test_none_and_zo_enhanced_agree_before_first_projection():
     for step in range(5):
         b = synthetic_batch(step, 4, 16, cfg.vocab_size, cand_ids=cands)
         assert e1.step(b, 1e-4, step).item() == e2.step(b, 1e-4, step).item()
+
+
+def test_loss_pair_equals_two_separate_forwards():
+    """One sweep per block that stages theta + eps z and theta - eps z from one draw of z, then the block on both
+    activation streams: the same two losses, bit for bit, as two forwards with +eps and -eps."""
+    import torch
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.models.llama import LlamaModel, preset as llama_preset
+    from dizo_b200.models.opt import OPTModel, Transform, preset
+    for dtype in (torch.float32, torch.bfloat16):
+        models = [OPTModel(preset("opt-tiny"), "cpu", dtype).init_random(0),
+                  OPTModel(preset("opt-tiny"), "cpu", dtype, mode="lora+prefix", num_prefix=3).init_random(0),
+                  OPTModel(preset("opt-tiny", do_layer_norm_before=False, word_embed_proj_dim=32), "cpu", dtype).init_random(0),
+                  LlamaModel(llama_preset("llama-tiny-gqa"), "cpu", dtype).init_random(0)]
+        for m in models:
+            assert m.pair_supported()
+            b = synthetic_batch(3, 4, 24, m.config.vocab_size, cand_ids=(10, 20), pad_left=5)
+            l1 = m.loss(b, Transform(seed=77, coef=1e-2))
+            l2 = m.loss(b, Transform(seed=77, coef=-1e-2))
+            p1, p2 = m.loss_pair(b, 77, 1e-2)
+            assert torch.equal(l1.reshape(1), p1.reshape(1)) and torch.equal(l2.reshape(1), p2.reshape(1)), (dtype, l1, p1, l2, p2)
+            assert not torch.equal(p1.reshape(1), p2.reshape(1))
+    assert not OPTModel(preset("opt-tiny"), "cpu", torch.float32, mode="prefix", prefix_reparam=True).pair_supported()

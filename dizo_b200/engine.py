@@ -23,6 +23,7 @@ theta <- theta_0 + gamma / ||theta - theta_0|| * (theta - theta_0).  The search 
 from __future__ import annotations
 
 import logging
+import os
 from typing import Callable
 
 import torch
@@ -30,6 +31,9 @@ import torch.distributed as dist
 
 from .models.opt import Batch, OPTModel, Transform
 from .ops.zo import GammaState, fd_eps, scalar_diff, sr_seed_for
+
+# DIZO_ZO_PAIRED=0 runs the two forwards of a step one after the other (two draws of z) - for measurements
+_PAIRED = os.environ.get("DIZO_ZO_PAIRED", "1") != "0"
 
 logger = logging.getLogger(__name__)
 
@@ -76,7 +80,8 @@ class ZOEngine:
         block where the model supports it (``OPTModel.loss_pair``), else two separate forwards."""
         eps = self.eps
         m = self.model
-        if loss_fn is None and getattr(m, "pair_supported", None) is not None and m.pair_supported():
+        if (loss_fn is None and _PAIRED and getattr(m, "pair_supported", None) is not None
+                and m.pair_supported()):
             return m.loss_pair(batch, seed, eps, seed_dev=seed_dev)
         fwd = loss_fn or self.forward
         return (fwd(batch, Transform(seed=seed, coef=eps, seed_dev=seed_dev)),

@@ -259,25 +259,45 @@ def run_ours(a, world, rank, local):
     # ---- perturb bandwidth: one pass of the in-flight perturbation over every parameter group
     #      (theta + eps z into the per-layer staging buffer, z regenerated), as each forward does;
     #      bytes = parameters read + staged copy written.  The update sweep is the same kernel in place.
-    sweep_gbs = None
+    # ---- perturb + update bandwidth: the sweeps of one step, timed on their own - the staging pass over every
+    #      parameter group as the forwards issue it (theta + eps z and theta - eps z side by side from one draw of
+    #      z where the model pairs the forwards: 2 B read + 4 B written per parameter; otherwise one side: 2 + 2)
+    #      and the update pass (stochastic rounding as in training; 2 + 2 B).  z is regenerated in every pass.
+    sweep_gbs, sweep_detail = None, None
     if par == "dp" and model.arena.trainable_numel() > 0:
         from dizo_b200.models.opt import Transform
         groups = model.arena.groups()
         biggest = max(model.arena.group_numel(g) for g in groups)
+        paired = bool(getattr(model, "pair_supported", lambda: False)()) and a.zo_mode == "inflight"
 
-        def one_pass(seed):
+        def staging_pass(seed):
             tr = Transform(seed=seed, coef=1e-3)
             for k, g in enumerate(groups):
-                model._sweep_group(g, tr, model._staging_for(("bench", k % 2), biggest))
-        one_pass(1)
-        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        w0.record()
-        for i in range(3):
-            one_pass(2 + i)
-        w1.record()
-        torch.cuda.synchronize()
-        sweep_ms = max_over_ranks(w0.elapsed_time(w1) / 3, world)
-        sweep_gbs = 2 * model.arena.trainable_numel() * model.arena.data.element_size() / sweep_ms / 1e6
+                b1 = model._staging_for(("bench", k % 2), biggest)
+                b2 = model._staging_for(("bench-", k % 2), biggest) if paired else None
+                model._sweep_group(g, tr, b1, dst2=b2)
+
+        def update_pass(seed):
+            engine.projected_grad.fill_(1e-9)            # lr * g far below a bf16 step: theta stays where it is
+            engine.update(seed, 1e-6)
+
+        def timed(fn):
+            fn(1)
+            w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            w0.record()
+            for i in range(3):
+                fn(2 + i)
+            w1.record()
+            torch.cuda.synchronize()
+            return max_over_ranks(w0.elapsed_time(w1) / 3, world)
+        stage_ms, update_ms = timed(staging_pass), timed(update_pass)
+        esz = model.arena.data.element_size()
+        pbytes = model.arena.trainable_numel() * esz
+        stage_b, update_b = (3 if paired else 2) * pbytes, 2 * pbytes
+        sweep_gbs = (stage_b + update_b) / (stage_ms + update_ms) / 1e6
+        sweep_detail = {"staging_ms": stage_ms, "staging_gbs": stage_b / stage_ms / 1e6, "two_sided": paired,
+                        "update_ms": update_ms, "update_gbs": update_b / update_ms / 1e6,
+                        "bytes_per_param_per_step": (stage_b * (1 if paired else 2) + update_b) / pbytes * esz}
     out = {
         "metric": "zo_train_tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s",
         "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
@@ -290,7 +310,7 @@ def run_ours(a, world, rank, local):
                    "zo_step_ms": step_ms, "gamma_search_ms": search_ms, "gamma_search_period": 50,
                    "l2_policy": "per-step working set (parameters) far exceeds L2; no flush needed",
                    "trainable_params": nparam},
-        "perturb_update_gbs": sweep_gbs,
+        "perturb_update_gbs": sweep_gbs, "perturb_update": sweep_detail,
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
     }
     if world > 1 and par == "dp" and a.mode == "full" and not a.skip_sharded:

@@ -241,6 +241,9 @@ class LlamaModel(OPTModel):
     def _embed(self, ids, positions, gget):
         return norm.embed(ids, None, gget(self.EMBED), None)
 
+    def _embed_param_names(self):
+        return [self.EMBED]
+
     def _final_norm(self, x, gget):
         return llama_ops.rmsnorm(x, gget(_LP + "norm.weight"), self.config.rms_norm_eps)
 

@@ -694,6 +694,10 @@ class OPTModel:
             return norm.add_rows(e, positions.reshape(-1), pos)
         return norm.embed(ids, positions, tok, pos)
 
+    def _embed_param_names(self) -> list[str]:
+        """The parameters :meth:`_embed` reads."""
+        return [self.EMBED, _P + "embed_positions.weight", _P + "project_in.weight"]
+
     def _final_norm(self, x: torch.Tensor, gget) -> torch.Tensor:
         """What sits between the last block and the LM head: final LayerNorm, project_out."""
         cfg = self.config
@@ -775,17 +779,26 @@ class OPTModel:
             g1, g2 = self._staging_for("globals", n), self._staging_for("globals-", n)
             shift = self._sweep_group(-1, tr, g1, dst2=g2)
             ggets = [self._resolver(-1, tr, g1, shift), self._resolver(-1, tr, g2, shift)]
-        hs = [self._embed(batch.input_ids, batch.positions, g) for g in ggets]
+        # the two streams are one and the same until the first perturbed tensor is read (head tuning: the whole
+        # decoder runs once, only the loss tail runs twice)
+        same = not any(n in self._where and self._where[n] is self.arena for n in self._embed_param_names())
+        h0 = self._embed(batch.input_ids, batch.positions, ggets[0])
+        hs = [h0, h0 if same else self._embed(batch.input_ids, batch.positions, ggets[1])]
         layer_numel = max((self.arena.group_numel(g) for g in groups if g >= 0), default=0)
         for i in range(nl):
+            only = batch.rows if i == nl - 1 else None
             if i in groups:
+                same = False
                 b1 = self._staging_for(("layer", i % 2), layer_numel)
                 b2 = self._staging_for(("layer-", i % 2), layer_numel)
                 shift = self._sweep_group(i, tr, b1, dst2=b2)
                 gets = [self._resolver(i, tr, b1, shift), self._resolver(i, tr, b2, shift)]
             else:
                 gets = [self._resolver(i, None, None, 0)] * 2
-            only = batch.rows if i == nl - 1 else None
+            if same:
+                h0 = self._layer_forward(hs[0], self._layer_weights(i, gets[0]), batch, only)
+                hs = [h0, h0]
+                continue
             for s in range(2):
                 hs[s] = self._layer_forward(hs[s], self._layer_weights(i, gets[s]), batch, only)
         losses = []

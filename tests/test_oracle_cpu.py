@@ -132,3 +132,16 @@ def test_loss_pair_equals_two_separate_forwards():
             assert torch.equal(l1.reshape(1), p1.reshape(1)) and torch.equal(l2.reshape(1), p2.reshape(1)), (dtype, l1, p1, l2, p2)
             assert not torch.equal(p1.reshape(1), p2.reshape(1))
     assert not OPTModel(preset("opt-tiny"), "cpu", torch.float32, mode="prefix", prefix_reparam=True).pair_supported()
+    # head tuning: nothing inside the decoder is perturbed, so the blocks run once for both sides
+    for m in (OPTModel(preset("opt-tiny"), "cpu", torch.float32, mode="head").init_random(0),
+              LlamaModel(llama_preset("llama-tiny"), "cpu", torch.float32, mode="head").init_random(0)):
+        calls = []
+        inner = m._layer_forward
+        m._layer_forward = lambda *a, **k: (calls.append(1), inner(*a, **k))[1]
+        b = synthetic_batch(3, 4, 24, m.config.vocab_size, cand_ids=(10, 20), pad_left=5)
+        p1, p2 = m.loss_pair(b, 5, 1e-2)
+        assert len(calls) == m.config.num_hidden_layers
+        m._layer_forward = inner
+        assert torch.equal(p1.reshape(1), m.loss(b, Transform(seed=5, coef=1e-2)).reshape(1))
+        assert torch.equal(p2.reshape(1), m.loss(b, Transform(seed=5, coef=-1e-2)).reshape(1))
+        assert not torch.equal(p1.reshape(1), p2.reshape(1))

@@ -520,28 +520,44 @@ class OPTModel:
                          small=small, dst2=dst2)
         return self.arena.span(lo, hi)[0]
 
-    def _lora_qkv_buffer(self, i: int) -> tuple[torch.Tensor, bool]:
+    def _lora_qkv_buffer(self, i: int, stream: int = 0) -> tuple[torch.Tensor, bool]:
         """The [3d, d] operand that receives W_q + s B_q A_q | W_k | W_v + s B_v A_v of layer ``i`` and
         whether its k section still has to be written.  With room to spare every layer keeps its own
-        buffer, so the frozen k weight is copied once and only q and v are re-merged per forward; when
-        memory is short one buffer is shared and k is copied along every time."""
+        buffer (two when both streams of a step run side by side), so the frozen k weight is copied once and
+        only q and v are re-merged per forward; when memory is short one buffer per stream is shared and k is
+        copied along every time."""
         d = self.config.hidden_size
         if self._merge_buf.get("per_layer") is None:
-            need = self.config.num_hidden_layers * 3 * d * d * torch.finfo(self.dtype).bits // 8
+            need = 2 * self.config.num_hidden_layers * 3 * d * d * torch.finfo(self.dtype).bits // 8
             free = torch.cuda.mem_get_info(self.device)[0] if self.device.type == "cuda" else 1 << 62
             self._merge_buf["per_layer"] = free > 4 * need
         if self._merge_buf["per_layer"]:
-            buf = self._merge_buf.get(i)
+            buf = self._merge_buf.get((i, stream))
             if buf is None:
                 buf = torch.empty((3 * d, d), dtype=self.dtype, device=self.device)
-                self._merge_buf[i] = buf
+                self._merge_buf[(i, stream)] = buf
                 return buf, True
             return buf, not self._k_frozen
-        buf = self._merge_buf.get("qkv")
+        buf = self._merge_buf.get(("qkv", stream))
         if buf is None:
             buf = torch.empty((3 * d, d), dtype=self.dtype, device=self.device)
-            self._merge_buf["qkv"] = buf
+            self._merge_buf[("qkv", stream)] = buf
         return buf, True
+
+    def _merged_qkv(self, i: int, get: Callable[[str], torch.Tensor], stream: int = 0) -> torch.Tensor:
+        """W_q + s B_q A_q | W_k | W_v + s B_v A_v of layer ``i`` with the adapters ``get`` resolves."""
+        d = self.config.hidden_size
+        a = layer_prefix(i) + "self_attn."
+        buf, fresh = self._lora_qkv_buffer(i, stream)
+        peft_ops.lora_merge(get(a + "q_proj.weight"), get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"),
+                            self.lora_scaling, out=buf[:d])
+        if fresh:
+            # the frozen k weight: copied by the merge kernel with a zero scale (W + 0 * B A)
+            peft_ops.lora_merge(get(a + "k_proj.weight"), get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"), 0.0,
+                                out=buf[d:2 * d])
+        peft_ops.lora_merge(get(a + "v_proj.weight"), get(a + "v_proj.lora_A"), get(a + "v_proj.lora_B"),
+                            self.lora_scaling, out=buf[2 * d:])
+        return buf
 
     def _layer_weights(self, i: int, get: Callable[[str], torch.Tensor]) -> SimpleNamespace:
         lp = layer_prefix(i)
@@ -551,20 +567,10 @@ class OPTModel:
             # the shared embeddings are a tensor of layer 0: read them through layer 0's resolver (so a
             # transform applies) and keep a copy for the layers above, whose staging buffers rotate
             self._prefix_embeds = get(a + "prefix_input_embeds").clone()
-        qw, kw, vw = get(a + "q_proj.weight"), get(a + "k_proj.weight"), get(a + "v_proj.weight")
         if self.use_lora:
-            d = self.config.hidden_size
-            buf, fresh = self._lora_qkv_buffer(i)
-            peft_ops.lora_merge(qw, get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"),
-                                self.lora_scaling, out=buf[:d])
-            if fresh:
-                # the frozen k weight: copied by the merge kernel with a zero scale (W + 0 * B A)
-                peft_ops.lora_merge(kw, get(a + "q_proj.lora_A"), get(a + "q_proj.lora_B"), 0.0, out=buf[d:2 * d])
-            peft_ops.lora_merge(vw, get(a + "v_proj.lora_A"), get(a + "v_proj.lora_B"),
-                                self.lora_scaling, out=buf[2 * d:])
-            w.qkv_w = buf
+            w.qkv_w = self._merged_qkv(i, get)
         else:
-            w.qkv_w = self._fused([qw, kw, vw])
+            w.qkv_w = self._fused([get(a + "q_proj.weight"), get(a + "k_proj.weight"), get(a + "v_proj.weight")])
         w.qkv_b = self._fused([get(a + "q_proj.bias"), get(a + "k_proj.bias"), get(a + "v_proj.bias")])
         w.out_w, w.out_b = get(a + "out_proj.weight"), get(a + "out_proj.bias")
         w.ln1_w, w.ln1_b = get(lp + "self_attn_layer_norm.weight"), get(lp + "self_attn_layer_norm.bias")
@@ -799,6 +805,11 @@ class OPTModel:
                 h0 = self._layer_forward(hs[0], self._layer_weights(i, gets[0]), batch, only)
                 hs = [h0, h0]
                 continue
+            if self._shares_block_tail():
+                # adapters only (LoRA / prefix): the rest of the block is frozen, so both streams go through its
+                # GEMMs together (twice the rows per launch: fuller waves, the weights are read once)
+                hs = self._layer_forward_pair(hs, i, gets, batch, only)
+                continue
             for s in range(2):
                 hs[s] = self._layer_forward(hs[s], self._layer_weights(i, gets[s]), batch, only)
         losses = []
@@ -816,6 +827,68 @@ class OPTModel:
                 losses.append(loss_ops.option_ce(lp, batch.seq_start, batch.ex_start, batch.labels,
                                                  batch.classification))
         return losses[0], losses[1]
+
+    def _shares_block_tail(self) -> bool:
+        """Adapter-only training (LoRA / prefix rows): between the two streams of a step a block differs in the
+        merged QKV operand and the prefix rows at most; LayerNorms, out_proj and the FFN are the same frozen tensors."""
+        return (type(self)._layer_forward is OPTModel._layer_forward and not self.prefix_reparam
+                and self.mode in ("lora", "prefix", "lora+prefix"))
+
+    @staticmethod
+    def _stack2(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+        """[2 * rows, d] holding a then b, without a copy when they already sit side by side."""
+        a2, b2 = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+        if (a2.is_contiguous() and b2.is_contiguous() and
+                a2.untyped_storage().data_ptr() == b2.untyped_storage().data_ptr() and
+                b2.data_ptr() == a2.data_ptr() + a2.numel() * a2.element_size()):
+            return torch.as_strided(a2, (2 * a2.shape[0], a2.shape[1]), a2.stride())
+        return torch.cat([a2, b2], dim=0)
+
+    def _layer_forward_pair(self, hs, i: int, gets, batch: Batch, rows: torch.Tensor | None):
+        """One block for both streams of the two-point estimate when only adapters are trained: the frozen parts
+        (LayerNorms, out_proj, FFN - and the QKV projection without LoRA) run once over both streams' rows, twice
+        the rows per launch; the QKV projection runs per stream when LoRA makes its operand differ, attention
+        always does (its prefix rows may differ)."""
+        cfg = self.config
+        B, L, d = hs[0].shape
+        M = B * L
+        pre = cfg.do_layer_norm_before
+        w = self._layer_weights(i, gets[0])
+        a = layer_prefix(i) + "self_attn."
+        H = self._stack2(hs[0], hs[1])                                   # [2M, d]
+        x = norm.layernorm(H, w.ln1_w, w.ln1_b, cfg.layer_norm_eps) if pre else H
+        if self.use_lora:
+            qkv_w1 = self._merged_qkv(i, gets[1], stream=1)
+            qkvs = [gemm.linear(x[:M], w.qkv_w, w.qkv_b), gemm.linear(x[M:], qkv_w1, w.qkv_b)]
+        else:
+            both = gemm.linear(x, w.qkv_w, w.qkv_b)
+            qkvs = [both[:M], both[M:]]
+        ctx = torch.empty((2, B, L, d), dtype=H.dtype, device=H.device)
+        for s in range(2):
+            pk = gets[s](a + "prefix_keys") if self.use_prefix else None
+            pv = gets[s](a + "prefix_values") if self.use_prefix else None
+            q3 = qkvs[s].view(B, L, 3 * d)
+            if q3.is_cuda:
+                attn_ops.attention(q3, cfg.num_attention_heads, batch.pad_left, pk, pv, out=ctx[s])
+            else:
+                ctx[s].copy_(attn_ops.attention(q3, cfg.num_attention_heads, batch.pad_left, pk, pv))
+        c = ctx.view(2 * M, d)
+        if rows is not None:
+            both_rows = torch.cat([rows, rows + M]).to(torch.int32)
+            c = norm.gather_rows(c, both_rows)
+            H = norm.gather_rows(H, both_rows)
+        h = gemm.linear(c, w.out_w, w.out_b, residual=H)
+        if not pre:
+            h = norm.layernorm(h, w.ln1_w, w.ln1_b, cfg.layer_norm_eps)
+        x2 = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps) if pre else h
+        f = gemm.linear(x2, w.fc1_w, w.fc1_b, act=cfg.activation_function)
+        h = gemm.linear(f, w.fc2_w, w.fc2_b, residual=h)
+        if not pre:
+            h = norm.layernorm(h, w.ln2_w, w.ln2_b, cfg.layer_norm_eps)
+        n = h.shape[0] // 2
+        if rows is not None:
+            return [h[:n], h[n:]]
+        return [h[:n].view(B, L, d), h[n:].view(B, L, d)]
 
     def lm_head_weight(self) -> torch.Tensor:
         return self._gget("lm_head.weight") if self.untied else self._gget(self.EMBED)

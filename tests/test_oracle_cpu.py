@@ -129,7 +129,14 @@ def test_loss_pair_equals_two_separate_forwards():
             l1 = m.loss(b, Transform(seed=77, coef=1e-2))
             l2 = m.loss(b, Transform(seed=77, coef=-1e-2))
             p1, p2 = m.loss_pair(b, 77, 1e-2)
-            assert torch.equal(l1.reshape(1), p1.reshape(1)) and torch.equal(l2.reshape(1), p2.reshape(1)), (dtype, l1, p1, l2, p2)
+            if m._shares_block_tail():
+                # adapter-only training sends both streams through the frozen GEMMs together: on the CPU the BLAS
+                # may block twice the rows differently (last bits); the GPU kernels are row-independent (exact
+                # equality is asserted there)
+                tol = dict(rtol=2e-6, atol=1e-7) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-3)
+                assert torch.allclose(l1.reshape(1), p1.reshape(1), **tol) and torch.allclose(l2.reshape(1), p2.reshape(1), **tol)
+            else:
+                assert torch.equal(l1.reshape(1), p1.reshape(1)) and torch.equal(l2.reshape(1), p2.reshape(1)), (dtype, l1, p1, l2, p2)
             assert not torch.equal(p1.reshape(1), p2.reshape(1))
     assert not OPTModel(preset("opt-tiny"), "cpu", torch.float32, mode="prefix", prefix_reparam=True).pair_supported()
     # head tuning: nothing inside the decoder is perturbed, so the blocks run once for both sides

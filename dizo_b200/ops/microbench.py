@@ -4,7 +4,7 @@ seconds, which is what a long training step sees under the power cap).
 
     python -m dizo_b200.ops.microbench gemm --m 8192 --n 15360 --k 5120 [--seconds 3]
     python -m dizo_b200.ops.microbench attn --batch 8 --seq 1024 --heads 40 --hd 128
-    python -m dizo_b200.ops.microbench sweep --mib 2048 [--flags z2,blend,norm,sr]
+    python -m dizo_b200.ops.microbench sweep --mib 2048 [--flags z2,blend,norm,sr,dual]
     python -m dizo_b200.ops.microbench layernorm --rows 8192 --d 5120
     python -m dizo_b200.ops.microbench dgrad --m 8192 --n 5120 --k 20480      # dX = dY W, W [k, n]
     python -m dizo_b200.ops.microbench attn_bwd --batch 8 --seq 1024 --heads 40 --hd 128
@@ -214,7 +214,11 @@ def main():
             kw.update(sq_out=torch.zeros(ar.n_slots, device=dev))
         if "sr" in fl:
             kw.update(stochastic_round_seed=5)
-        nbytes = 4.0 * n * (1.5 if ("blend" in fl or "norm" in fl) else 1.0)
+        if "dual" in fl:
+            # the two-sided staging sweep: theta + c z and theta - c z from one draw of z (2 B read, 4 B written)
+            kw.update(dst=torch.empty(ar.data.numel(), dtype=torch.bfloat16, device=dev),
+                      dst2=torch.empty(ar.data.numel(), dtype=torch.bfloat16, device=dev))
+        nbytes = 4.0 * n * (1.5 if ("blend" in fl or "norm" in fl or "dual" in fl) else 1.0)
         ms = time_fn(lambda: ar.sweep(**kw), a.iters, seconds=a.seconds, flush=flush)
         out.update(elements=n, flags=sorted(fl), ours_ms=ms, ours_gbs=nbytes / ms / 1e6,
                    ours_frac_of_measured=nbytes / ms / 1e6 / peaks["hbm_gbs"])

@@ -116,6 +116,10 @@ constexpr int RSLN_MAXV = 4;
 
 // Owner side of GEMM -> reduce-scatter.  part: [world][rows][ld_part] bf16 (slot r written by
 // rank r's GEMM epilogue over NVLink); flags[r] >= epoch once rank r has finished writing.
+// Pull form (mc_part != nullptr, flags == nullptr, world == 0): every rank kept its whole partial
+// product in its own copy of one symmetric buffer and a peer barrier ran since; mc_part is the
+// NVSwitch multicast address of this rank's first row there, and one multimem.ld_reduce per 16
+// bytes returns the sum over the ranks (added in fp32 inside the switch, rounded to bf16 once).
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rs_reduce_layernorm_kernel(const __nv_bfloat16* __restrict__ part, long long slot_stride,
@@ -125,13 +129,13 @@ rs_reduce_layernorm_kernel(const __nv_bfloat16* __restrict__ part, long long slo
                            const __nv_bfloat16* __restrict__ lnw, const __nv_bfloat16* __restrict__ lnb,
                            __nv_bfloat16* __restrict__ h_out, long long ldh,
                            __nv_bfloat16* __restrict__ y_out, long long ldy, int d, float eps,
-                           uint32_t* err) {
+                           uint32_t* err, const __nv_bfloat16* mc_part) {
   __shared__ float s_red[THREADS / 32];
   __shared__ float s_bcast;
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
-  if ((int)threadIdx.x < world) {
+  if (flags && (int)threadIdx.x < world) {
     if (!wait_flag(flags + threadIdx.x, epoch, err, ERR_WAIT_PEER)) s_ok = 0;
   }
   __syncthreads();
@@ -151,6 +155,18 @@ rs_reduce_layernorm_kernel(const __nv_bfloat16* __restrict__ part, long long slo
       for (int j = 0; j < 4; ++j) {
         v[i][2 * j] = bf16_lo(rr[j]) + bf16_lo(bb[j]);
         v[i][2 * j + 1] = bf16_hi(rr[j]) + bf16_hi(bb[j]);
+      }
+      if (mc_part) {
+        uint4 p4;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(p4.x), "=r"(p4.y), "=r"(p4.z), "=r"(p4.w)
+                     : "l"(mc_part + row * ld_part + idx * 8));
+        const uint32_t pp[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[i][2 * j] += bf16_lo(pp[j]);
+          v[i][2 * j + 1] += bf16_hi(pp[j]);
+        }
       }
       for (int r = 0; r < world; ++r) {
         uint4 p4 = *reinterpret_cast<const uint4*>(part + r * slot_stride + row * ld_part + idx * 8);
@@ -247,13 +263,42 @@ extern "C" int dz_norm_allreduce_gamma(const float* partial, int n, const void* 
   return cuda_rc(cudaGetLastError());
 }
 
+static int rs_reduce_layernorm_launch(const void* part, long long slot_stride, long long ld_part,
+                                      const uint32_t* flags, uint32_t epoch, int world,
+                                      const void* residual, long long ldr, const void* bias,
+                                      const void* lnw, const void* lnb, void* h_out, long long ldh,
+                                      void* y_out, long long ldy, long long rows, int d, float eps,
+                                      uint32_t* err, const void* mc_rows, cudaStream_t stream);
+
 extern "C" int dz_rs_reduce_layernorm(const void* part, long long slot_stride, long long ld_part,
                                       const uint32_t* flags, uint32_t epoch, int world,
                                       const void* residual, long long ldr, const void* bias,
                                       const void* lnw, const void* lnb, void* h_out, long long ldh,
                                       void* y_out, long long ldy, long long rows, int d, float eps,
                                       uint32_t* err, cudaStream_t stream) {
-  if (!part || !flags || !residual || !h_out || rows <= 0 || d <= 0 || world <= 0 || world > 32)
+  return rs_reduce_layernorm_launch(part, slot_stride, ld_part, flags, epoch, world, residual, ldr, bias, lnw,
+                                    lnb, h_out, ldh, y_out, ldy, rows, d, eps, err, nullptr, stream);
+}
+
+// Pull form of the above: mc_rows = multicast address of this rank's first row of the symmetric
+// partial-product buffer (row pitch ld_part); the caller ran a peer barrier after its GEMM.
+extern "C" int dz_rs_pull_layernorm(const void* mc_rows, long long ld_part, const void* residual,
+                                    long long ldr, const void* bias, const void* lnw, const void* lnb,
+                                    void* h_out, long long ldh, void* y_out, long long ldy,
+                                    long long rows, int d, float eps, uint32_t* err, cudaStream_t stream) {
+  if (!mc_rows || ((uintptr_t)mc_rows & 15)) return DZ_ERR_ALIGN;
+  return rs_reduce_layernorm_launch(nullptr, 0, ld_part, nullptr, 0, 0, residual, ldr, bias, lnw, lnb, h_out,
+                                    ldh, y_out, ldy, rows, d, eps, err, mc_rows, stream);
+}
+
+static int rs_reduce_layernorm_launch(const void* part, long long slot_stride, long long ld_part,
+                                      const uint32_t* flags, uint32_t epoch, int world,
+                                      const void* residual, long long ldr, const void* bias,
+                                      const void* lnw, const void* lnb, void* h_out, long long ldh,
+                                      void* y_out, long long ldy, long long rows, int d, float eps,
+                                      uint32_t* err, const void* mc_rows, cudaStream_t stream) {
+  if (!mc_rows && (!part || !flags || world <= 0)) return DZ_ERR_ARG;
+  if (!residual || !h_out || rows <= 0 || d <= 0 || world < 0 || world > 32)
     return DZ_ERR_ARG;
   if (y_out && (!lnw || !lnb)) return DZ_ERR_ARG;
   if ((d & 7) || (ld_part & 7) || (ldr & 7) || (ldh & 7) || (slot_stride & 7) || (y_out && (ldy & 7)))
@@ -262,12 +307,13 @@ extern "C" int dz_rs_reduce_layernorm(const void* part, long long slot_stride, l
   auto P = (const __nv_bfloat16*)part; auto R = (const __nv_bfloat16*)residual;
   auto B = (const __nv_bfloat16*)bias; auto W = (const __nv_bfloat16*)lnw; auto Lb = (const __nv_bfloat16*)lnb;
   auto H = (__nv_bfloat16*)h_out; auto Y = (__nv_bfloat16*)y_out;
+  auto MC = (const __nv_bfloat16*)mc_rows;
   if (nvec <= 128 * RSLN_MAXV)
-    rs_reduce_layernorm_kernel<128><<<(unsigned)rows, 128, 0, stream>>>(P, slot_stride, ld_part, flags, epoch, world, R, ldr, B, W, Lb, H, ldh, Y, ldy, d, eps, err);
+    rs_reduce_layernorm_kernel<128><<<(unsigned)rows, 128, 0, stream>>>(P, slot_stride, ld_part, flags, epoch, world, R, ldr, B, W, Lb, H, ldh, Y, ldy, d, eps, err, MC);
   else if (nvec <= 256 * RSLN_MAXV)
-    rs_reduce_layernorm_kernel<256><<<(unsigned)rows, 256, 0, stream>>>(P, slot_stride, ld_part, flags, epoch, world, R, ldr, B, W, Lb, H, ldh, Y, ldy, d, eps, err);
+    rs_reduce_layernorm_kernel<256><<<(unsigned)rows, 256, 0, stream>>>(P, slot_stride, ld_part, flags, epoch, world, R, ldr, B, W, Lb, H, ldh, Y, ldy, d, eps, err, MC);
   else if (nvec <= 512 * RSLN_MAXV)
-    rs_reduce_layernorm_kernel<512><<<(unsigned)rows, 512, 0, stream>>>(P, slot_stride, ld_part, flags, epoch, world, R, ldr, B, W, Lb, H, ldh, Y, ldy, d, eps, err);
+    rs_reduce_layernorm_kernel<512><<<(unsigned)rows, 512, 0, stream>>>(P, slot_stride, ld_part, flags, epoch, world, R, ldr, B, W, Lb, H, ldh, Y, ldy, d, eps, err, MC);
   else
     return DZ_ERR_TOO_LARGE;
   return cuda_rc(cudaGetLastError());

@@ -262,6 +262,33 @@ class FusedComm:
         self._launch(d, False, M, N)
         return idx
 
+    @property
+    def has_multicast(self) -> bool:
+        """The symmetric region is bound to an NVSwitch multicast object (multimem addresses work)."""
+        return bool(self.region.multicast_ptr)
+
+    def gemm_rs_pull(self, a: torch.Tensor, w: torch.Tensor) -> int:
+        """Pull form of :meth:`gemm_rs`: the partial product a @ w.T stays in this rank's copy of the
+        staging buffer (the stand-alone two-SM GEMM, no remote stores), a peer barrier follows, and
+        :meth:`rs_reduce_layernorm` lets the switch add the ranks' copies (``multimem.ld_reduce``): the
+        owner reads rows x N x 2 bytes once instead of receiving world - 1 partials.  Needs
+        :attr:`has_multicast`.  The buffer of call k is written again by call k + 2, after the barrier of
+        call k + 1, which every rank passes only once all ranks have finished reducing call k."""
+        from ..ops import gemm
+        assert self.has_multicast, "no NVSwitch multicast mapping on this region"
+        idx = self._calls["rs"] % 2
+        ch = self.rs[idx]
+        self._calls["rs"] += 1
+        M, N = a.shape[0], w.shape[0]
+        rows = M // self.world
+        assert M * N * 2 <= ch.nbytes and rows * self.world == M
+        part = ch.view[:M * N * 2].view(torch.bfloat16).view(M, N)
+        gemm.linear(a, w, out=part)
+        self.barrier()
+        ch.shape = (rows, N)
+        ch.pull = True
+        return idx
+
     def rs_reduce_layernorm(self, idx: int, residual: torch.Tensor, bias, ln_w=None, ln_b=None,
                             eps: float = 1e-5, y_out: torch.Tensor | None = None):
         """h = residual + bias + sum_r partial_r (rows this rank owns); y = LayerNorm(h) written to
@@ -272,6 +299,15 @@ class FusedComm:
         y = None
         if ln_w is not None:
             y = y_out if y_out is not None else torch.empty((rows, N), dtype=torch.bfloat16, device=self.device)
+        if getattr(ch, "pull", False):
+            ch.pull = False
+            mc = self.region.multicast_addr(ch.off) + self.rank * rows * N * 2
+            rc = _lib.lib().dz_rs_pull_layernorm(
+                c_void(mc), c_ll(N), _lib.ptr(residual), c_ll(residual.stride(0)), _lib.ptr(bias), _lib.ptr(ln_w),
+                _lib.ptr(ln_b), _lib.ptr(h), c_ll(N), _lib.ptr(y), c_ll(y.stride(0) if y is not None else 0),
+                c_ll(rows), N, c_float(eps), _lib.ptr(_lib.err_word(self.device)), _lib.stream_ptr())
+            _lib.check(rc, "dz_rs_pull_layernorm")
+            return h, y
         rc = _lib.lib().dz_rs_reduce_layernorm(
             _lib.ptr(ch.view), c_ll(rows * N), c_ll(N), _lib.ptr(ch.ready), ctypes.c_uint(ch.epoch), self.world,
             _lib.ptr(residual), c_ll(residual.stride(0)), _lib.ptr(bias), _lib.ptr(ln_w), _lib.ptr(ln_b),

@@ -1,7 +1,7 @@
 """Timing of the fused compute+collective kernels against the NCCL + GEMM composition.
 
     python -m torch.distributed.run --nproc-per-node N -m dizo_b200.parallel.microbench \
-        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas N --push-share F]
+        [--rows 8192 --hidden 9216 --ffn-dim 36864] [--iters 10] [--push-ctas N --push-share F] [--switch-reduce]
 
 For every path, device time (CUDA events, max over ranks) of the fused launch and of the
 composition it replaces (NCCL all-gather or reduce-scatter plus the framework's own GEMM), and
@@ -49,6 +49,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--push-ctas", dest="n_push", type=int, default=0,
                     help="CTAs whose push warps are active (0 = the default policy for this number of ranks)")
+    ap.add_argument("--switch-reduce", action="store_true",
+                    help="also time GEMM -> reduce-scatter with the sum taken inside the switch (multimem.ld_reduce)")
     ap.add_argument("--one-sm", action="store_true", help="keep the fused launches on the one-SM tile kernel")
     ap.add_argument("--push-share", type=float, default=0.0,
                     help="output tiles of a pushing CTA relative to the others (0 = it only pushes)")
@@ -107,8 +109,16 @@ def main():
         linear(y, w2, out=part)
         dist.reduce_scatter_tensor(rs_out, part)
         torch.nn.functional.layer_norm(rs_out + x_local, (d,), lnw, lnb)
-    report("tp_gemm_rs_ln", timed(fused_rs, a.iters, world), timed(base_rs, a.iters, world),
+    t_base_rs = timed(base_rs, a.iters, world)
+    report("tp_gemm_rs_ln", timed(fused_rs, a.iters, world), t_base_rs,
            2.0 * M * d * Fl, (world - 1) * rows * d * 2)
+    if a.switch_reduce and fc.has_multicast:
+        # pull form: local GEMM, barrier, the switch adds the ranks' copies while the owner reads its rows
+        def pull_rs():
+            idx = fc.gemm_rs_pull(y, w2)
+            fc.rs_reduce_layernorm(idx, x_local, lnb, lnw, lnb)
+        report("tp_gemm_rs_ln_switch_reduce", timed(pull_rs, a.iters, world), t_base_rs,
+               2.0 * M * d * Fl, (world - 1) * rows * d * 2)
 
     # ---- FSDP: shard push + perturbation + GEMM (fc1 of the full width, per-rank tokens)
     xs = torch.randn(M, d, device=dev, generator=g).bfloat16()

@@ -1,7 +1,8 @@
 """Worker for tests/test_multigpu_fused.py: run under torchrun on >= 2 GPUs.
 
 Checks every fused compute+collective path against the composition of an NCCL collective and
-the single-GPU kernels.  NVLS is off and the kernels use plain peer stores (no multimem)."""
+the single-GPU kernels.  NVLS is off and the kernels use plain peer stores; with ``--multimem`` only the two
+paths that reduce inside the switch run (multimem.ld_reduce on the symmetric region's multicast address)."""
 import os
 import sys
 
@@ -18,6 +19,48 @@ from dizo_b200.ops.zo import GammaState  # noqa: E402
 from dizo_b200.parallel.fused import FusedComm  # noqa: E402
 
 
+def switch_reduction(fc, dev, rank, world, g):
+    """Norm all-reduce and GEMM -> reduce-scatter -> LayerNorm with the sum taken inside the switch."""
+    if not fc.has_multicast:
+        if rank == 0:
+            print("FUSED_OK (no multicast mapping on this box: nothing to check)")
+        return dist.destroy_process_group()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+    gs = GammaState(6, dev)
+    for rep in range(3):
+        part = torch.arange(1, 7, device=dev, dtype=torch.float32) * (rank + 1) * (rep + 1)
+        fc.norm_allreduce_gamma(part, gs, reinit=True, use_multimem=True)
+        want = part.clone()
+        dist.all_reduce(want)
+        torch.cuda.synchronize()
+        assert torch.allclose(gs.sq, want), (gs.sq, want)
+    M, d, Fl = 1024 * world, 2560, 1280
+    rows = M // world
+    y = torch.randn(M, Fl, device=dev, generator=g).bfloat16()
+    w2_l = (torch.randn(d, Fl * world, device=dev, generator=g) * 0.03).bfloat16()[:, rank * Fl:(rank + 1) * Fl].contiguous()
+    b2 = torch.randn(d, device=dev, generator=g).bfloat16()
+    lnw = torch.randn(d, device=dev, generator=g).bfloat16()
+    lnb = torch.randn(d, device=dev, generator=g).bfloat16()
+    resid_all = torch.randn(M, d, device=dev, generator=g).bfloat16()
+    for rep in range(4):                                    # both buffers twice: reuse after the barrier
+        y_rep = (y.float() * (1 + 0.25 * rep)).bfloat16()
+        resid = resid_all[rank * rows:(rank + 1) * rows]
+        idx = fc.gemm_rs_pull(y_rep, w2_l)
+        h, z = fc.rs_reduce_layernorm(idx, resid, b2, lnw, lnb)
+        part_ref = linear(y_rep, w2_l, out_dtype=torch.float32)
+        dist.all_reduce(part_ref)
+        h_ref = (part_ref[rank * rows:(rank + 1) * rows] + b2.float() + resid.float()).bfloat16()
+        z_ref = layernorm(h_ref, lnw, lnb)
+        torch.cuda.synchronize()
+        assert rel(h, h_ref) < 6e-3, ("gemm_rs_pull", rep, rel(h, h_ref))
+        assert rel(z, z_ref) < 1e-2, ("rs_pull_ln", rep, rel(z, z_ref))
+    _lib.check_device_errors()
+    dist.barrier()
+    if rank == 0:
+        print("FUSED_OK switch reduction")
+    dist.destroy_process_group()
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -30,6 +73,8 @@ def main():
     Mx, dx, Fx = cases[-1][:3]
     fc = FusedComm(ag_bytes=Mx * dx * 2, rs_bytes=Mx * dx * 2, w_bytes=max(Fx, 3 * cases[-1][4]) * dx * 2, n_push=8)
     g = torch.Generator(device=dev).manual_seed(1234)          # same stream on every rank
+    if "--multimem" in sys.argv:
+        return switch_reduction(fc, dev, rank, world, g)
 
     # ---- barrier + norm all-reduce fused with the gamma arithmetic
     fc.barrier()

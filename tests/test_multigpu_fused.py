@@ -22,6 +22,19 @@ def test_fused_collectives_match_nccl_compositions():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_switch_reduction_matches_nccl():
+    """multimem.ld_reduce forms (norm all-reduce; GEMM -> reduce-scatter pulled through the switch); the worker
+    reports success without checking anything where the symmetric region has no multicast mapping."""
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29536",
+           os.path.join(ROOT, "tests", "multigpu_fused_worker.py"), "--multimem"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "FUSED_OK" in res.stdout, (res.stdout[-3000:], res.stderr[-3000:])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tensor_parallel_model_matches_unsharded():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",

@@ -1,4 +1,4 @@
-"""Differentiable statement of the OPT forward, for the two places that need a backward pass.
+"""Differentiable statement of the OPT and LLaMA-family forwards, for the two places that need a backward pass.
 
 1. The first-order gamma search of DiZO (``--enhanced fo``; large_models/trainer.py:714-741,
    :805-830): the loss is differentiated with respect to the per-tensor gamma scalars only.
@@ -53,6 +53,53 @@ def _ln(x, w, b, eps):
     return F.layer_norm(x.float(), (x.shape[-1],), w.float(), b.float(), eps).to(x.dtype)
 
 
+def _rms(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+def _llama_hidden(model, batch: Batch, W: Callable, use_checkpoint: bool) -> torch.Tensor:
+    """Hidden states [B, L, d] of a LLaMA-family model before the final norm (the statement of
+    ``LlamaModel._layer_forward``: RMSNorm, rotary q / k with grouped-query head expansion, SwiGLU)."""
+    from ..ops.llama import rope_qkv_reference
+    cfg = model.config
+    ids = batch.input_ids.long()
+    B, L = ids.shape
+    d, H, Hkv, hd = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    h = F.embedding(ids, W(model.EMBED))
+
+    def layer(i, h):
+        lp = model.layer_prefix(i)
+        a = lp + "self_attn."
+        x = _rms(h, W(lp + "input_layernorm.weight"), cfg.rms_norm_eps)
+        qkv = torch.cat([F.linear(x, W(a + "q_proj.weight")), F.linear(x, W(a + "k_proj.weight")),
+                         F.linear(x, W(a + "v_proj.weight"))], dim=-1)
+        qkv = rope_qkv_reference(qkv.reshape(B * L, -1), L, model.num_prefix, H, Hkv, hd,
+                                 cfg.rope_theta).view(B, L, 3 * d)
+        if model.use_prefix and model.prefix_reparam:
+            emb = W(model.layer_prefix(0) + "self_attn.prefix_input_embeds")
+
+            def mlp(stem):
+                mid = torch.tanh(F.linear(emb, W(stem + "0.weight"), W(stem + "0.bias")))
+                return F.linear(mid, W(stem + "2.weight"), W(stem + "2.bias"))
+            pk, pv = mlp(a + "prefix_mlp_keys."), mlp(a + "prefix_mlp_values.")
+        else:
+            pk = W(a + "prefix_keys") if model.use_prefix else None
+            pv = W(a + "prefix_values") if model.use_prefix else None
+        ctx = _attention(qkv, H, batch.pad_left, pk, pv)
+        h = h + F.linear(ctx, W(a + "o_proj.weight"))
+        x = _rms(h, W(lp + "post_attention_layernorm.weight"), cfg.rms_norm_eps)
+        f = F.silu(F.linear(x, W(lp + "mlp.gate_proj.weight"))) * F.linear(x, W(lp + "mlp.up_proj.weight"))
+        return h + F.linear(f, W(lp + "mlp.down_proj.weight"))
+
+    for i in range(cfg.num_hidden_layers):
+        if use_checkpoint and torch.is_grad_enabled():
+            h = checkpoint(layer, i, h, use_reentrant=False)
+        else:
+            h = layer(i, h)
+    return h
+
+
 def functional_loss(model: OPTModel, batch: Batch, weight_fn: Optional[Callable] = None,
                     use_checkpoint: bool = True) -> torch.Tensor:
     """Scalar loss with autograd.  ``weight_fn(name, tensor)`` may replace any trainable tensor
@@ -64,6 +111,11 @@ def functional_loss(model: OPTModel, batch: Batch, weight_fn: Optional[Callable]
         t = model.param(name)
         return wf(name, t) if model._where[name] is model.arena else t
 
+    if cfg.model_type != "opt":
+        B, L = batch.input_ids.shape
+        h = _llama_hidden(model, batch, W, use_checkpoint)
+        x = _rms(h.reshape(B * L, cfg.hidden_size)[batch.rows.long()], W("model.norm.weight"), cfg.rms_norm_eps)
+        return _loss_tail(batch, x, W("lm_head.weight") if model.untied else W(model.EMBED))
     ids = batch.input_ids.long()
     B, L = ids.shape
     d = cfg.hidden_size
@@ -120,7 +172,11 @@ def functional_loss(model: OPTModel, batch: Batch, weight_fn: Optional[Callable]
         x = _ln(x, W(_P + "final_layer_norm.weight"), W(_P + "final_layer_norm.bias"), cfg.layer_norm_eps)
     if cfg.word_embed_proj_dim != d:
         x = F.linear(x, W(_P + "project_out.weight"))
-    table = W("lm_head.weight") if model.untied else W(_P + "embed_tokens.weight")
+    return _loss_tail(batch, x, W("lm_head.weight") if model.untied else W(_P + "embed_tokens.weight"))
+
+
+def _loss_tail(batch: Batch, x: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """The loss of the rows ``x`` [R, d] (already normalised) under the head ``table`` [V, d]."""
     if batch.cand_ids is not None:
         logits = x.float() @ table[batch.cand_ids.long()].float().t()
         return F.cross_entropy(logits, batch.labels.long())

@@ -344,10 +344,8 @@ class OurTrainer:
         if a.enhanced == "fo":
             from .models import gamma_grad
             if not gamma_grad.supported(self.model):
-                # configurations the kernel backward does not cover (GELU blocks, sharded LoRA): autograd statement
-                if self.model.config.model_type != "opt":
-                    raise NotImplementedError("--enhanced fo differentiates OPT blocks; use --enhanced zo for "
-                                              f"{self.model.config.model_type} models")
+                # configurations the kernel backward does not cover (GELU blocks, sharded LoRA, LLaMA-family
+                # blocks): autograd statement
                 from .models.opt_autograd import make_fo_loss
                 fo_loss = make_fo_loss(self.model)
         self._dizo_seed_rng = np.random.RandomState(a.seed + 7919)
@@ -455,8 +453,6 @@ class OurTrainer:
     def train(self, resume_from_checkpoint: Optional[str] = None) -> Dict[str, Any]:
         a = self.args
         assert a.trainer in ("zo", "regular"), "train() needs --trainer zo|regular"
-        if a.trainer == "regular" and self.model.config.model_type != "opt":
-            raise NotImplementedError("--trainer regular (first-order comparison arm) is built for OPT models")
         n = len(self.train_dataset)
         gb = a.per_device_train_batch_size * self._world
         accum = max(1, a.gradient_accumulation_steps) if a.trainer == "regular" else 1

@@ -143,3 +143,44 @@ def test_command_line_trains_saves_and_hugging_face_reloads(tmp_path, monkeypatc
     rc = main(["--task_name", "Synthetic", "--model_name", str(out), "--num_train", "0", "--num_eval", "4",
                "--output_dir", str(tmp_path / "eval"), "--head_tuning", "--trainer", "none"])
     assert rc == 0
+
+
+@pytest.mark.parametrize("name,mode", [("llama-tiny-gqa", "full"), ("llama-tiny", "prefix")])
+def test_autograd_statement_equals_the_forward_and_differentiates_alpha(name, mode):
+    """The differentiable statement used by --enhanced fo / --trainer regular: same loss as the forward of the
+    engine, and d loss / d alpha (blend of k / v weights with their anchors) equal to central differences."""
+    from dizo_b200.engine import DiZOProjector
+    from dizo_b200.models.opt_autograd import functional_loss, make_fo_loss
+    cfg = preset(name)
+    m = LlamaModel(cfg, "cpu", torch.float32, mode=mode, num_prefix=3).init_random(0)
+    ids, mask = _inputs(cfg)
+    b = make_batch(ids, mask, rows=torch.tensor([16, 33, 50], dtype=torch.int32),
+                   targets=torch.tensor([5, 6, 7], dtype=torch.int32), seq_start=torch.tensor([0, 1, 2, 3], dtype=torch.int32),
+                   ex_start=torch.tensor([0, 3], dtype=torch.int32), labels=torch.tensor([1], dtype=torch.int32))
+    assert abs(float(functional_loss(m, b, use_checkpoint=False)) - float(m.loss(b))) < 1e-5
+    if mode != "full":
+        return
+    proj = DiZOProjector(m)
+    g = torch.Generator().manual_seed(3)
+    for n in m.arena.slot_names:
+        m.param(n).add_(torch.randn(m.param(n).shape, generator=g) * 0.05)
+    fo = make_fo_loss(m)
+    alpha = torch.full((proj.n,), 0.8, dtype=torch.float32).requires_grad_(True)
+    fo(b, alpha).backward()
+    for s in (0, proj.n - 1):
+        e = torch.zeros(proj.n)
+        e[s] = 1e-2
+        with torch.no_grad():
+            fd = (float(fo(b, alpha.detach() + e)) - float(fo(b, alpha.detach() - e))) / 2e-2
+        assert abs(fd - float(alpha.grad[s])) < 2e-3 * max(1.0, abs(fd)), (s, fd, float(alpha.grad[s]))
+
+
+@pytest.mark.parametrize("extra", [("--trainer", "zo", "--enhanced", "fo", "--dizo_interval", "2", "--dizo_max_iters", "2"),
+                                   ("--trainer", "regular", "--learning_rate", "1e-3")])
+def test_command_line_first_order_paths(tmp_path, monkeypatch, extra):
+    monkeypatch.chdir(tmp_path)
+    rc = main(["--task_name", "Synthetic", "--model_name", "llama-tiny", "--random_init",
+               "--num_train", "16", "--num_dev", "4", "--num_eval", "4", "--max_steps", "4",
+               "--per_device_train_batch_size", "4", "--output_dir", str(tmp_path / "run"),
+               "--train_as_classification", "--train_set_seed", "0", *extra])
+    assert rc == 0

@@ -94,3 +94,9 @@ def test_model_matches_cpu_statement_and_zo_step_runs(name):
     _sync_ok()
     assert not torch.equal(before, gpu.param(gpu.EMBED))
     assert torch.isfinite(torch.as_tensor(float(l1)))
+    # the differentiable statement (first-order gamma search, first-order fine-tuning) on the device in bf16
+    from dizo_b200.models.opt_autograd import functional_loss
+    with torch.no_grad():
+        fl = functional_loss(gpu, b.to(DEV), use_checkpoint=False)
+    _sync_ok()
+    assert torch.isfinite(fl) and abs(fl.item() - float(l1)) < 0.2 * max(1.0, abs(float(l1)))

@@ -234,7 +234,7 @@ class LlamaModel(OPTModel):
 
     def _mlp(self, h: torch.Tensor, w: SimpleNamespace) -> torch.Tensor:
         x = llama_ops.rmsnorm(h, w.ln2_w, self.config.rms_norm_eps)
-        f = llama_ops.silu_mul(gemm.linear(x, w.gu_w))
+        f = gemm.linear_swiglu(x, w.gu_w)
         return gemm.linear(f, w.down_w, residual=h)
 
     # ------------------------------------------------------------------ forward

@@ -123,7 +123,11 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const uint32_t b_dst = a_dst + G2_A_BYTES;
           if (leader) mbar_arrive_expect_tx(full_local, 2 * G2_STAGE_BYTES);  // both CTAs' bytes
           tma_load_2d_2sm(a_dst, &tmA, full_leader, kb * G2_BK, mb * G2_BM + (int)rank * 128);
-          tma_load_2d_2sm(b_dst, &tmB, full_leader, kb * G2_BK, nb * G2_BN + (int)rank * (G2_BN / 2));
+          // act 3 (SwiGLU over W = gate rows | up rows): the leader's half of the tile is 128 gate rows, the
+          // peer's half the matching 128 up rows, so that column j and column 128 + j of the accumulator pair up
+          const int b_row = p.act == 3 ? (int)rank * (p.N >> 1) + nb * (G2_BN / 2)
+                                       : nb * G2_BN + (int)rank * (G2_BN / 2);
+          tma_load_2d_2sm(b_dst, &tmB, full_leader, kb * G2_BK, b_row);
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -182,6 +186,32 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const long long row = (long long)mb * G2_BM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quad * 32) << 16);
+      if (p.act == 3) {
+        // out[row, nb * 128 + j] = silu(gate_j) * up_j from the fp32 accumulators, one rounding to bf16
+#pragma unroll 1
+        for (int c = 0; c < G2_BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c * 32, g);
+          tmem_ld_32x32(t_row + G2_BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          auto f = [](uint32_t a, uint32_t b) {
+            const float x = __uint_as_float(a);
+            return x / (1.f + __expf(-x)) * __uint_as_float(b);
+          };
+          uint4* op4 = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo +
+                                                nb * (G2_BN / 2) + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(f(g[q * 8 + 0], u[q * 8 + 0]), f(g[q * 8 + 1], u[q * 8 + 1]));
+            o.y = pack_bf16x2(f(g[q * 8 + 2], u[q * 8 + 2]), f(g[q * 8 + 3], u[q * 8 + 3]));
+            o.z = pack_bf16x2(f(g[q * 8 + 4], u[q * 8 + 4]), f(g[q * 8 + 5], u[q * 8 + 5]));
+            o.w = pack_bf16x2(f(g[q * 8 + 6], u[q * 8 + 6]), f(g[q * 8 + 7], u[q * 8 + 7]));
+            if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < G2_BN / 32; ++c) {
         uint32_t r[32];
@@ -273,6 +303,7 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
         }
       }
+      }
       // this CTA's half of the accumulator is drained: tell the leader's MMA issuer
       tc_fence_before();
       __syncwarp();
@@ -312,6 +343,9 @@ extern "C" int dz_gemm2_bf16_tn(const void* A, long long lda, const void* W, lon
   if ((reinterpret_cast<uintptr_t>(out) & 15) || ((ldo * esz) & 15)) return DZ_ERR_ALIGN;
   if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) return DZ_ERR_ALIGN;
   if (residual && ((reinterpret_cast<uintptr_t>(residual) & 15) || (ldr & 7))) return DZ_ERR_ALIGN;
+  // act 3: W = gate rows | up rows (N / 2 each), out [M, N / 2] = silu(A gate^T) * (A up^T), bf16, no bias
+  if (act == 3 && ((N % G2_BN) || bias || residual || out_fp32 || out_scale != 1.0f || ldo < N / 2))
+    return DZ_ERR_ARG;
   Gemm2Args a{};
   a.M = M; a.N = N; a.K = K;
   a.out = out; a.ldo = ldo;

@@ -37,6 +37,34 @@ def linear_reference(x, w, bias=None, act=None, residual=None, scale: float = 1.
     return y.to(out_dtype or x.dtype)
 
 
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ gate.T) * (x @ up.T) for ``w_gate_up`` [2F, K] = gate rows | up rows -> [..., F].
+
+    Where the two-SM kernel runs, each 256-column accumulator tile holds 128 gate columns beside the matching
+    128 up columns (the two CTAs of a pair load their halves of the W tile from the two sections) and the
+    epilogue writes the product: the [M, 2F] intermediate never reaches memory.  Other shapes go through
+    :func:`linear` and the stand-alone ``silu_mul`` kernel."""
+    from . import llama as llama_ops
+    N, K = w_gate_up.shape
+    F = N // 2
+    x2 = x.reshape(-1, K)
+    M = x2.shape[0]
+    fused = (x.is_cuda and _VARIANT in (0, 2) and N % 256 == 0 and M >= 256
+             and ((M + 255) // 256) * (N // 256) >= 48)
+    if not fused:
+        return llama_ops.silu_mul(linear(x, w_gate_up))
+    assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.stride(-1) == 1
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().dz_gemm2_bf16_tn(
+        _lib.ptr(x2), ctypes.c_longlong(x2.stride(0)), _lib.ptr(w_gate_up), ctypes.c_longlong(w_gate_up.stride(0)),
+        _lib.ptr(out), ctypes.c_longlong(F), None, None, ctypes.c_longlong(0),
+        M, N, K, 3, 0, ctypes.c_float(1.0), _lib.ptr(_lib.err_word(x.device)), _lib.stream_ptr())
+    _lib.check(rc, "dz_gemm2_bf16_tn")
+    return out.reshape(*x.shape[:-1], F)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
            residual: torch.Tensor | None = None, scale: float = 1.0,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,

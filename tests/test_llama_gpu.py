@@ -60,6 +60,29 @@ def test_silu_mul(rows, F):
     assert _rel(y.cpu(), ref) < 4e-3
 
 
+@pytest.mark.parametrize("M,K,F", [(2048, 512, 3072), (2000, 1024, 1792), (4096, 256, 11008), (192, 256, 1024)])
+def test_gemm_with_swiglu_epilogue(M, K, F):
+    """silu(x gate^T) * (x up^T) from the two-SM GEMM's epilogue (the last shape takes the unfused route)."""
+    from dizo_b200.ops import gemm
+    g = torch.Generator(device=DEV).manual_seed(M + F)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(2 * F, K, device=DEV, generator=g) * K ** -0.5).bfloat16()
+    y = gemm.linear_swiglu(x, w)
+    _sync_ok()
+    assert y.shape == (M, F)
+    acc = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(acc[:, :F]) * acc[:, F:]
+    assert _rel(y, ref) < 6e-3
+    # against the unfused route (bf16 intermediate): same up to that rounding
+    unfused = llama_ops.silu_mul(gemm.linear(x, w))
+    assert _rel(y, unfused) < 1e-2
+    # a view of a wider weight buffer (row pitch larger than K)
+    wide = torch.zeros(2 * F, K + 64, device=DEV, dtype=torch.bfloat16)
+    wide[:, :K] = w
+    assert torch.equal(gemm.linear_swiglu(x, wide[:, :K]), y)
+    _sync_ok()
+
+
 @pytest.mark.parametrize("name", ["llama-tiny", "llama-tiny-gqa"])
 def test_model_matches_cpu_statement_and_zo_step_runs(name):
     from dizo_b200.data.synthetic import synthetic_batch

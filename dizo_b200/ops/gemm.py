@@ -18,6 +18,8 @@ from . import _lib
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
 # 0 = choose per shape, 1 = one-SM kernel, 2 = two-SM (cta_group::2) kernel
 _VARIANT = int(os.environ.get("DIZO_GEMM_VARIANT", "0"))
+# 0: SwiGLU as a GEMM followed by the stand-alone silu_mul kernel (for A/B measurements)
+_SWIGLU_FUSED = os.environ.get("DIZO_SWIGLU_FUSED", "1") != "0"
 
 
 def linear_reference(x, w, bias=None, act=None, residual=None, scale: float = 1.0,
@@ -49,7 +51,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     F = N // 2
     x2 = x.reshape(-1, K)
     M = x2.shape[0]
-    fused = (x.is_cuda and _VARIANT in (0, 2) and N % 256 == 0 and M >= 256
+    fused = (_SWIGLU_FUSED and x.is_cuda and _VARIANT in (0, 2) and N % 256 == 0 and M >= 256
              and ((M + 255) // 256) * (N // 256) >= 48)
     if not fused:
         return llama_ops.silu_mul(linear(x, w_gate_up))

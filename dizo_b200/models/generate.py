@@ -286,7 +286,7 @@ def _make_decoder(model, B: int, max_len: int) -> _Decoder:
         return _TPDecoder(model, B, max_len)
     if kind in ("FSDPOPTModel", "FSDPCompositionModel"):
         return _FSDPDecoder(model, B, max_len)
-    if kind == "PPOPTModel":
+    if kind in ("PPOPTModel", "PPLlamaModel"):
         return _PPDecoder(model, B, max_len)
     raise NotImplementedError(f"autoregressive decoding is not built for {kind}")
 

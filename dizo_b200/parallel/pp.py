@@ -1,4 +1,4 @@
-"""Pipeline-parallel OPT for zeroth-order training: consecutive blocks on consecutive ranks.
+"""Pipeline-parallel OPT / LLaMA for zeroth-order training: consecutive blocks on consecutive ranks.
 
 The reference's only multi-GPU placement is ``device_map='auto'`` (large_models/run.py:167-181):
 accelerate puts consecutive layers on different GPUs and runs them one after the other, one GPU
@@ -26,9 +26,9 @@ import re
 import torch
 import torch.distributed as dist
 
-from ..models.opt import _P, Batch, OPTConfig, OPTModel, Transform
+from ..models.llama import LlamaModel
+from ..models.opt import Batch, OPTModel, Transform
 from ..ops import loss as loss_ops
-from ..ops import norm
 
 _LAYER_RE = re.compile(r"layers\.(\d+)\.")
 
@@ -44,16 +44,20 @@ def stage_bounds(n_layers: int, n_stages: int) -> list[tuple[int, int]]:
     return out
 
 
-class PPOPTModel(OPTModel):
-    def __init__(self, config: OPTConfig, device, dtype=torch.bfloat16, group=None, micro_batches: int = 0,
-                 **kw):
+class _Pipeline:
+    """The pipeline placement, written against the architecture hooks of :class:`OPTModel` (``EMBED``,
+    ``_embed``, ``_embed_param_names``, ``_layer_weights``, ``_layer_forward``, ``final_rows``); mixed into the
+    OPT and LLaMA model classes below."""
+
+    def __init__(self, config, device, dtype=torch.bfloat16, group=None, micro_batches: int = 0, **kw):
         self.group = group if group is not None else dist.group.WORLD
         self.n = dist.get_world_size(self.group)
         self.stage = dist.get_rank(self.group)
         assert config.num_hidden_layers >= self.n, "more pipeline stages than blocks"
         self.lo, self.hi = stage_bounds(config.num_hidden_layers, self.n)[self.stage]
         self.micro_batches = micro_batches            # 0 = one micro-batch per stage
-        assert config.word_embed_proj_dim == config.hidden_size, "project_in/out models are not staged"
+        assert getattr(config, "word_embed_proj_dim", config.hidden_size) == config.hidden_size, \
+            "project_in/out models are not staged"
         assert not kw.get("prefix_reparam"), "the shared prefix embeddings live with the first block: not staged"
         super().__init__(config, device, dtype, **kw)
 
@@ -63,11 +67,11 @@ class PPOPTModel(OPTModel):
         if m:
             return self.lo <= int(m.group(1)) < self.hi
         first, last = self.stage == 0, self.stage == self.n - 1
-        if name == _P + "embed_tokens.weight":
+        if name == self.EMBED:
             return first or (last and not self.untied)           # tied LM head reads the table
-        if name == _P + "embed_positions.weight":
+        if name in self._embed_param_names():
             return first
-        return last                                               # final LayerNorm, lm_head.weight
+        return last                                               # final norm, lm_head.weight
 
     def _rank_of(self, s: int) -> int:
         return dist.get_global_rank(self.group, s) if self.group is not dist.group.WORLD else s
@@ -80,7 +84,7 @@ class PPOPTModel(OPTModel):
         for p in parts:
             sd.update(p)
         if not self.untied:
-            sd["lm_head.weight"] = sd[_P + "embed_tokens.weight"]
+            sd["lm_head.weight"] = sd[self.EMBED]
         return sd
 
     def state_dict(self) -> dict:
@@ -136,8 +140,7 @@ class PPOPTModel(OPTModel):
             mb = dataclasses.replace(batch, input_ids=batch.input_ids[a:b], positions=batch.positions[a:b],
                                      pad_left=batch.pad_left[a:b] if batch.pad_left is not None else None)
             if first:
-                h = norm.embed(mb.input_ids, mb.positions, self._gget(_P + "embed_tokens.weight"),
-                               self._gget(_P + "embed_positions.weight"))
+                h = self._embed(mb.input_ids, mb.positions, self._gget)
             else:
                 h = torch.empty((b - a, L, d), dtype=self.dtype, device=self.device)
                 dist.recv(h, src=prev_r, group=self.group)
@@ -193,3 +196,11 @@ class PPOPTModel(OPTModel):
         return self._from_last(lambda: gemm.linear(self.final_rows(h, rows), self.lm_head_weight(),
                                                    out_dtype=torch.float32),
                                (rows.numel(), self.config.vocab_size))
+
+
+class PPOPTModel(_Pipeline, OPTModel):
+    """OPT blocks over the ranks of ``group``."""
+
+
+class PPLlamaModel(_Pipeline, LlamaModel):
+    """LLaMA-family blocks over the ranks of ``group`` (every stage builds the rotary table it needs)."""

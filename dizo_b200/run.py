@@ -144,12 +144,20 @@ class Framework:
             world = torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
             self.dp_group = None                      # None: the default group, when there is one
             if cfg.model_type != "opt":
-                if a.pp > 1 or a.tp > 1 or a.fsdp_shard:
-                    raise NotImplementedError("--pp / --tp / --fsdp_shard shard the OPT family; LLaMA-family "
-                                              "models run replicated (data parallel)")
-                from .models.llama import LlamaModel
-                model = LlamaModel(cfg, self.device, self._dtype(), mode=mode, num_prefix=a.num_prefix,
-                                   prefix_reparam=not a.no_reparam)
+                if a.tp > 1 or a.fsdp_shard:
+                    raise NotImplementedError("--tp / --fsdp_shard shard the OPT family; LLaMA-family models run "
+                                              "replicated (data parallel) or as a pipeline of blocks (--pp)")
+                if a.pp > 1:
+                    assert a.pp == world, "--pp must equal the number of ranks (one pipeline)"
+                    assert a.enhanced != "fo", "the first-order gamma search is not staged over a pipeline"
+                    from .parallel.pp import PPLlamaModel
+                    model = PPLlamaModel(cfg, self.device, self._dtype(), micro_batches=a.pp_micro_batches,
+                                         mode=mode, num_prefix=a.num_prefix, prefix_reparam=not a.no_reparam)
+                    self.dp_group = False
+                else:
+                    from .models.llama import LlamaModel
+                    model = LlamaModel(cfg, self.device, self._dtype(), mode=mode, num_prefix=a.num_prefix,
+                                       prefix_reparam=not a.no_reparam)
             elif a.pp > 1:
                 # consecutive blocks on consecutive ranks; every rank sees the same batch
                 assert a.pp == world, "--pp must equal the number of ranks (one pipeline)"

@@ -58,6 +58,51 @@ PP_SCRIPT = textwrap.dedent('''
 ''')
 
 
+PP_LLAMA_SCRIPT = textwrap.dedent('''
+    import torch, torch.distributed as dist
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import ZOEngine, DiZOProjector
+    from dizo_b200.models.llama import LlamaModel, preset
+    from dizo_b200.models.opt import Transform
+    from dizo_b200.parallel.pp import PPLlamaModel
+    dist.init_process_group("gloo")
+    rank = dist.get_rank()
+    cfg = preset("llama-tiny-gqa", num_hidden_layers=3)
+    for mode in ("full", "prefix"):
+        solo = LlamaModel(cfg, "cpu", torch.float32, mode=mode, num_prefix=3).init_random(0)
+        pp = PPLlamaModel(cfg, "cpu", torch.float32, micro_batches=2, mode=mode, num_prefix=3)
+        pp.load_state_dict(solo.state_dict(), strict=False)
+        assert pp.num_parameters() < solo.num_parameters()
+        def batch(step, pad=0): return synthetic_batch(step, 5, 16, cfg.vocab_size, cand_ids=(10, 20), pad_left=pad)
+        for tr in (None, Transform(seed=5, coef=1e-2)):
+            a, b = solo.loss(batch(0, 3), tr), pp.loss(batch(0, 3), tr)
+            assert torch.allclose(a.reshape(1), b.reshape(1), rtol=1e-5, atol=1e-6), (mode, a, b)
+        e1, e2 = ZOEngine(solo, eps=1e-3, dp_group=False), ZOEngine(pp, eps=1e-3, dp_group=False)
+        for step in range(3):
+            l1 = e1.step(batch(step), 1e-3, seed=100 + step)
+            l2 = e2.step(batch(step), 1e-3, seed=100 + step)
+            assert abs(float(l1) - float(l2)) < 1e-5, (mode, step, l1, l2)
+        full, ref = pp.gather_state_dict(), solo.state_dict()
+        assert set(full) == set(ref)
+        for k in ref:
+            assert torch.allclose(full[k], ref[k], rtol=0, atol=1e-5), k
+    p2 = DiZOProjector(pp, max_iters=2, dp_group=False) if mode == "full" else None
+    from dizo_b200.models.generate import generate
+    ids = batch(7).input_ids[:, :9].long()
+    mask = torch.ones_like(ids); mask[1, :3] = 0; ids[1, :3] = 0
+    want = generate(solo, ids, mask, max_new_tokens=5, pad_token_id=0)
+    got = generate(pp, ids, mask, max_new_tokens=5, pad_token_id=0)
+    assert want == got, (want, got)
+    print("PP_OK", rank)
+''')
+
+
+def test_llama_pipeline_matches_single_process():
+    outs = _run_ranks(PP_LLAMA_SCRIPT, 2)
+    for rc, out in outs:
+        assert rc == 0 and "PP_OK" in out, out[-3000:]
+
+
 def test_pipeline_matches_single_process():
     outs = _run_ranks(PP_SCRIPT, 3)
     for rc, out in outs:

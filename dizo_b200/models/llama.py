@@ -251,7 +251,8 @@ class LlamaModel(OPTModel):
         cfg = self.config
         B, L, d = h.shape
         x = llama_ops.rmsnorm(h, w.ln1_w, cfg.rms_norm_eps)
-        qkv = self._rope(gemm.linear(x.reshape(B * L, d), w.qkv_w), L, 0)
+        qkv = gemm.linear_qkv_rope(x.reshape(B * L, d), w.qkv_w, L, self.num_prefix, cfg.num_attention_heads,
+                                   cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta)
         if self.kv_capture is not None:
             self.kv_capture.append(qkv)
         ctx = attn_ops.attention(qkv.view(B, L, 3 * d), cfg.num_attention_heads, batch.pad_left,

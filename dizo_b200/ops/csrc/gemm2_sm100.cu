@@ -46,6 +46,9 @@ struct Gemm2Args {
   int out_fp32;
   float out_scale;
   uint32_t* err;
+  // act 4: rotary embedding of a fused q | k | v projection in the epilogue (head dim 128)
+  const float* rope_cs;     // fp32 [n_pos][64][2] = (cos, sin)
+  int rope_L, rope_pos0, rope_n_pos, rope_H, rope_Hkv;
 };
 
 __device__ __forceinline__ void tile_coords2(int tile, const Gemm2Args& p, int& mb, int& nb) {
@@ -186,11 +189,69 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const long long row = (long long)mb * G2_BM + row_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quad * 32) << 16);
-      if (p.act == 3) {
+      if (p.act == 4) {
+        // The tile holds two heads of 128 columns of q | k | v (raw layout: H query heads, Hkv key heads, Hkv value
+        // heads).  q and k heads are rotated - columns j and j + 64 of a head pair up, angle from the row's position
+        // and j - and written to the expanded layout [q: H heads | k: H heads | v: H heads], k / v heads repeated
+        // H / Hkv times; v heads are copied.
+        const int H = p.rope_H, Hkv = p.rope_Hkv, rep = H / Hkv;
+        int pos = p.rope_pos0 + (int)(row % p.rope_L);
+        pos = pos < p.rope_n_pos ? pos : p.rope_n_pos - 1;
+        const float4* csr = reinterpret_cast<const float4*>(p.rope_cs + (long long)pos * 128);
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo;
+        auto store32 = [&](int head_out, int n_rep, int col, const float* v) {
+          // 32 consecutive columns of one head, to n_rep consecutive output heads
+          uint4 o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]); o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]); o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          }
+          for (int r = 0; r < n_rep; ++r) {
+            uint4* op4 = reinterpret_cast<uint4*>(orow + (long long)(head_out + r) * 128 + col);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o[q];
+          }
+        };
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          const int g = nb * 2 + hh;                    // head in the raw layout
+          const bool is_q = g < H, is_k = !is_q && g < H + Hkv;
+          const int head_out = is_q ? g : (is_k ? H + (g - H) * rep : 2 * H + (g - H - Hkv) * rep);
+          const int n_rep = is_q ? 1 : rep;
+#pragma unroll 1
+          for (int pc = 0; pc < 2; ++pc) {
+            uint32_t a[32], b[32];
+            __syncwarp();                                 // lanes of rows past M skipped the stores above
+            tmem_ld_32x32(t_row + hh * 128 + pc * 32, a);
+            tmem_ld_32x32(t_row + hh * 128 + 64 + pc * 32, b);
+            tmem_ld_wait();
+            if (!row_ok) continue;
+            float lo[32], hi[32];
+            if (is_q || is_k) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float4 c = __ldg(csr + pc * 16 + i);       // (cos, sin) of frequencies 2i and 2i + 1
+                const float a0 = __uint_as_float(a[2 * i]), a1 = __uint_as_float(a[2 * i + 1]);
+                const float b0 = __uint_as_float(b[2 * i]), b1 = __uint_as_float(b[2 * i + 1]);
+                lo[2 * i] = a0 * c.x - b0 * c.y;      lo[2 * i + 1] = a1 * c.z - b1 * c.w;
+                hi[2 * i] = b0 * c.x + a0 * c.y;      hi[2 * i + 1] = b1 * c.z + a1 * c.w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) { lo[i] = __uint_as_float(a[i]); hi[i] = __uint_as_float(b[i]); }
+            }
+            store32(head_out, n_rep, pc * 32, lo);
+            store32(head_out, n_rep, 64 + pc * 32, hi);
+          }
+        }
+      } else if (p.act == 3) {
         // out[row, nb * 128 + j] = silu(gate_j) * up_j from the fp32 accumulators, one rounding to bf16
 #pragma unroll 1
         for (int c = 0; c < G2_BN / 64; ++c) {
           uint32_t g[32], u[32];
+          __syncwarp();                                   // lanes of rows past M skipped the stores above
           tmem_ld_32x32(t_row + c * 32, g);
           tmem_ld_32x32(t_row + G2_BN / 2 + c * 32, u);
           tmem_ld_wait();
@@ -331,11 +392,40 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 using namespace dz;
 DZ_DEBUG_TU(gemm2)
 
+static int gemm2_launch(const void* A, long long lda, const void* W, long long ldw, void* out,
+                        long long ldo, const void* bias, const void* residual, long long ldr,
+                        int M, int N, int K, int act, int out_fp32, float out_scale,
+                        uint32_t* err, cudaStream_t stream, const Gemm2Args* rope);
+
 // Same contract as dz_gemm_bf16_tn (gemm_sm100.cu); computed by pairs of SMs.
 extern "C" int dz_gemm2_bf16_tn(const void* A, long long lda, const void* W, long long ldw, void* out,
                                 long long ldo, const void* bias, const void* residual, long long ldr,
                                 int M, int N, int K, int act, int out_fp32, float out_scale,
                                 uint32_t* err, cudaStream_t stream) {
+  if (act == 4) return DZ_ERR_ARG;
+  return gemm2_launch(A, lda, W, ldw, out, ldo, bias, residual, ldr, M, N, K, act, out_fp32, out_scale, err,
+                      stream, nullptr);
+}
+
+// Fused q | k | v projection with the rotary embedding in the epilogue: A [M, K], W [(H + 2 Hkv) * 128, K] ->
+// out [M, 3 * H * 128] bf16 (q | k | v with the k / v heads repeated H / Hkv times), row m at position
+// pos0 + m % L; cs: fp32 [n_pos][64][2] (cos, sin).  Head dim 128, H and Hkv even.
+extern "C" int dz_gemm2_qkv_rope(const void* A, long long lda, const void* W, long long ldw, void* out,
+                                 long long ldo, const float* cs, int M, int K, int L, int pos0, int n_pos,
+                                 int H, int Hkv, uint32_t* err, cudaStream_t stream) {
+  if (!cs || L <= 0 || pos0 < 0 || n_pos < pos0 + L || H <= 0 || Hkv <= 0 || (H & 1) || (Hkv & 1) || H % Hkv)
+    return DZ_ERR_ARG;
+  if (ldo < 3LL * H * 128 || (reinterpret_cast<uintptr_t>(cs) & 15)) return DZ_ERR_ALIGN;
+  Gemm2Args r{};
+  r.rope_cs = cs; r.rope_L = L; r.rope_pos0 = pos0; r.rope_n_pos = n_pos; r.rope_H = H; r.rope_Hkv = Hkv;
+  return gemm2_launch(A, lda, W, ldw, out, ldo, nullptr, nullptr, 0, M, (H + 2 * Hkv) * 128, K, 4, 0, 1.0f, err,
+                      stream, &r);
+}
+
+static int gemm2_launch(const void* A, long long lda, const void* W, long long ldw, void* out,
+                        long long ldo, const void* bias, const void* residual, long long ldr,
+                        int M, int N, int K, int act, int out_fp32, float out_scale,
+                        uint32_t* err, cudaStream_t stream, const Gemm2Args* rope) {
   if (!A || !W || !out || M <= 0 || N <= 0 || K <= 0) return DZ_ERR_ARG;
   if ((K & 7) || (lda & 7) || (ldw & 7)) return DZ_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return DZ_ERR_ALIGN;
@@ -352,6 +442,10 @@ extern "C" int dz_gemm2_bf16_tn(const void* A, long long lda, const void* W, lon
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   a.ldr = ldr; a.act = act; a.out_fp32 = out_fp32; a.out_scale = out_scale; a.err = err;
+  if (rope) {
+    a.rope_cs = rope->rope_cs; a.rope_L = rope->rope_L; a.rope_pos0 = rope->rope_pos0;
+    a.rope_n_pos = rope->rope_n_pos; a.rope_H = rope->rope_H; a.rope_Hkv = rope->rope_Hkv;
+  }
   a.num_m = (M + G2_BM - 1) / G2_BM;
   a.num_n = (N + G2_BN - 1) / G2_BN;
   a.group_m = a.num_m < 8 ? a.num_m : 8;

@@ -20,6 +20,7 @@ ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
 _VARIANT = int(os.environ.get("DIZO_GEMM_VARIANT", "0"))
 # 0: SwiGLU as a GEMM followed by the stand-alone silu_mul kernel (for A/B measurements)
 _SWIGLU_FUSED = os.environ.get("DIZO_SWIGLU_FUSED", "1") != "0"
+_ROPE_FUSED = os.environ.get("DIZO_ROPE_FUSED", "1") != "0"
 
 
 def linear_reference(x, w, bias=None, act=None, residual=None, scale: float = 1.0,
@@ -65,6 +66,36 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         M, N, K, 3, 0, ctypes.c_float(1.0), _lib.ptr(_lib.err_word(x.device)), _lib.stream_ptr())
     _lib.check(rc, "dz_gemm2_bf16_tn")
     return out.reshape(*x.shape[:-1], F)
+
+
+def linear_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, L: int, pos0: int, H: int, Hkv: int, hd: int,
+                    theta: float) -> torch.Tensor:
+    """Fused q | k | v projection followed by the rotary embedding (and the grouped-query head expansion):
+    x [M, K], w_qkv [(H + 2 Hkv) hd, K] -> [M, 3 H hd], row m at position ``pos0 + m % L``.
+
+    With head dim 128 and even head counts the rotation runs in the two-SM GEMM's epilogue (a 256-column
+    accumulator tile holds two whole heads, columns j and j + 64 of a head pair up): the raw projection never
+    reaches memory.  Other shapes go through :func:`linear` and the stand-alone rotary kernel."""
+    from . import llama as llama_ops
+    N, K = w_qkv.shape
+    x2 = x.reshape(-1, K)
+    M = x2.shape[0]
+    fused = (_ROPE_FUSED and x.is_cuda and _VARIANT in (0, 2) and hd == 128 and H % 2 == 0 and Hkv % 2 == 0
+             and M >= 256 and ((M + 255) // 256) * (N // 256) >= 48)
+    if not fused:
+        return llama_ops.rope_qkv(linear(x2, w_qkv), L, pos0, H, Hkv, hd, theta)
+    assert x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and w_qkv.stride(-1) == 1
+    assert N == (H + 2 * Hkv) * hd
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    cs = llama_ops.rope_table(pos0 + L, hd, theta, x.device)
+    out = torch.empty((M, 3 * H * hd), dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().dz_gemm2_qkv_rope(
+        _lib.ptr(x2), ctypes.c_longlong(x2.stride(0)), _lib.ptr(w_qkv), ctypes.c_longlong(w_qkv.stride(0)),
+        _lib.ptr(out), ctypes.c_longlong(out.stride(0)), _lib.ptr(cs), M, K, L, pos0, cs.shape[0], H, Hkv,
+        _lib.ptr(_lib.err_word(x.device)), _lib.stream_ptr())
+    _lib.check(rc, "dz_gemm2_qkv_rope")
+    return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,

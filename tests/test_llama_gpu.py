@@ -83,6 +83,33 @@ def test_gemm_with_swiglu_epilogue(M, K, F):
     _sync_ok()
 
 
+@pytest.mark.parametrize("B,L,K,H,Hkv,pos0", [(8, 256, 512, 8, 8, 0), (8, 250, 1024, 8, 2, 5), (4, 1024, 256, 32, 8, 3),
+                                               (2, 64, 256, 8, 8, 0)])
+def test_gemm_with_rotary_epilogue(B, L, K, H, Hkv, pos0):
+    """q | k | v projection with the rotation (and the grouped-query head expansion) in the two-SM GEMM's epilogue
+    against the fp32 statement (the last shape takes the unfused route)."""
+    from dizo_b200.ops import gemm
+    hd, M = 128, B * L
+    g = torch.Generator(device=DEV).manual_seed(M + K + H)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn((H + 2 * Hkv) * hd, K, device=DEV, generator=g) * K ** -0.5).bfloat16()
+    y = gemm.linear_qkv_rope(x, w, L, pos0, H, Hkv, hd, 10000.0)
+    _sync_ok()
+    assert y.shape == (M, 3 * H * hd)
+    ref = llama_ops.rope_qkv_reference(x.float() @ w.float().t(), L, pos0, H, Hkv, hd, 10000.0)
+    assert _rel(y, ref) < 6e-3
+    for sec in range(3):                                   # every section on its own (q, k, v)
+        assert _rel(y[:, sec * H * hd:(sec + 1) * H * hd], ref[:, sec * H * hd:(sec + 1) * H * hd]) < 6e-3
+    unfused = llama_ops.rope_qkv(gemm.linear(x, w), L, pos0, H, Hkv, hd, 10000.0)
+    assert _rel(y, unfused) < 1e-2
+    # repeated k / v heads are bit-equal copies
+    rep = H // Hkv
+    if rep > 1:
+        k = y[:, H * hd:2 * H * hd].view(M, Hkv, rep, hd)
+        assert torch.equal(k[:, :, 0], k[:, :, rep - 1])
+    _sync_ok()
+
+
 @pytest.mark.parametrize("name", ["llama-tiny", "llama-tiny-gqa"])
 def test_model_matches_cpu_statement_and_zo_step_runs(name):
     from dizo_b200.data.synthetic import synthetic_batch

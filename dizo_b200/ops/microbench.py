@@ -102,6 +102,24 @@ def main():
         fl = 2.0 * a.m * a.n * a.k
         peak = peaks["bf16_tflops_sustained" if a.seconds else "bf16_tflops"]
         out.update(shape=[a.m, a.n, a.k])
+        if a.flags in ("swiglu", "rope"):
+            # fused epilogues of the LLaMA block: n = 2F (gate | up) or (H + 2 Hkv) * 128 (q | k | v, H = Hkv);
+            # the alternative is the plain GEMM followed by the stand-alone kernel
+            from . import gemm as gemm_mod
+            from . import llama as llama_ops
+            H = a.n // (3 * 128)
+            L = a.seq
+            fused = (lambda: gemm_mod.linear_swiglu(x, w)) if a.flags == "swiglu" else \
+                (lambda: gemm_mod.linear_qkv_rope(x, w, L, 0, H, H, 128, 10000.0))
+            plain = (lambda: llama_ops.silu_mul(linear(x, w, out=y))) if a.flags == "swiglu" else \
+                (lambda: llama_ops.rope_qkv(linear(x, w, out=y), L, 0, H, H, 128, 10000.0))
+            ms = time_fn(fused, a.iters, seconds=a.seconds, flush=flush)
+            out.update(epilogue=a.flags, ours_ms=ms, ours_tflops=fl / ms / 1e9,
+                       ours_frac_of_measured=fl / ms / 1e9 / peak)
+            ms = time_fn(plain, a.iters, seconds=a.seconds, flush=flush)
+            out.update(unfused_ms=ms, unfused_tflops=fl / ms / 1e9)
+            print(json.dumps(out))
+            return
         if a.only != "lib":
             ms = time_fn(lambda: linear(x, w, out=y, tile_n=a.tile_n), a.iters, seconds=a.seconds, flush=flush)
             out.update(ours_ms=ms, ours_tflops=fl / ms / 1e9, ours_frac_of_measured=fl / ms / 1e9 / peak)

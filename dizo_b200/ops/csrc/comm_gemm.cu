@@ -74,6 +74,7 @@ struct CommGemmArgs {
   long long ldr;
   int act, out_fp32;
   float out_scale;
+  int wide_store;                // local bf16 output rows are 32-byte aligned: 256-bit stores
   // ---- gathered operand: 0 none, 1 = rows of A come from peers, 2 = rows of W come from peers
   int gather;
   int rows_per_src;              // rows owned by each source rank
@@ -412,16 +413,15 @@ __device__ __forceinline__ void cg_drain_tile(const CommGemmArgs& p, const uint3
                        : "memory");
         }
       } else if (full_chunk) {
-        uint4* op4 = reinterpret_cast<uint4*>(orow_bf + col0);
+        uint4 o[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint4 o;
-          o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-          o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-          o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-          o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-          if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
+          o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+          o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+          o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+          o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
         }
+        store_row32(orow_bf + col0, o, p.wide_store != 0);
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
@@ -969,6 +969,7 @@ extern "C" int dz_comm_gemm(const DzCommGemmDesc* d, uint32_t* err, cudaStream_t
   a.out = d->out; a.ldo = d->ldo;
   a.bias = (const __nv_bfloat16*)d->bias; a.residual = (const __nv_bfloat16*)d->residual; a.ldr = d->ldr;
   a.act = d->act; a.out_fp32 = d->out_fp32; a.out_scale = d->out_scale;
+  a.wide_store = d->out && !d->out_fp32 && !(reinterpret_cast<uintptr_t>(d->out) & 31) && !(d->ldo & 15);
   a.gather = has_gemm ? d->gather : 0; a.rows_per_src = d->rows_per_src; a.wait_self = d->wait_self;
   a.src_period = d->src_period;
   a.ready_flags = (const uint32_t*)d->ready_flags; a.ready_epoch = d->ready_epoch;

@@ -328,6 +328,26 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+// 32 consecutive bf16 outputs of one lane's row: two 32-byte stores (one whole sector each) when the address allows,
+// else four 16-byte stores.
+__device__ __forceinline__ void store_row32(__nv_bfloat16* op, const uint4 (&o)[4], bool wide) {
+  if (wide) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (DZ_STORE_OK(op + h * 16, 32))
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(op + h * 16),
+                     "r"(o[2 * h].x), "r"(o[2 * h].y), "r"(o[2 * h].z), "r"(o[2 * h].w), "r"(o[2 * h + 1].x),
+                     "r"(o[2 * h + 1].y), "r"(o[2 * h + 1].z), "r"(o[2 * h + 1].w)
+                     : "memory");
+    }
+  } else {
+    uint4* op4 = reinterpret_cast<uint4*>(op);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o[q];
+  }
+}
+
 __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }

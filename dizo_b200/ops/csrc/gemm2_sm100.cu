@@ -17,6 +17,7 @@
 //              the leader's "accumulator empty" barrier (count 8 = 4 warps x 2 CTAs)
 // Every wait is bounded (see common.cuh); both CTAs meet at a cluster barrier before TMEM is
 // released, so neither exits while the other may still read its shared memory.
+#include <stdlib.h>
 #include "common.cuh"
 #include "cluster2sm.cuh"
 #include "host_util.h"
@@ -47,6 +48,7 @@ struct Gemm2Args {
   float out_scale;
   uint32_t* err;
   // act 4: rotary embedding of a fused q | k | v projection in the epilogue (head dim 128)
+  int wide_store;           // out and its row pitch are 32-byte aligned: 256-bit stores in the bf16 epilogues
   const float* rope_cs;     // fp32 [n_pos][64][2] = (cos, sin)
   int rope_L, rope_pos0, rope_n_pos, rope_H, rope_Hkv;
 };
@@ -207,12 +209,8 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]); o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
             o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]); o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
           }
-          for (int r = 0; r < n_rep; ++r) {
-            uint4* op4 = reinterpret_cast<uint4*>(orow + (long long)(head_out + r) * 128 + col);
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o[q];
-          }
+          for (int r = 0; r < n_rep; ++r)
+            store_row32(orow + (long long)(head_out + r) * 128 + col, o, p.wide_store != 0);
         };
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
@@ -260,17 +258,16 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const float x = __uint_as_float(a);
             return x / (1.f + __expf(-x)) * __uint_as_float(b);
           };
-          uint4* op4 = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo +
-                                                nb * (G2_BN / 2) + c * 32);
+          uint4 o[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_bf16x2(f(g[q * 8 + 0], u[q * 8 + 0]), f(g[q * 8 + 1], u[q * 8 + 1]));
-            o.y = pack_bf16x2(f(g[q * 8 + 2], u[q * 8 + 2]), f(g[q * 8 + 3], u[q * 8 + 3]));
-            o.z = pack_bf16x2(f(g[q * 8 + 4], u[q * 8 + 4]), f(g[q * 8 + 5], u[q * 8 + 5]));
-            o.w = pack_bf16x2(f(g[q * 8 + 6], u[q * 8 + 6]), f(g[q * 8 + 7], u[q * 8 + 7]));
-            if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
+            o[q].x = pack_bf16x2(f(g[q * 8 + 0], u[q * 8 + 0]), f(g[q * 8 + 1], u[q * 8 + 1]));
+            o[q].y = pack_bf16x2(f(g[q * 8 + 2], u[q * 8 + 2]), f(g[q * 8 + 3], u[q * 8 + 3]));
+            o[q].z = pack_bf16x2(f(g[q * 8 + 4], u[q * 8 + 4]), f(g[q * 8 + 5], u[q * 8 + 5]));
+            o[q].w = pack_bf16x2(f(g[q * 8 + 6], u[q * 8 + 6]), f(g[q * 8 + 7], u[q * 8 + 7]));
           }
+          store_row32(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + nb * (G2_BN / 2) + c * 32, o,
+                      p.wide_store != 0);
         }
       } else {
 #pragma unroll 1
@@ -346,16 +343,15 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           } else {
             __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
             if (full_chunk) {
-              uint4* op4 = reinterpret_cast<uint4*>(op);
+              uint4 o[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                uint4 o;
-                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                if (DZ_STORE_OK(op4 + q, 16)) op4[q] = o;
+                o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
               }
+              store_row32(op, o, p.wide_store != 0);
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
@@ -442,6 +438,9 @@ static int gemm2_launch(const void* A, long long lda, const void* W, long long l
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   a.ldr = ldr; a.act = act; a.out_fp32 = out_fp32; a.out_scale = out_scale; a.err = err;
+  // 256-bit stores need 32-byte aligned rows (DIZO_GEMM_ST256=0 keeps the 128-bit ones, for measurements)
+  static const bool st256 = [] { const char* e = getenv("DIZO_GEMM_ST256"); return !(e && e[0] == '0'); }();
+  a.wide_store = st256 && !out_fp32 && !(reinterpret_cast<uintptr_t>(out) & 31) && !(ldo & 15);
   if (rope) {
     a.rope_cs = rope->rope_cs; a.rope_L = rope->rope_L; a.rope_pos0 = rope->rope_pos0;
     a.rope_n_pos = rope->rope_n_pos; a.rope_H = rope->rope_H; a.rope_Hkv = rope->rope_Hkv;

@@ -49,6 +49,7 @@ struct Gemm2Args {
   uint32_t* err;
   // act 4: rotary embedding of a fused q | k | v projection in the epilogue (head dim 128)
   int wide_store;           // out and its row pitch are 32-byte aligned: 256-bit stores in the bf16 epilogues
+  int wide_residual;        // the same for the residual rows: 256-bit loads
   const float* rope_cs;     // fp32 [n_pos][64][2] = (cos, sin)
   int rope_L, rope_pos0, rope_n_pos, rope_H, rope_Hkv;
 };
@@ -312,7 +313,22 @@ gemm2_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (row_ok) {
           if (p.residual) {
             const __nv_bfloat16* rp = p.residual + row * p.ldr + col0;
-            if (full_chunk) {
+            if (full_chunk && p.wide_residual) {
+              // one whole 32-byte sector per lane and load
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint32_t b[8];
+                asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]),
+                               "=r"(b[7])
+                             : "l"(rp + h * 16));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  v[h * 16 + 2 * j] += bf16_lo(b[j]);
+                  v[h * 16 + 2 * j + 1] += bf16_hi(b[j]);
+                }
+              }
+            } else if (full_chunk) {
               const uint4* rp4 = reinterpret_cast<const uint4*>(rp);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -441,6 +457,7 @@ static int gemm2_launch(const void* A, long long lda, const void* W, long long l
   // 256-bit stores need 32-byte aligned rows (DIZO_GEMM_ST256=0 keeps the 128-bit ones, for measurements)
   static const bool st256 = [] { const char* e = getenv("DIZO_GEMM_ST256"); return !(e && e[0] == '0'); }();
   a.wide_store = st256 && !out_fp32 && !(reinterpret_cast<uintptr_t>(out) & 31) && !(ldo & 15);
+  a.wide_residual = st256 && residual && !(reinterpret_cast<uintptr_t>(residual) & 31) && !(ldr & 15);
   if (rope) {
     a.rope_cs = rope->rope_cs; a.rope_L = rope->rope_L; a.rope_pos0 = rope->rope_pos0;
     a.rope_n_pos = rope->rope_n_pos; a.rope_H = rope->rope_H; a.rope_Hkv = rope->rope_Hkv;

@@ -184,3 +184,18 @@ def test_command_line_first_order_paths(tmp_path, monkeypatch, extra):
                "--per_device_train_batch_size", "4", "--output_dir", str(tmp_path / "run"),
                "--train_as_classification", "--train_set_seed", "0", *extra])
     assert rc == 0
+
+
+def test_fused_projection_entry_points_have_cpu_statements():
+    """gemm.linear_swiglu / gemm.linear_qkv_rope (GEMM epilogues on the device) fall back to GEMM + elementwise here."""
+    from dizo_b200.ops import gemm
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(6, 32, generator=g)
+    w = torch.randn(2 * 48, 32, generator=g) * 0.2
+    acc = x @ w.t()
+    assert torch.allclose(gemm.linear_swiglu(x, w), torch.nn.functional.silu(acc[:, :48]) * acc[:, 48:], atol=1e-5)
+    H, Hkv, hd, L = 4, 2, 16, 3
+    wq = torch.randn((H + 2 * Hkv) * hd, 32, generator=g) * 0.2
+    got = gemm.linear_qkv_rope(x, wq, L, 2, H, Hkv, hd, 10000.0)
+    want = llama_ops.rope_qkv_reference(x @ wq.t(), L, 2, H, Hkv, hd, 10000.0)
+    assert got.shape == (6, 3 * H * hd) and torch.allclose(got, want, atol=1e-5)

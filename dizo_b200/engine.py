@@ -317,3 +317,74 @@ class DiZOProjector:
             self.fo_gamma = sd["fo_gamma"].to(self.model.device).requires_grad_(True)
             self.fo_opt = torch.optim.Adam([self.fo_gamma], lr=self.proj_lr)
             self.fo_opt.load_state_dict(sd["fo_opt"])
+
+
+class DiZO:
+    """The reference's ``DiZO(model, norm_mode, exclude_list)`` module (large_models/trainer.py:378-614) as a
+    thin facade over :class:`DiZOProjector`, for callers that drive the projection by hand.
+
+    The reference copies ``theta_0 + gamma / ||theta - theta_0|| (theta - theta_0)`` into the weights before a
+    forward and divides it out again afterwards (``apply_constraints`` / ``reverse_constraints``); here a forward
+    blends the constrained tensors in flight, so theta is only written when ``apply=True``:
+
+    * ``constraints`` - the gamma vector (one entry per constrained tensor, in ``constraints_name`` order),
+      ``alpha`` - gamma / (||theta - theta_0|| + 1e-8), ``ts`` - the norms, ``init`` - True until gamma has
+      been initialised to the norms;
+    * ``apply_constraints(apply=False)`` - measure the norms, initialise gamma on the first call, refresh
+      alpha; with ``apply=True`` project theta in place (one sweep);
+    * ``reverse_constraints()`` - nothing to undo (kept for call-site compatibility);
+    * ``perturb_gamma(random_seed, scaling_factor)`` - gamma += scaling_factor * zo_eps * z(random_seed),
+      clipped as the reference clips it, alpha refreshed;
+    * ``zo_forward(batch)`` / ``forward(batch, apply=False)`` - the loss under the current alpha.
+    """
+
+    def __init__(self, model: OPTModel, norm_mode: str = "l2norm", exclude_list: list[str] | None = None, **kw):
+        names = list(model.dizo_include_names())
+        if exclude_list:
+            drop = set(exclude_list)
+            names = [n for n in names if n not in drop]
+        self.norm_mode = norm_mode
+        self.exclude_list = list(exclude_list or [])
+        self.projector = DiZOProjector(model, include=names, norm_mode=norm_mode, **kw)
+        self.model = model
+        self.constraints_name = list(model.arena.slot_names)
+        self.init = True
+        self._seed = 0
+
+    @property
+    def constraints(self) -> torch.Tensor:
+        return self.projector.gs.gamma
+
+    @property
+    def alpha(self) -> torch.Tensor:
+        return self.projector.gs.alpha
+
+    @property
+    def ts(self) -> torch.Tensor:
+        return self.projector.gs.ts
+
+    def apply_constraints(self, new=None, pre_trained=None, constraint_iterator=None, apply: bool = False) -> None:
+        self.projector.measure()
+        self.projector._begin(reinit=self.init)
+        self.init = False
+        if apply:
+            self.projector.project()
+
+    def reverse_constraints(self, new=None, pre_trained=None) -> None:
+        return None
+
+    def perturb_gamma(self, random_seed: int | None = None, scaling_factor: float = 1.0) -> None:
+        if random_seed is not None:
+            self._seed = int(random_seed)
+            self.projector.gs.perturb(float(scaling_factor), seed=self._seed, it=0)
+        else:
+            self.projector.gs.perturb(float(scaling_factor))       # the same z again (restore / flip)
+
+    def zo_forward(self, batch: Batch) -> torch.Tensor:
+        return self.model.loss(batch, Transform(alpha=self.projector.gs.alpha))
+
+    def forward(self, batch: Batch, apply: bool = False) -> torch.Tensor:
+        self.apply_constraints(apply=apply)
+        return self.model.loss(batch) if apply else self.zo_forward(batch)
+
+    __call__ = forward

@@ -47,3 +47,36 @@ def test_prefix_reparameterisation_mlp_trains_the_mlp_and_matches_autograd_forwa
                   prefix_embed_dim=16, prefix_mid_dim=24).init_random(9)
     m2.load_state_dict(sd)
     assert abs(m2.loss(b).item() - m.loss(b).item()) < 1e-6
+
+
+def test_dizo_module_facade():
+    """The reference-shaped DiZO module: constraints / alpha / ts, apply_constraints, perturb_gamma, zo_forward."""
+    import torch
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.engine import DiZO
+    from dizo_b200.models.opt import OPTModel, preset
+    cfg = preset("opt-tiny")
+    m = OPTModel(cfg, "cpu", torch.float32).init_random(0)
+    d = DiZO(m, "l2norm", exclude_list=[m.dizo_include_names()[0]])
+    assert len(d.constraints_name) == len(m.dizo_include_names()) - 1 and d.init
+    g = torch.Generator().manual_seed(3)
+    for n in d.constraints_name:
+        m.param(n).add_(torch.randn(m.param(n).shape, generator=g) * 0.02)
+    b = synthetic_batch(0, 4, 16, cfg.vocab_size, cand_ids=(10, 20))
+    l0 = float(m.loss(b))
+    d.apply_constraints()
+    assert not d.init and torch.allclose(d.constraints, d.ts) and torch.allclose(d.alpha, torch.ones_like(d.alpha), atol=1e-6)
+    assert abs(float(d.zo_forward(b)) - l0) < 1e-6
+    d.perturb_gamma(5, 1.0)
+    lp = float(d.zo_forward(b))
+    d.perturb_gamma(None, -2.0)
+    lm = float(d.zo_forward(b))
+    d.perturb_gamma(None, 1.0)
+    assert lp != lm and torch.allclose(d.alpha, torch.ones_like(d.alpha), atol=1e-5)
+    # apply=True writes the projection into theta: with gamma = 0.5 ts the distance to the anchor halves
+    before = (m.param(d.constraints_name[0]) - m.arena.anchor_view(d.constraints_name[0])).norm()
+    d.constraints.mul_(0.5)
+    d.projector.gs.alpha.copy_(d.constraints / (d.ts + 1e-8))
+    d.projector.project()
+    after = (m.param(d.constraints_name[0]) - m.arena.anchor_view(d.constraints_name[0])).norm()
+    assert abs(float(after / before) - 0.5) < 1e-4

@@ -87,6 +87,36 @@ class DizoTrainerView:
         self.i += 1
 
 
+def dizo_trainer(model: OPTModel, pgmloader, norm_mode: str = "l2norm", proj_lr: float = 0.1, max_iters: int = 10,
+                 exclude_list: Optional[List[str]] = None, seed: int = 0, to_batch: Optional[Callable] = None,
+                 **projector_kw) -> DizoTrainerView:
+    """The reference's constructor ``dizo_trainer(base_model, pgmloader, norm_mode, proj_lr, max_iters,
+    exclude_list)`` (large_models/trainer.py:744-761) for callers that build the projection loop themselves.
+    ``model`` takes the place of ``base_model``: the anchor theta_0 of the constrained tensors lives in the
+    model's arena.  ``pgmloader`` is any re-iterable of batches (``to_batch`` converts collated inputs); the
+    search draws from its own endless iterator over it, as the reference does (:762-763)."""
+    names = [n for n in model.dizo_include_names() if n not in set(exclude_list or [])]
+    proj = DiZOProjector(model, include=names, norm_mode=norm_mode, proj_lr=proj_lr, max_iters=max_iters,
+                         **projector_kw)
+    state = {"it": iter(pgmloader)}
+
+    def next_batch():
+        try:
+            b = next(state["it"])
+        except StopIteration:
+            state["it"] = iter(pgmloader)
+            b = next(state["it"])
+        return to_batch(b) if to_batch is not None else b
+
+    rng = np.random.RandomState(seed + 7919)
+    fo_loss = None
+    from .models import gamma_grad
+    if not gamma_grad.supported(model):
+        from .models.opt_autograd import make_fo_loss
+        fo_loss = make_fo_loss(model)
+    return DizoTrainerView(proj, next_batch, lambda: int(rng.randint(1_000_000_000)), fo_loss)
+
+
 class OurTrainer:
     def __init__(self, model: OPTModel, args: OurArguments, train_dataset=None, eval_dataset=None,
                  processing_class=None, tokenizer=None, data_collator=None, engine: ZOEngine | None = None,

@@ -80,3 +80,21 @@ def test_dizo_module_facade():
     d.projector.project()
     after = (m.param(d.constraints_name[0]) - m.arena.anchor_view(d.constraints_name[0])).norm()
     assert abs(float(after / before) - 0.5) < 1e-4
+
+
+def test_dizo_trainer_constructor():
+    """dizo_trainer(model, pgmloader, norm_mode, proj_lr, max_iters, exclude_list): both searches run from it."""
+    import torch
+    from dizo_b200.data.synthetic import synthetic_batch
+    from dizo_b200.models.opt import OPTModel, preset
+    from dizo_b200.trainer import dizo_trainer
+    cfg = preset("opt-tiny")
+    m = OPTModel(cfg, "cpu", torch.float32).init_random(0)
+    loader = [synthetic_batch(s, 4, 16, cfg.vocab_size, cand_ids=(10, 20)) for s in range(3)]
+    t = dizo_trainer(m, loader, "l2norm", 0.1, 2)
+    g = torch.Generator().manual_seed(3)
+    for n in m.arena.slot_names:
+        m.param(n).add_(torch.randn(m.param(n).shape, generator=g) * 0.02)
+    t.dizo_zo_iters()
+    t.dizo_iters()
+    assert t.i == 2 and t.projector.searches == 2 and torch.isfinite(t.projector.gs.gamma).all()

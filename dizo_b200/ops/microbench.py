@@ -255,6 +255,14 @@ def main():
         b = torch.randn(a.d, device=dev, generator=g).bfloat16()
         y = torch.empty_like(x)
         nbytes = 4.0 * a.rows * a.d
+        if a.flags == "rms":
+            # RMSNorm of the LLaMA block (same traffic: one read, one write)
+            from . import llama as llama_ops
+            ms = time_fn(lambda: llama_ops.rmsnorm(x, w, 1e-5), a.iters, seconds=a.seconds, flush=flush)
+            out.update(kernel="rmsnorm", shape=[a.rows, a.d], ours_ms=ms, ours_gbs=nbytes / ms / 1e6,
+                       ours_frac_of_measured=nbytes / ms / 1e6 / peaks["hbm_gbs"])
+            print(json.dumps(out))
+            return
         ms = time_fn(lambda: layernorm(x, w, b, out=y), a.iters, seconds=a.seconds, flush=flush)
         out.update(shape=[a.rows, a.d], ours_ms=ms, ours_gbs=nbytes / ms / 1e6,
                    ours_frac_of_measured=nbytes / ms / 1e6 / peaks["hbm_gbs"])

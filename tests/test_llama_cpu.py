@@ -1,7 +1,6 @@
 """LLaMA-family model (RMSNorm, rotary embedding, grouped-query attention, SwiGLU) against the Hugging Face
 implementation on CPU in fp32, and through the command line (ZO training, head / prefix modes, checkpoints)."""
 import json
-import os
 
 import pytest
 import torch

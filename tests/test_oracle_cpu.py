@@ -7,8 +7,6 @@ step by step instead of statistically.  Scaled-down version of the CPU configura
 (OPT-125m architecture, eps 1e-3, lr 1e-6, projection by ZO); the full-size run is
 ``python -m baseline.cpu_oracle``.
 """
-import numpy as np
-import pytest
 import torch
 import torch.nn.functional as F
 

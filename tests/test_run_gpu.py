@@ -3,12 +3,11 @@ LoRA + prefix, evaluation, generation, checkpoint round trip."""
 import json
 import os
 
-import numpy as np
 import pytest
 import torch
 
 from dizo_b200.models.generate import generate
-from dizo_b200.models.opt import OPTModel, make_batch, preset
+from dizo_b200.models.opt import OPTModel, preset
 from dizo_b200.ops import _lib
 from dizo_b200.run import main
 

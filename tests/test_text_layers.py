@@ -1,11 +1,9 @@
 """Templates, tasks, prompt encoding, collators, metrics, argument surface (CPU)."""
 import json
-import os
 import random
 
 import numpy as np
 import pytest
-import torch
 
 from dizo_b200 import templates as T
 from dizo_b200.args import OurArguments, parse_args

@@ -13,7 +13,7 @@ from dizo_b200.evaluation import Evaluator
 from dizo_b200.models.generate import filter_logits, generate
 from dizo_b200.models.opt import OPTModel, make_batch, preset
 from dizo_b200.models.peft import init_prefix_by_real_activations
-from dizo_b200.run import Framework, main, result_file_tag
+from dizo_b200.run import main, result_file_tag
 from dizo_b200.tasks import SyntheticDataset
 from dizo_b200.trainer import OurTrainer
 from dizo_b200.utils import (DataCollatorWithPaddingAndNesting, DataCollatorForTokenClassification,
